@@ -1,0 +1,5 @@
+"""Typed configuration and the architecture registry."""
+
+from .llama import LlamaConfig, read_config_json  # noqa: F401
+from .registry import (Architecture, register_architecture, registered_architectures,  # noqa: F401
+                       resolve_architecture)

@@ -1,0 +1,85 @@
+"""Causal grouped-query attention over the paged cache.
+
+q = h Wq^T, k = h Wk^T, v = h Wv^T (no bias); q and k rotated by position; k and v appended to
+the request's cache pages; scores (q . k) / sqrt(head_dim) over the keys at positions
+<= the query's (and, with `window`, newer than position - window); softmax; weighted values;
+output projection (cuongvng/bare-cuda-4gib engine/src/model.cpp:540-572,
+engine/kernels/attention_qk.cu:49-68, softmax.cu:28-42, attention_av.cu:24-44).
+The three projections are one matrix product against [Wq; Wk; Wv], fused at load.
+
+params: `hidden`, `heads`, `kv_heads`, `head_dim`, `window` (None = every key), `position`
+(a `PartSpec` of the position family).  tensors: `q`, `k`, `v`, `o`.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..errors import ConfigError
+from ..kernels import lib as K
+from .base import KVCacheRequest, Part
+from .linear import Linear
+from .registry import build_part, register_mixer
+
+
+@register_mixer("attention")
+class Attention(Part):
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = self.params
+        self.hidden, self.heads, self.kv_heads, self.head_dim = (
+            int(p["hidden"]), int(p["heads"]), int(p["kv_heads"]), int(p["head_dim"]))
+        self.window = p.get("window")
+        if self.heads % self.kv_heads:
+            raise ConfigError(f"attention: {self.heads} heads cannot share {self.kv_heads} key/value heads")
+        self.position = build_part("position", p["position"])
+        self.scale = 1.0 / math.sqrt(self.head_dim)
+
+    def children(self):
+        return [self.position]
+
+    def local_weights(self):
+        qd, kvd = self.heads * self.head_dim, self.kv_heads * self.head_dim
+        return {"q": ((qd, self.hidden), "matrix"), "k": ((kvd, self.hidden), "matrix"),
+                "v": ((kvd, self.hidden), "matrix"), "o": ((self.hidden, qd), "matrix")}
+
+    def cache_request(self):
+        return KVCacheRequest(self.kv_heads, self.head_dim, self.window)
+
+    def state_request(self):
+        return None
+
+    def prepare(self, dtype, device) -> None:
+        t = self.tensors
+        parts = [t.pop("q"), t.pop("k"), t.pop("v")]
+        widest = torch.float32 if any(w.dtype == torch.float32 for w in parts) else parts[0].dtype
+        self.qkv = Linear(torch.cat([w.to(widest) for w in parts], dim=0), "qkv")
+        self.o = Linear(t.pop("o"), "o")
+        self.qkv.prepare(dtype)
+        self.o.prepare(dtype)
+        self.position.prepare(dtype, device)
+        if dtype == torch.bfloat16 and device.type == "cuda":
+            from ..kernels import attention as fast
+            self.fast = fast.plan_for(self.head_dim, self.heads, self.kv_heads)
+        else:
+            self.fast = None
+
+    def forward(self, ctx, call, h: torch.Tensor) -> K.Partials:
+        n = ctx.n_tokens
+        qd = self.heads * self.head_dim
+        qkv = self.qkv.forward(ctx, h, n, ctx.dtype, "qkv", allow_partials=True)
+        q = ctx.ws.get("q", (n, qd), ctx.dtype)
+        inv_freq = self.position.fused_rotation()
+        K.rope_cache_write(qkv, q, call.cache, ctx.positions, ctx.row_seq, inv_freq, self.heads,
+                           call.writes_cache, n, ctx.stream)
+        out = ctx.ws.get("attn_out", (n, qd), ctx.dtype)
+        window = int(self.window) if self.window else 0
+        if self.fast is not None and ctx.use_fast_attention:
+            from ..kernels import attention as fast
+            fast.run(ctx, self.fast, q, out, call.cache, self.scale, window)
+        else:
+            K.attention_plain(q, out, call.cache, ctx.positions, ctx.row_seq, self.heads, n,
+                              self.scale, window, ctx.stream)
+        return self.o.forward(ctx, out, n, torch.float32, "attn_proj", allow_partials=True)

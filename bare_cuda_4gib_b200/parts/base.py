@@ -1,0 +1,89 @@
+"""Interfaces of the part families, and what a step hands to them.
+
+Families and the one method each must have besides `weight_specs` / `bind`:
+
+* norm          `forward(ctx, residual, delta, rows, row_index=None) -> activations`
+                adds `delta` (a `Partials`, or None) into the float32 residual stream, then
+                normalises; returns [rows, hidden] in the step's activation type.
+* position      either `fused_rotation()` -> float32 inverse frequencies [head_dim / 2] that the
+                attention kernels apply themselves, or `apply(ctx, q, k)` on separate tensors.
+* mixer         `forward(ctx, call, h) -> Partials` (the mixer's contribution to the residual);
+                `cache_request()` -> `KVCacheRequest` or None; `state_request()` ->
+                `StateRequest` or None.  The cache manager serves both.
+* feed_forward  `forward(ctx, h) -> Partials`
+* block         `forward(ctx, call, residual, pending) -> Partials`: runs one layer; `pending` is
+                the previous layer's contribution that has not been added to the residual yet.
+* embedding     `forward(ctx) -> residual [tokens, hidden] float32`
+* head          `forward(ctx, normed) -> logits [rows, vocab] float32`
+
+A part gets its sizes and constants from `spec.params` only.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from .spec import PartSpec, WeightSpec
+
+
+@dataclass(frozen=True)
+class KVCacheRequest:
+    """Keys and values per token that a mixer wants paged: `window` None keeps every key, a
+    number keeps the last `window` positions (older pages are given back)."""
+
+    kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateRequest:
+    """Per-request state of fixed size: one tensor of `shape` and `dtype` per request slot,
+    zeroed when a request takes the slot."""
+
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+class Part:
+    """Common ground of all parts: the spec, expected tensors, binding of loaded tensors."""
+
+    def __init__(self, spec: PartSpec):
+        self.spec = spec
+        self.params = spec.params
+        self.tensors: Dict[str, torch.Tensor] = {}
+
+    # local tensor name -> (shape, init kind); subclasses fill this in
+    def local_weights(self) -> Dict[str, Tuple[Tuple[int, ...], str]]:
+        return {}
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        out = {}
+        for local, (shape, init) in self.local_weights().items():
+            if local not in self.spec.weights:
+                raise KeyError(f"part '{self.spec.kind}' needs a file name for its tensor '{local}'")
+            out[local] = WeightSpec(self.spec.weights[local], tuple(shape), init)
+        return out
+
+    def bind(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype) -> None:
+        """Receives the loaded tensors by local name; `dtype` is the step's activation type."""
+        self.tensors = dict(tensors)
+
+    def children(self) -> List["Part"]:
+        return []
+
+    def prepare(self, dtype: torch.dtype, device: torch.device) -> None:
+        """Called once after binding, on the device: fuse tensors, build tables, compile kernels."""
+
+
+class CallContext:
+    """One run of a layer inside a step: its index in the run order, the cache it reads (and
+    whether it also writes it) and its per-request state."""
+
+    __slots__ = ("index", "cache", "writes_cache", "state")
+
+    def __init__(self, index, cache, writes_cache, state):
+        self.index, self.cache, self.writes_cache, self.state = index, cache, writes_cache, state

@@ -1,0 +1,30 @@
+"""Arrangement of a mixer and a feed-forward in one layer.
+
+"prenorm": x += mixer(norm(x)); x += feed_forward(norm(x))
+(cuongvng/bare-cuda-4gib engine/src/model.cpp:526-604).  Each add is carried out by the norm
+that follows it, so a layer hands its last contribution on, not yet added, as `pending`.
+"""
+
+from __future__ import annotations
+
+from ..kernels import lib as K
+from .registry import build_part, register_block
+
+
+@register_block("prenorm")
+class PreNormBlock:
+    def __init__(self, layer_spec):
+        self.mixer_norm = build_part("norm", layer_spec.mixer_norm)
+        self.mixer = build_part("mixer", layer_spec.mixer)
+        self.ffn_norm = build_part("norm", layer_spec.ffn_norm)
+        self.ffn = build_part("feed_forward", layer_spec.ffn)
+
+    def parts(self):
+        return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
+
+    def forward(self, ctx, call, residual, pending):
+        n = ctx.n_tokens
+        h = self.mixer_norm.forward(ctx, residual, pending, n)
+        mixed = self.mixer.forward(ctx, call, h)
+        h = self.ffn_norm.forward(ctx, residual, mixed, n)
+        return self.ffn.forward(ctx, h)

@@ -1,0 +1,32 @@
+"""RMSNorm, fused with the residual add that precedes it.
+
+out = x * rsqrt(mean(x^2) + eps) * w with eps inside the root, on the mean, and the weight
+multiplied last (cuongvng/bare-cuda-4gib engine/kernels/rmsnorm.cu:26-40).  The reference adds
+the residual in a kernel of its own (engine/kernels/residual_add.cu:20); here the add of the
+previous part's contribution and the norm are one kernel, and the residual stream stays float32.
+
+params: `size` (width), `eps`.  tensors: `weight` [size].
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..kernels import lib as K
+from .base import Part
+from .registry import register_norm
+
+
+@register_norm("rmsnorm")
+class RMSNorm(Part):
+    def local_weights(self):
+        return {"weight": ((self.params["size"],), "norm")}
+
+    def forward(self, ctx, residual: torch.Tensor, delta: Optional[K.Partials], rows: int,
+                row_index: Optional[torch.Tensor] = None, buffer: str = "normed") -> torch.Tensor:
+        out = ctx.ws.get(buffer, (rows, self.params["size"]), ctx.dtype)
+        K.add_rmsnorm(residual, delta, self.tensors["weight"], out, float(self.params["eps"]), rows,
+                      row_index, ctx.stream)
+        return out
