@@ -1,0 +1,399 @@
+// bfloat16 matrix product out[t, f] = sum_k act[t, k] * w[f, k] on the Blackwell tensor cores:
+// TMA loads into 128-byte-swizzled shared memory, tcgen05.mma with the accumulator in tensor
+// memory, tcgen05.ld for the epilogue.  This replaces the SIMT matmuls of cuongvng/bare-cuda-4gib
+// (engine/kernels/gemm_tiled.cuh:36-96 for m > 16, engine/kernels/gemv_fp16.cu:21-101 for
+// m <= 16) with one kernel for prefill and decode.
+//
+// Orientation.  The weight matrix is the 128-row MMA operand (A) and the activations are the
+// N operand (B): one thread block computes 128 output features for BN tokens, BN in
+// {16, 32, 64, 128, 256}.  A decode step with few tokens therefore still fills the 128 MMA
+// rows with weights, which is what has to be streamed from memory; a prefill step uses BN=256.
+// In tensor memory, lane = feature and column = token, so an epilogue warp stores 32
+// consecutive features of one token with one coalesced store.
+//
+// Split K.  gridDim.z thread blocks share the K range of a tile; each writes its float32 partial
+// result to out + z * partial_stride.  The consumer kernels (residual add + norm, rotation,
+// SwiGLU) add the partials in index order, so no atomics and no reduction pass are needed and
+// the result does not depend on timing.
+//
+// MODE 1 (SwiGLU): w is [gate rows; up rows]; the block accumulates gate and up for the same
+// 128 features in two accumulators and stores silu(gate) * up.
+//
+// Warps: 0 = TMA producer, 1 = tensor memory allocation + MMA issue, 2..5 = epilogue.
+// Every wait on an mbarrier is bounded: after about a second without progress the thread sets
+// the error word, every role leaves its loop, tensor memory is released and the block returns.
+
+#include "common.cuh"
+
+#include <cuda.h>
+#include <string.h>
+
+namespace {
+
+constexpr int BM = 128;      // features per block (MMA M)
+constexpr int BK = 64;       // k elements per stage (one 128-byte swizzle row)
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;
+
+constexpr int ERR_TIMEOUT_PRODUCER = 1;
+constexpr int ERR_TIMEOUT_MMA = 2;
+constexpr int ERR_TIMEOUT_EPILOGUE = 3;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ unsigned long long global_timer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Waits for the phase with the given parity; gives up after WAIT_LIMIT_NS or when another role
+// has already given up.  Returns false on giving up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long start = global_timer();
+  for (unsigned spins = 0;; ++spins) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spins & 63u) == 63u) {
+      if (*abort_flag) return false;
+      if (global_timer() - start > WAIT_LIMIT_NS) return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes, swizzled in
+// 1024-byte groups of 8 rows (start address and offsets in 16-byte units, Blackwell version 1,
+// layout type 2 = 128-byte swizzle).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);  // start address
+  d |= (uint64_t)1 << 16;                  // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;        // stride byte offset: 8 rows of 128 bytes
+  d |= (uint64_t)1 << 46;                  // descriptor version
+  d |= (uint64_t)2 << 61;                  // 128-byte swizzle
+  return d;
+}
+
+// Instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major, M x N tile.
+__host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, "
+      "%14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+
+template <int BN, int MODE>
+struct Layout {
+  static constexpr int A_TILES = MODE == 1 ? 2 : 1;
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
+  // small token tiles are the weight-streaming case: two blocks per SM keep more tiles resident
+  static constexpr int BLOCKS_PER_SM = (BN <= 64 && MODE == 0) ? 2 : 1;
+  static constexpr int SMEM_BUDGET = (BLOCKS_PER_SM == 2 ? 104 : 200) * 1024;
+  static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int TMEM_COLS_RAW = BN * A_TILES;
+  static constexpr int TMEM_COLS = TMEM_COLS_RAW < 32 ? 32 : TMEM_COLS_RAW;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+template <int BN, int MODE>
+__global__ void __launch_bounds__(NUM_THREADS, (Layout<BN, MODE>::BLOCKS_PER_SM))
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+                    void* __restrict__ out, int out_is_f32, int n_tokens, int n_features, int k_blocks,
+                    int k_blocks_per_split, long long ld_out, long long partial_stride, int up_row_offset,
+                    int* __restrict__ error_word) {
+  using L = Layout<BN, MODE>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::STAGES * L::STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + L::STAGES;
+  uint64_t* tmem_full_bar = empty_bar + L::STAGES;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int f0 = blockIdx.x * BM;
+  const int t0 = blockIdx.y * BN;
+  const int kb_begin = blockIdx.z * k_blocks_per_split;
+  const int kb_end = min(k_blocks, kb_begin + k_blocks_per_split);
+  const int n_kb = max(0, kb_end - kb_begin);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < L::STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(tmem_full_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)),
+                 "r"(L::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int armed = 0;
+      for (int i = 0; i < n_kb; ++i) {
+        const int s = i % L::STAGES;
+        const uint32_t phase = (i / L::STAGES) & 1;
+        if (!mbar_wait(&empty_bar[s], phase ^ 1, abort_flag)) {
+          *abort_flag = 1;
+          atomicCAS(error_word, 0, ERR_TIMEOUT_PRODUCER);
+          break;
+        }
+        uint8_t* stage = smem + s * L::STAGE_BYTES;
+        mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+        const int k0 = (kb_begin + i) * BK;
+        tma_load_2d(stage, &map_w, &full_bar[s], k0, f0);
+        if (MODE == 1) tma_load_2d(stage + L::A_BYTES, &map_w, &full_bar[s], k0, up_row_offset + f0);
+        tma_load_2d(stage + L::A_TILES * L::A_BYTES, &map_a, &full_bar[s], k0, t0);
+        armed = i + 1;
+      }
+      if (*abort_flag) {
+        // copies already issued still land in shared memory: wait for them (bounded) before leaving
+        for (int i = max(0, armed - L::STAGES); i < armed; ++i) {
+          const unsigned long long start = global_timer();
+          while (!mbar_try_wait(&full_bar[i % L::STAGES], (i / L::STAGES) & 1) &&
+                 global_timer() - start < WAIT_LIMIT_NS / 10) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc_bf16(BM, BN);
+      bool ok = true;
+      for (int i = 0; i < n_kb && ok; ++i) {
+        const int s = i % L::STAGES;
+        const uint32_t phase = (i / L::STAGES) & 1;
+        if (!mbar_wait(&full_bar[s], phase, abort_flag)) {
+          *abort_flag = 1;
+          atomicCAS(error_word, 0, ERR_TIMEOUT_MMA);
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = smem_u32(smem + s * L::STAGE_BYTES);
+        const uint32_t b_addr = a_addr + L::A_TILES * L::A_BYTES;
+        const uint64_t desc_a = smem_desc_sw128(a_addr);
+        const uint64_t desc_b = smem_desc_sw128(b_addr);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+          const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);
+          umma_bf16(tmem_base, desc_a + koff, desc_b + koff, idesc, acc);
+          if (MODE == 1) {
+            const uint64_t desc_up = smem_desc_sw128(a_addr + L::A_BYTES);
+            umma_bf16(tmem_base + BN, desc_up + koff, desc_b + koff, idesc, acc);
+          }
+        }
+        umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+      }
+      umma_commit(tmem_full_bar);    // accumulator complete (or, after giving up, releases the epilogue)
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5)
+    const int quad = warp & 3;  // tensor-memory lanes 32 * quad .. + 31 belong to this warp
+    const int f = f0 + quad * 32 + lane;
+    bool ok = mbar_wait(tmem_full_bar, 0, abort_flag);
+    if (!ok) {
+      *abort_flag = 1;
+      atomicCAS(error_word, 0, ERR_TIMEOUT_EPILOGUE);
+    }
+    ok = ok && !*abort_flag;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+      float* out_f32 = reinterpret_cast<float*>(out) + (long long)blockIdx.z * partial_stride;
+      __nv_bfloat16* out_bf16 = reinterpret_cast<__nv_bfloat16*>(out) + (long long)blockIdx.z * partial_stride;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        if (t0 + c0 >= n_tokens) break;  // uniform across the warp
+        uint32_t g[16], u[16];
+        if (n_kb > 0) {
+          tmem_load16(lane_base + c0, g);
+          if (MODE == 1) tmem_load16(lane_base + BN + c0, u);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) g[j] = u[j] = 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int t = t0 + c0 + j;
+          if (t < n_tokens && f < n_features) {
+            float v = __uint_as_float(g[j]);
+            if (MODE == 1) v = v / (1.0f + expf(-v)) * __uint_as_float(u[j]);
+            if (out_is_f32) out_f32[(long long)t * ld_out + f] = v;
+            else out_bf16[(long long)t * ld_out + f] = __float2bfloat16_rn(v);
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::TMEM_COLS)
+                 : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+template <int BN, int MODE>
+int launch(const CUtensorMap* map_w, const CUtensorMap* map_a, void* out, int out_is_f32, int n_tokens,
+           int n_features, int K, long long ld_out, long long partial_stride, int splits, int up_row_offset,
+           int* error_word, cudaStream_t stream) {
+  using L = Layout<BN, MODE>;
+  static bool configured = false;
+  auto kern = gemm_tcgen05_kernel<BN, MODE>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES) != cudaSuccess)
+      return launch_status();
+    configured = true;
+  }
+  const int k_blocks = (K + BK - 1) / BK;
+  const int per_split = (k_blocks + splits - 1) / splits;
+  dim3 grid((n_features + BM - 1) / BM, (n_tokens + BN - 1) / BN, splits);
+  kern<<<grid, NUM_THREADS, L::SMEM_BYTES, stream>>>(*map_w, *map_a, out, out_is_f32, n_tokens, n_features,
+                                                      k_blocks, per_split, ld_out, partial_stride,
+                                                      up_row_offset, error_word);
+  return launch_status();
+}
+
+}  // namespace
+
+// Writes a 128-byte CUtensorMap for a row-major bfloat16 matrix [rows, cols] (row stride in
+// elements) with a box of box_rows x 64 columns and the 128-byte swizzle.  Out-of-range parts of
+// a box read as zero.  The base must be 16-byte aligned and the row stride a multiple of 8.
+extern "C" int llm_gemm_tensor_map(void* map_out, const void* base, long long rows, long long cols,
+                                   long long row_stride, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return 1000 + (int)cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (row_stride % 8) || rows <= 0 || cols <= 0) return ERR_BAD_ALIGN;
+  if (box_rows <= 0 || box_rows > 256) return ERR_BAD_SIZE;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)row_stride * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(reinterpret_cast<CUtensorMap*>(map_out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 2000 + (int)r;
+}
+
+// out[z][t, f] (z < splits) = partial sums of act[t, :] . w[f, :]; mode 1: silu(gate) * up with
+// w = [gate; up], the up rows starting at `up_row_offset` (splits must be 1 then).
+// `bn` is the token tile (16, 32, 64, 128, 256); map_a's box must have bn rows, map_w's 128.
+extern "C" int llm_gemm_bf16(const void* map_w, const void* map_a, void* out, int out_dtype, int n_tokens,
+                             int n_features, int K, long long ld_out, long long partial_stride, int splits,
+                             int bn, int mode, int up_row_offset, int* error_word, cudaStream_t stream) {
+  if (n_tokens <= 0 || n_features <= 0) return 0;
+  if (K <= 0 || splits <= 0 || (mode == 1 && splits != 1)) return ERR_BAD_SIZE;
+  if (splits > 1 && out_dtype != DT_F32) return ERR_BAD_DTYPE;
+  if (out_dtype != DT_F32 && out_dtype != DT_BF16) return ERR_BAD_DTYPE;
+  CUtensorMap mw_copy, ma_copy;  // the caller's buffers need not be 64-byte aligned
+  memcpy(&mw_copy, map_w, sizeof(CUtensorMap));
+  memcpy(&ma_copy, map_a, sizeof(CUtensorMap));
+  const CUtensorMap* mw = &mw_copy;
+  const CUtensorMap* ma = &ma_copy;
+  const int f32 = out_dtype == DT_F32;
+#define GEMM_CASE(BN_)                                                                                   \
+  case BN_:                                                                                              \
+    return mode == 1 ? launch<BN_, 1>(mw, ma, out, f32, n_tokens, n_features, K, ld_out, partial_stride, \
+                                      splits, up_row_offset, error_word, stream)                         \
+                     : launch<BN_, 0>(mw, ma, out, f32, n_tokens, n_features, K, ld_out, partial_stride, \
+                                      splits, up_row_offset, error_word, stream)
+  switch (bn) {
+    GEMM_CASE(16);
+    GEMM_CASE(32);
+    GEMM_CASE(64);
+    GEMM_CASE(128);
+    GEMM_CASE(256);
+    default:
+      return ERR_BAD_SIZE;
+  }
+#undef GEMM_CASE
+}

@@ -42,11 +42,12 @@ class Workspace:
         self.device, self.max_rows = device, max_rows
         self._buffers: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
 
-    def get(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
-        """A [rows, width] (or [n, rows, width]) view; the rows axis is sized for the largest step."""
+    def get(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype, max_rows: Optional[int] = None) -> torch.Tensor:
+        """A [rows, width] (or [n, rows, width]) view; the rows axis is sized for the largest step
+        (or for `max_rows` when the caller only uses the buffer for small steps)."""
         rows_axis = len(shape) - 2
         full = list(shape)
-        full[rows_axis] = max(self.max_rows, shape[rows_axis])
+        full[rows_axis] = max(min(self.max_rows, max_rows) if max_rows else self.max_rows, shape[rows_axis])
         need = int(np.prod(full))
         key = (name, dtype)
         buf = self._buffers.get(key)

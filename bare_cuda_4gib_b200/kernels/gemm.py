@@ -1,5 +1,150 @@
-"""Launcher of the tensor-core matrix product (filled in with the tcgen05 kernel)."""
+"""Launcher of the tcgen05 bfloat16 matrix product (csrc/gemm_tcgen05.cu): tensor maps, choice of
+the token tile and of the K split, and the device error word that bounded waits report to."""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_longlong, c_void_p
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from ..errors import KernelLaunchError
+from . import build
+from .lib import DT_BF16, DT_F32, Partials, _check
+
+BM, BK = 128, 64
+TARGET_BLOCKS = 148 * 2
+SPLIT_MAX_ROWS = 256          # steps with more rows never split K
+_lib = None
+_error_word: Optional[torch.Tensor] = None
 
 
-def plan_for(weight):
-    return None
+def lib():
+    global _lib
+    if _lib is None:
+        l = build.load_library("gemm_tcgen05.cu")
+        P, I, L = c_void_p, c_int, c_longlong
+        l.llm_gemm_tensor_map.argtypes = [P, P, L, L, L, I]
+        l.llm_gemm_tensor_map.restype = c_int
+        l.llm_gemm_bf16.argtypes = [P, P, P, I, I, I, I, L, L, I, I, I, I, P, P]
+        l.llm_gemm_bf16.restype = c_int
+        _lib = l
+    return _lib
+
+
+def error_word(device) -> torch.Tensor:
+    global _error_word
+    if _error_word is None:
+        _error_word = torch.zeros(1, dtype=torch.int32, device=device)
+    return _error_word
+
+
+def check_errors() -> None:
+    """Reads the device error word (synchronises); raises if a kernel gave up on a wait."""
+    if _error_word is not None:
+        code = int(_error_word.item())
+        if code:
+            _error_word.zero_()
+            role = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue"}.get(code, f"code {code}")
+            raise KernelLaunchError(f"gemm_tcgen05: a bounded wait ran out in the {role}; the result is invalid")
+
+
+def supports(weight: torch.Tensor) -> bool:
+    n, k = weight.shape
+    return (weight.dtype == torch.bfloat16 and weight.is_cuda and weight.is_contiguous()
+            and k % 8 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def tensor_map(base_ptr: int, rows: int, cols: int, row_stride: int, box_rows: int) -> ctypes.Array:
+    buf = (ctypes.c_ubyte * 128)()
+    _check(lib().llm_gemm_tensor_map(ctypes.addressof(buf), base_ptr, rows, cols, row_stride, box_rows),
+           "gemm tensor map")
+    return buf
+
+
+class GemmPlan:
+    """A weight matrix ready for the kernel: its tensor map and the maps of the activation buffers
+    it has been multiplied with."""
+
+    def __init__(self, weight: torch.Tensor):
+        self.weight = weight
+        self.n, self.k = weight.shape
+        self.map_w = tensor_map(weight.data_ptr(), self.n, self.k, self.k, BM)
+        self.act_maps: Dict[Tuple[int, int, int], ctypes.Array] = {}
+
+    def act_map(self, a: torch.Tensor, bn: int) -> ctypes.Array:
+        key = (a.data_ptr(), bn, a.stride(0))
+        m = self.act_maps.get(key)
+        if m is None:
+            esize = a.element_size()
+            storage_left = a.untyped_storage().nbytes() - a.storage_offset() * esize
+            capacity = max(a.shape[0], storage_left // (a.stride(0) * esize))
+            m = tensor_map(a.data_ptr(), capacity, self.k, a.stride(0), bn)
+            self.act_maps[key] = m
+        return m
+
+
+def plan_for(weight: torch.Tensor) -> Optional[GemmPlan]:
+    if not supports(weight):
+        return None
+    return GemmPlan(weight)
+
+
+def token_tile(rows: int) -> int:
+    for bn in (16, 32, 64, 128):
+        if rows <= bn:
+            return bn
+    return 256
+
+
+def choose_splits(rows: int, n: int, k: int, bn: int) -> int:
+    """How many thread blocks share the K range of one output tile: enough to put about two
+    blocks on every SM, at least four 64-wide K blocks each, and partial results (written and
+    read back in float32) of at most a quarter of the weight bytes."""
+    if rows > SPLIT_MAX_ROWS:
+        return 1
+    tiles = -(-n // BM) * -(-rows // bn)
+    k_blocks = -(-k // BK)
+    splits = min(k_blocks // 4, TARGET_BLOCKS // tiles, max(1, k // (16 * rows)))
+    splits = max(1, splits)
+    per = -(-k_blocks // splits)
+    return -(-k_blocks // per)
+
+
+def run(ctx, plan: GemmPlan, a: torch.Tensor, rows: int, out_dtype: torch.dtype, buffer: str,
+        allow_partials: bool, swiglu: bool) -> Partials:
+    if a.dtype != torch.bfloat16 or a.stride(-1) != 1 or a.shape[-1] != plan.k or a.data_ptr() % 16 or a.stride(0) % 8:
+        raise KernelLaunchError(f"gemm_tcgen05: activations {tuple(a.shape)} {a.dtype} do not fit weight "
+                                f"[{plan.n}, {plan.k}]")
+    bn = token_tile(rows)
+    err = error_word(a.device)
+    l = lib()
+    if swiglu:
+        inter = plan.n // 2
+        tiles = -(-inter // BM) * -(-rows // bn)
+        if tiles * 2 >= 148 or rows > SPLIT_MAX_ROWS:
+            out = ctx.ws.get(buffer, (rows, inter), out_dtype)
+            _check(l.llm_gemm_bf16(ctypes.addressof(plan.map_w), ctypes.addressof(plan.act_map(a, bn)),
+                                   out.data_ptr(), DT_BF16 if out_dtype == torch.bfloat16 else DT_F32, rows,
+                                   inter, plan.k, out.stride(0), 0, 1, bn, 1, inter, err.data_ptr(), ctx.stream),
+                   "gemm_tcgen05 (swiglu)")
+            return Partials(out)
+        # few tiles: stream [gate; up] as one product split over K, then reduce inside SwiGLU
+        from . import lib as K
+        full = run(ctx, plan, a, rows, torch.float32, buffer + ".gate_up", True, False)
+        out = ctx.ws.get(buffer, (rows, inter), out_dtype)
+        K.swiglu(full, out, rows, ctx.stream)
+        return Partials(out)
+    splits = choose_splits(rows, plan.n, plan.k, bn) if (allow_partials and out_dtype == torch.float32) else 1
+    if splits > 1:
+        out = ctx.ws.get(buffer + ".partials", (splits, rows, plan.n), torch.float32, max_rows=SPLIT_MAX_ROWS)
+        stride = out.stride(0)
+    else:
+        out = ctx.ws.get(buffer, (rows, plan.n), out_dtype)
+        stride = 0
+    _check(l.llm_gemm_bf16(ctypes.addressof(plan.map_w), ctypes.addressof(plan.act_map(a, bn)), out.data_ptr(),
+                           DT_BF16 if out_dtype == torch.bfloat16 else DT_F32, rows, plan.n, plan.k,
+                           out.stride(-2), stride, splits, bn, 0, 0, err.data_ptr(), ctx.stream),
+           "gemm_tcgen05")
+    return Partials(out, splits)

@@ -1,0 +1,256 @@
+"""Each CUDA kernel alone against a plain PyTorch float32 statement of the same operation, at
+sizes other than the engine's: widths that are no power of two, ragged tiles, one row."""
+
+import math
+import random
+import types
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _ctx(max_rows=4096):
+    from bare_cuda_4gib_b200.engine.step import Workspace
+    return types.SimpleNamespace(ws=Workspace(torch.device(DEV), max_rows),
+                                 stream=torch.cuda.current_stream().cuda_stream)
+
+
+def _close(got, want, rtol, atol):
+    got, want = got.double().cpu(), want.double().cpu()
+    bad = (got - want).abs() > atol + rtol * want.abs()
+    assert not bad.any(), f"{int(bad.sum())} of {bad.numel()} differ; worst {float((got - want).abs().max()):.3e}"
+
+
+# ------------------------------------------------------------------------------ plain kernels
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_gather(dtype):
+    from bare_cuda_4gib_b200.kernels import lib as K
+    table = torch.randn(301, 70, device=DEV).to(dtype)
+    ids = torch.tensor([0, 300, 5, 5, 17], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 70, device=DEV)
+    K.embed_gather(table, ids, out, 5)
+    assert torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("hidden", [300, 64, 2050])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm(hidden, out_dtype):
+    from bare_cuda_4gib_b200.kernels import lib as K
+    rows, eps = 7, 1e-6
+    x = torch.randn(rows, hidden, device=DEV)
+    delta = torch.randn(3, rows, hidden, device=DEV)
+    w = (1 + 0.1 * torch.randn(hidden, device=DEV))
+    res = x.clone()
+    out = torch.empty(rows, hidden, device=DEV, dtype=out_dtype)
+    K.add_rmsnorm(res, K.Partials(delta, 3), w, out, eps, rows)
+    want_res = x.double() + delta.double().sum(0)
+    want = want_res * torch.rsqrt(want_res.pow(2).mean(-1, keepdim=True) + eps) * w.double()
+    _close(res, want_res, 1e-6, 1e-6)
+    if out_dtype == torch.float32:
+        _close(out, want, 1e-5, 1e-5)
+    else:
+        _close(out, want, 2 ** -8, 1e-5)
+    # gathered rows, no delta
+    index = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(3, hidden, device=DEV)
+    K.add_rmsnorm(res, None, w, out2, eps, 3, index)
+    _close(out2, want[index.long()], 1e-5, 1e-5)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 70, 300), (17, 130, 64), (150, 64, 176), (5, 258, 96)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_matmul_plain(m, n, k, dtype):
+    from bare_cuda_4gib_b200.kernels import lib as K
+    a = torch.randn(m, k, device=DEV).to(dtype)
+    w = torch.randn(n, k, device=DEV).to(dtype)
+    out = torch.empty(m, n, device=DEV)
+    K.matmul_plain(a, w, out, m)
+    _close(out, a.double() @ w.double().t(), 1e-5, 1e-4)
+
+
+def _paged_cache(kv_heads, head_dim, page_tokens, n_pages, dtype):
+    from bare_cuda_4gib_b200.kernels.lib import CacheView
+    elems = 2 * kv_heads * page_tokens * head_dim
+    storage = torch.zeros(n_pages, elems, device=DEV, dtype=dtype)
+    table = torch.full((4, 16), -1, dtype=torch.int32, device=DEV)
+    esize = storage.element_size()
+    view = CacheView(storage.data_ptr(), storage.data_ptr() + (elems // 2) * esize, table, elems, 16,
+                     page_tokens, kv_heads, head_dim, dtype)
+    return storage, table, view
+
+
+def _rope_ref(x, pos, inv_freq):
+    half = x.shape[-1] // 2
+    ang = (pos.float().unsqueeze(-1) * inv_freq).double()
+    c, s = torch.cos(ang).unsqueeze(1), torch.sin(ang).unsqueeze(1)
+    lo, hi = x[..., :half].double(), x[..., half:].double()
+    return torch.cat([lo * c - hi * s, hi * c + lo * s], -1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rope_cache_write_and_attention_plain(dtype):
+    """Rotation + cache write, then attention over scrambled pages with a window, against dense math."""
+    from bare_cuda_4gib_b200.kernels import lib as K
+    heads, kv_heads, d, page, window = 6, 2, 48, 8, 13
+    lens = [21, 5]      # two sequences, fed whole
+    storage, table, view = _paged_cache(kv_heads, d, page, 12, dtype)
+    pages = list(range(12))
+    random.Random(3).shuffle(pages)
+    table[0, :3] = torch.tensor(pages[:3], dtype=torch.int32)
+    table[1, :1] = torch.tensor(pages[3:4], dtype=torch.int32)
+    n = sum(lens)
+    positions = torch.tensor(list(range(lens[0])) + list(range(lens[1])), dtype=torch.int32, device=DEV)
+    row_seq = torch.tensor([0] * lens[0] + [1] * lens[1], dtype=torch.int32, device=DEV)
+    width = (heads + 2 * kv_heads) * d
+    qkv = torch.randn(2, n, width, device=DEV).to(dtype)          # two partial results
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(d // 2, dtype=torch.float32) * 2.0 / d))).to(DEV)
+    q = torch.empty(n, heads * d, device=DEV, dtype=dtype)
+    K.rope_cache_write(K.Partials(qkv, 2), q, view, positions, row_seq, inv_freq, heads, True, n)
+    full = qkv.float().sum(0) if dtype == torch.float32 else (qkv[0].float() + qkv[1].float())
+    qr = _rope_ref(full[:, : heads * d].view(n, heads, d), positions, inv_freq)
+    kr = _rope_ref(full[:, heads * d: (heads + kv_heads) * d].view(n, kv_heads, d), positions, inv_freq)
+    vr = full[:, (heads + kv_heads) * d:].view(n, kv_heads, d).double()
+    tol = 1e-5 if dtype == torch.float32 else 2 ** -7
+    _close(q.view(n, heads, d), qr, tol, tol)
+    out = torch.empty(n, heads * d, device=DEV, dtype=dtype)
+    scale = 1.0 / math.sqrt(d)
+    K.attention_plain(q, out, view, positions, row_seq, heads, n, scale, window)
+    # dense reference from what the kernels stored (q as stored, k/v rounded as the cache holds them)
+    qs = q.view(n, heads, d).double()
+    ks, vs = kr.to(dtype).double(), vr.to(dtype).double()
+    want = torch.zeros(n, heads, d, dtype=torch.float64, device=DEV)
+    start = 0
+    for L in lens:
+        for i in range(L):
+            lo = max(0, i - window + 1)
+            for h in range(heads):
+                kvh = h // (heads // kv_heads)
+                s = (ks[start + lo: start + i + 1, kvh] @ qs[start + i, h]) * scale
+                p = torch.softmax(s, 0)
+                want[start + i, h] = p @ vs[start + lo: start + i + 1, kvh]
+        start += L
+    _close(out.view(n, heads, d), want, 1e-5 if dtype == torch.float32 else 2 ** -7, 1e-5 if dtype == torch.float32 else 2e-3)
+
+
+def test_attention_plain_far_key_stands_out():
+    """One far key among hundreds gets a large score: the output must be its value row."""
+    from bare_cuda_4gib_b200.kernels import lib as K
+    heads, kv_heads, d, page = 2, 1, 32, 16
+    L = 300
+    storage, table, view = _paged_cache(kv_heads, d, page, 19, torch.float32)
+    from bare_cuda_4gib_b200.kernels.lib import CacheView
+    table = torch.full((1, 32), -1, dtype=torch.int32, device=DEV)
+    perm = list(range(19))
+    random.Random(1).shuffle(perm)
+    table[0, :19] = torch.tensor(perm, dtype=torch.int32)
+    view.block_table, view.table_stride = table, 32
+    k = 0.01 * torch.randn(L, d, device=DEV)
+    v = torch.randn(L, d, device=DEV)
+    far = 37
+    k[far] = 0
+    k[far, 0] = 100.0
+    for pos in range(L):
+        pg = perm[pos // page]
+        storage[pg, (pos % page) * d: (pos % page) * d + d] = k[pos]
+        storage[pg, page * d + (pos % page) * d: page * d + (pos % page) * d + d] = v[pos]
+    q = torch.zeros(1, heads * d, device=DEV)
+    q[0, 0] = 10.0
+    q[0, d] = 10.0
+    out = torch.empty(1, heads * d, device=DEV)
+    positions = torch.tensor([L - 1], dtype=torch.int32, device=DEV)
+    row_seq = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K.attention_plain(q, out, view, positions, row_seq, heads, 1, 1.0 / math.sqrt(d), 0)
+    _close(out.view(heads, d), v[far].expand(heads, d), 1e-5, 1e-5)
+
+
+@pytest.mark.parametrize("in_dtype,out_dtype", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16),
+                                                (torch.bfloat16, torch.bfloat16)])
+def test_swiglu(in_dtype, out_dtype):
+    from bare_cuda_4gib_b200.kernels import lib as K
+    rows, inter = 5, 173
+    x = torch.randn(2, rows, 2 * inter, device=DEV).to(in_dtype)
+    out = torch.empty(rows, inter, device=DEV, dtype=out_dtype)
+    K.swiglu(K.Partials(x, 2), out, rows)
+    s = x[0].float() + x[1].float()
+    g, u = s[:, :inter].double(), s[:, inter:].double()
+    want = g / (1 + torch.exp(-g)) * u
+    _close(out, want, 1e-5 if out_dtype == torch.float32 else 2 ** -8, 1e-6)
+
+
+def test_argmax_rows_ties_and_last():
+    from bare_cuda_4gib_b200.kernels import lib as K
+    logits = torch.randn(4, 1000, device=DEV)
+    logits[1, 10] = logits[1, 700] = 50.0      # tie: the lowest index wins
+    logits[2, 999] = 60.0                      # last slot
+    logits[3] = 0.0                            # all equal
+    out = torch.empty(4, dtype=torch.int32, device=DEV)
+    K.argmax_rows(logits, out, 4)
+    assert out.tolist() == [int(logits[0].argmax()), 10, 999, 0]
+
+
+def test_sample_rows_matches_inverse_cdf_walk():
+    import plain_llama as pl
+    from bare_cuda_4gib_b200.kernels import lib as K
+    vocab, rows = 777, 6
+    logits = 3 * torch.randn(rows, vocab, device=DEV)
+    temps = torch.tensor([0.0, 0.7, 1.0, 1.5, 0.3, 2.0], device=DEV)
+    us = torch.tensor([0.5, 0.01, 0.5, 0.999, 0.25, 0.75], device=DEV)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    K.sample_rows(logits, temps, us, out, rows)
+    got = out.tolist()
+    assert got[0] == int(logits[0].argmax())
+    for r in range(1, rows):
+        w = pl.sampling_weights(logits[r].cpu(), float(temps[r]))
+        want = pl.inverse_cdf_pick(w.tolist(), list(range(vocab)), float(us[r]))
+        # float32 sums on the device may move the boundary by one id with negligible mass
+        cdf = torch.cumsum(w / w.sum(), 0)
+        assert abs(float(cdf[got[r]]) - float(cdf[want])) < 1e-4, (r, got[r], want)
+
+
+# ------------------------------------------------------------------------------ tcgen05 GEMM
+
+GEMM_SHAPES = [(1, 2560, 2048), (7, 96, 96), (16, 300, 176), (17, 128, 64), (33, 1000, 128),
+               (64, 2048, 5632), (100, 512, 256), (200, 640, 320), (257, 384, 192), (700, 256, 512)]
+
+
+@pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_tcgen05(m, n, k, out_dtype):
+    from bare_cuda_4gib_b200.kernels import gemm
+    torch.manual_seed(m * 7 + n)
+    ctx = _ctx()
+    a = ctx.ws.get("a", (m, k), torch.bfloat16)
+    a.copy_(torch.randn(m, k, device=DEV))
+    w = torch.randn(n, k, device=DEV).to(torch.bfloat16)
+    plan = gemm.plan_for(w)
+    assert plan is not None
+    res = gemm.run(ctx, plan, a, m, out_dtype, "out", allow_partials=True, swiglu=False)
+    gemm.check_errors()
+    got = res.tensor.float().sum(0) if res.n > 1 else res.tensor.float()
+    want = a.double() @ w.double().t()
+    if out_dtype == torch.float32:
+        _close(got, want, 1e-5, 1e-4 * math.sqrt(k))
+    else:
+        _close(got, want, 2 ** -8, 1e-4 * math.sqrt(k))
+
+
+@pytest.mark.parametrize("m,inter,k", [(3, 176, 64), (40, 5632, 256), (130, 256, 96), (300, 200, 128), (9, 2816, 512)])
+def test_gemm_tcgen05_swiglu(m, inter, k):
+    from bare_cuda_4gib_b200.kernels import gemm
+    torch.manual_seed(m)
+    ctx = _ctx()
+    a = ctx.ws.get("a", (m, k), torch.bfloat16)
+    a.copy_(torch.randn(m, k, device=DEV) * 0.5)
+    w = (torch.randn(2 * inter, k, device=DEV) * 0.2).to(torch.bfloat16)
+    plan = gemm.plan_for(w)
+    res = gemm.run(ctx, plan, a, m, torch.bfloat16, "act", allow_partials=False, swiglu=True)
+    gemm.check_errors()
+    gu = a.double() @ w.double().t()
+    g, u = gu[:, :inter], gu[:, inter:]
+    want = g / (1 + torch.exp(-g)) * u
+    _close(res.tensor, want, 2 ** -7, 1e-3)
