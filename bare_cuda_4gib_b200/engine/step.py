@@ -86,7 +86,7 @@ class StepContext:
 
 class StepRunner:
     def __init__(self, model, cache: CacheManager, *, max_step_tokens: int, max_batch_seqs: Optional[int] = None,
-                 use_fast_gemm: bool = True, use_fast_attention: bool = True):
+                 use_fast_gemm: bool = True, use_fast_attention: bool = True, use_cuda_graphs: bool = True):
         if model.device is None or model.device.type != "cuda":
             raise EngineError("the step function needs a model bound on a CUDA device; there is no CPU path")
         self.model, self.cache = model, cache

@@ -1,0 +1,119 @@
+"""Generation through the entry points against the plain implementation's cacheless greedy decode."""
+
+import random
+
+import pytest
+import torch
+
+import helpers as H
+import plain_llama as pl
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_matches_plain(name, dtype):
+    from bare_cuda_4gib_b200.engine.engine import LLMEngine
+
+    folder, page = H.model_folder(name), H.TINY[name][1]
+    cfg = H.TINY[name][0]
+    rng = random.Random(21)
+    prompt = H.random_ids(rng, 19, cfg["vocab_size"])
+    steps = 40
+    engine = LLMEngine(folder, max_tokens=len(prompt) + steps, max_seqs=2, dtype=dtype, page_tokens=page)
+    got = engine.generate(prompt, steps)
+    model = H.plain_model(folder)
+    if dtype == "float32":
+        assert got == pl.greedy_decode(model, prompt, steps)
+    else:
+        # bfloat16 may pick the other of two near-equal logits: accept a different id only where the
+        # plain logits of the two ids differ by less than the bfloat16 tolerance, then follow the engine
+        ids = list(prompt)
+        for t in got:
+            logits = pl.forward_logits(model, ids)[-1]
+            best = int(torch.argmax(logits))
+            if t != best:
+                gap = float(logits[best] - logits[t]) / float(logits.abs().max())
+                assert gap <= H.TOLERANCE["bfloat16"], f"token {t} instead of {best}: gap {gap:.3e}"
+            ids.append(t)
+
+
+def test_batch_equals_alone_with_chunked_prompts():
+    """Several requests through the scheduler with a small token budget give the ids each gives alone."""
+    from bare_cuda_4gib_b200.engine.engine import LLMEngine
+
+    folder, page = H.model_folder("B"), 32
+    rng = random.Random(5)
+    prompts = [H.random_ids(rng, n, 320) for n in (3, 45, 100, 17, 64)]
+    alone = LLMEngine(folder, max_tokens=140, max_seqs=1, dtype="float32", page_tokens=page)
+    want = [alone.generate(p, 24) for p in prompts]
+    batch = LLMEngine(folder, max_tokens=140, max_seqs=3, dtype="float32", page_tokens=page, max_step_tokens=24)
+    got = batch.generate_batch(prompts, 24)
+    assert got == want
+    assert batch.scheduler.stats().prefill_chunks > len(prompts)
+    assert batch.cache.pages_in_use() == [0]
+
+
+def test_on_demand_preemption_recomputes():
+    """With too few pages for everyone, the on-demand policy preempts and still gives the same ids."""
+    from bare_cuda_4gib_b200.engine.engine import LLMEngine
+
+    folder, page = H.model_folder("A"), 16
+    rng = random.Random(8)
+    prompts = [H.random_ids(rng, n, 256) for n in (30, 28, 33, 25)]
+    alone = LLMEngine(folder, max_tokens=96, max_seqs=1, dtype="float32", page_tokens=page)
+    want = [alone.generate(p, 40) for p in prompts]
+    tight = LLMEngine(folder, max_tokens=96, max_seqs=4, kv_pages=11, dtype="float32", page_tokens=page,
+                      policy="on_demand")
+    got = tight.generate_batch(prompts, 40)
+    assert got == want
+    assert tight.scheduler.stats().preemptions > 0
+    assert tight.cache.pages_in_use() == [0]
+
+
+def test_seeded_sampling_same_alone_and_batched():
+    from bare_cuda_4gib_b200.engine.engine import LLMEngine
+    from bare_cuda_4gib_b200.sampling.params import SamplingParams
+
+    folder, page = H.model_folder("A"), 16
+    rng = random.Random(9)
+    prompts = [H.random_ids(rng, n, 256) for n in (5, 12, 9)]
+    params = SamplingParams(temperature=0.9, seed=1234)
+    alone = LLMEngine(folder, max_tokens=64, max_seqs=1, dtype="float32", page_tokens=page)
+    want = [alone.generate(p, 20, sampling=params) for p in prompts]
+    batch = LLMEngine(folder, max_tokens=64, max_seqs=3, dtype="float32", page_tokens=page)
+    assert batch.generate_batch(prompts, 20, sampling=params) == want
+    assert want[0] != alone.generate(prompts[0], 20)          # it does sample
+    topk = SamplingParams(temperature=0.8, top_k=5, top_p=0.9, seed=7)
+    assert batch.generate_batch(prompts, 10, sampling=topk) == [alone.generate(p, 10, sampling=topk) for p in prompts]
+
+
+def test_async_engine_surface():
+    from bare_cuda_4gib_b200.engine.engine import Engine
+
+    folder = H.model_folder("A")
+    engine = Engine(str(folder), max_tokens=64, max_seqs=2, max_waiting=1, dtype="float32", page_tokens=16)
+    try:
+        assert engine.vocab_size == 256 and engine.max_seqs == 2 and engine.healthy
+        assert engine.submit(1, [], 4)[0] == "invalid"
+        assert engine.submit(1, [1, 2, 3], 4) == ("ok", "")
+        assert engine.submit(1, [1, 2, 3], 4)[0] in ("invalid", "ok")   # duplicate while live is invalid
+        assert engine.submit(2, [4, 5], 3, temperature=-1.0)[0] == "invalid"
+        events = []
+        for _ in range(200):
+            events += engine.poll(50)
+            if any(e[0] == 1 and e[3] for e in events):
+                break
+        mine = [e for e in events if e[0] == 1]
+        assert [e[2] for e in mine if e[1] >= 0][:4] == [0, 1, 2, 3] and mine[-1][3] == "length"
+        assert engine.stats()["decode_tokens"] >= 3
+        engine._fail_for_test("injected")
+        for _ in range(100):
+            if not engine.healthy:
+                break
+            engine.poll(20)
+        assert not engine.healthy and "injected" in engine.failure
+        assert engine.submit(5, [1], 1)[0] == "unavailable"
+    finally:
+        engine.stop()
