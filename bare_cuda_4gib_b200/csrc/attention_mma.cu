@@ -1,0 +1,427 @@
+// Paged flash attention for bfloat16 on the tensor cores (mma.sync m16n8k16, float32 softmax and
+// accumulators), one kernel for prefill portions, decode rows and mixed batches.  It replaces
+// the three-kernel attention of cuongvng/bare-cuda-4gib (engine/kernels/attention_qk.cu:49-68,
+// softmax.cu:28-42, attention_av.cu:24-44), which materialises [heads, T, keys] scores.
+//
+// Rows.  The query heads that share one key/value head are packed into the rows of a tile:
+// packed row R of a request = (token R / group, head R % group).  A thread block owns one tile
+// of BM packed rows of one request and one key/value head, so a key block loaded once serves
+// every head of the group.  Keys are visited in blocks of 64 positions, copied from the
+// request's pages into padded shared memory with cp.async (two stages).
+//
+// Two shapes of the same kernel:
+//   WARPS_M = 4, WARPS_N = 1: 64 rows, each warp 16 rows and all 64 keys of a block (prefill);
+//   WARPS_M = 1, WARPS_N = 4: 16 rows, each warp 16 of the 64 keys of a block (decode); the
+//   warps' partial softmax states are merged through shared memory.
+// gridDim.z > 1 splits a tile's key blocks over several thread blocks; each writes a
+// normalised partial output and its log-sum-exp to scratch memory and `attention_combine`
+// merges them.  Softmax runs in base 2: scores are multiplied by scale * log2(e).
+//
+// HEAD_DIM is a compile-time constant (-DHEAD_DIM=64): a multiple of 16 up to 128.
+
+#include "common.cuh"
+
+#ifndef HEAD_DIM
+#define HEAD_DIM 64
+#endif
+
+namespace {
+
+constexpr int D = HEAD_DIM;
+static_assert(D % 16 == 0 && D >= 16 && D <= 128, "HEAD_DIM must be a multiple of 16 up to 128");
+constexpr int BN = 64;        // keys per block
+constexpr int LDS = D + 8;    // padded row length in shared memory (conflict-free ldmatrix)
+constexpr int CHUNKS = D / 8; // 16-byte chunks per row
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(dst)), "l"(src), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_addr(p)));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_addr(p)));
+}
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct AttnArgs {
+  const __nv_bfloat16* q;      // [tokens, q_heads, D]
+  __nv_bfloat16* out;          // [tokens, q_heads * D]
+  PagedCache cache;
+  const int32_t* seq_q_start;  // per batch sequence: first row of its tokens in this step
+  const int32_t* seq_q_len;    // tokens it brings
+  const int32_t* seq_kv_len;   // its length after this step
+  const int32_t* tile_seq;     // per tile: batch sequence (-1: nothing to do)
+  const int32_t* tile_index;   // per tile: which BM-row tile of the sequence's packed rows
+  float* part_o;               // scratch for split keys: [tile][kv head][split][BM][D], normalised
+  float* part_lse;             // [tile][kv head][split][BM], base-2 log-sum-exp (-inf: no keys)
+  int q_heads;
+  float scale_log2;
+  int window;                  // <= 0: every key
+};
+
+template <int WARPS_M, int WARPS_N>
+__global__ void __launch_bounds__(WARPS_M* WARPS_N * 32)
+attention_mma_kernel(AttnArgs a) {
+  constexpr int NW = WARPS_M * WARPS_N;
+  constexpr int NT_THREADS = NW * 32;
+  constexpr int BM = 16 * WARPS_M;
+  constexpr int KEYS_W = BN / WARPS_N;  // keys of a block that one warp handles
+  constexpr int NT = KEYS_W / 8;        // score n-tiles per warp
+  static_assert(NT % 2 == 0, "a warp handles keys in pairs of n-tiles");
+
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [BM][LDS]
+  __nv_bfloat16* Ks = Qs + BM * LDS;                                   // [2][BN][LDS]
+  __nv_bfloat16* Vs = Ks + 2 * BN * LDS;                               // [2][BN][LDS]
+
+  const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, n_splits = gridDim.z;
+  const int seq = a.tile_seq[tile];
+  if (seq < 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wm = warp / WARPS_N, wn = warp % WARPS_N;
+  const int group = a.q_heads / a.cache.kv_heads;
+  const int q_start = a.seq_q_start[seq], q_len = a.seq_q_len[seq], kv_len = a.seq_kv_len[seq];
+  const int row0 = a.tile_index[tile] * BM;  // first packed row of the tile
+  const int n_rows = q_len * group;
+  const int pos0 = kv_len - q_len;           // position of the request's first token in this step
+
+  // ---- key blocks this thread block visits
+  const int last_token = min(q_len - 1, (row0 + BM - 1) / group);
+  const int first_token = row0 / group;
+  const int hi_key = pos0 + last_token;  // newest visible key of any row
+  int lo_key = 0;
+  if (a.window > 0) lo_key = max(0, pos0 + first_token - a.window + 1);
+  const int kb_lo = lo_key / BN, kb_hi = hi_key / BN;  // inclusive
+  const int n_kb_total = kb_hi - kb_lo + 1;
+  const int per_split = (n_kb_total + n_splits - 1) / n_splits;
+  const int kb_begin = kb_lo + split * per_split;
+  const int kb_end = min(kb_hi + 1, kb_begin + per_split);  // exclusive
+
+  // ---- stage Q (rows beyond the request's packed rows are zero)
+  for (int i = threadIdx.x; i < BM * CHUNKS; i += NT_THREADS) {
+    const int r = i / CHUNKS, c = i % CHUNKS;
+    const int R = row0 + r;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (R < n_rows) {
+      const int token = R / group, head = kvh * group + R % group;
+      v = *reinterpret_cast<const uint4*>(a.q + ((long long)(q_start + token) * a.q_heads + head) * D + c * 8);
+    }
+    *reinterpret_cast<uint4*>(Qs + r * LDS + c * 8) = v;
+  }
+
+  const __nv_bfloat16* kc = reinterpret_cast<const __nv_bfloat16*>(a.cache.k);
+  const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(a.cache.v);
+  auto load_block = [&](int kb, int stage) {
+    __nv_bfloat16* ks = Ks + stage * BN * LDS;
+    __nv_bfloat16* vs = Vs + stage * BN * LDS;
+    for (int i = threadIdx.x; i < BN * CHUNKS; i += NT_THREADS) {
+      const int r = i / CHUNKS, c = i % CHUNKS;
+      const int key = kb * BN + r;
+      long long off = -1;
+      if (key < kv_len) off = cache_offset(a.cache, seq, key, kvh);
+      const bool valid = off >= 0;
+      const long long src = valid ? off + c * 8 : 0;
+      cp_async16(ks + r * LDS + c * 8, kc + src, valid);
+      cp_async16(vs + r * LDS + c * 8, vc + src, valid);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  if (kb_begin < kb_end) load_block(kb_begin, 0);
+  __syncthreads();  // Q staged
+
+  // ---- Q fragments stay in registers
+  uint32_t qf[D / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks)
+    ldmatrix_x4(qf[ks], Qs + (wm * 16 + (lane & 15)) * LDS + ks * 16 + (lane >> 4) * 8);
+
+  // this thread's two rows
+  int row_pos[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int R = row0 + wm * 16 + (lane >> 2) + h * 8;
+    row_pos[h] = R < n_rows ? pos0 + R / group : -1;  // -1: no key is visible
+  }
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+
+  for (int kb = kb_begin; kb < kb_end; ++kb) {
+    const int stage = (kb - kb_begin) & 1;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();  // block kb has landed; everyone is done with the other stage
+    if (kb + 1 < kb_end) load_block(kb + 1, stage ^ 1);
+    const __nv_bfloat16* ks_ = Ks + stage * BN * LDS;
+    const __nv_bfloat16* vs_ = Vs + stage * BN * LDS;
+    const int key0 = kb * BN + wn * KEYS_W;  // first key this warp scores
+
+    float s[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+      for (int nt = 0; nt < NT; nt += 2) {
+        uint32_t kf[4];
+        const int mid = lane >> 3;
+        ldmatrix_x4(kf, ks_ + (wn * KEYS_W + (nt + (mid >> 1)) * 8 + (lane & 7)) * LDS + ks * 16 + (mid & 1) * 8);
+        mma_bf16(s[nt], qf[ks], kf[0], kf[1]);
+        mma_bf16(s[nt + 1], qf[ks], kf[2], kf[3]);
+      }
+    }
+
+    // scale, mask, running maximum
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h = e >> 1;
+        const int key = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+        const bool visible = key <= row_pos[h] && (a.window <= 0 || key > row_pos[h] - a.window);
+        const float v = visible ? s[nt][e] * a.scale_log2 : -INFINITY;
+        s[nt][e] = v;
+        mx[h] = fmaxf(mx[h], v);
+      }
+    }
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      const float m_new = fmaxf(m[h], mx[h]);
+      m_use[h] = m_new == -INFINITY ? 0.0f : m_new;
+      corr[h] = exp2f(m[h] - m_use[h]);  // m = -inf gives 0
+      m[h] = m_new;
+      l[h] *= corr[h];
+    }
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      o[i][0] *= corr[0];
+      o[i][1] *= corr[0];
+      o[i][2] *= corr[1];
+      o[i][3] *= corr[1];
+    }
+    // probabilities, as A fragments for P V
+    uint32_t pf[NT / 2][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const float p0 = exp2f(s[nt][0] - m_use[0]), p1 = exp2f(s[nt][1] - m_use[0]);
+      const float p2 = exp2f(s[nt][2] - m_use[1]), p3 = exp2f(s[nt][3] - m_use[1]);
+      l[0] += p0 + p1;
+      l[1] += p2 + p3;
+      pf[nt / 2][(nt & 1) * 2 + 0] = pack_bf16(p0, p1);
+      pf[nt / 2][(nt & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int kk = 0; kk < KEYS_W / 16; ++kk) {
+#pragma unroll
+      for (int dt = 0; dt < D / 8; dt += 2) {
+        uint32_t vf[4];
+        const int mid = lane >> 3;
+        ldmatrix_x4_trans(vf, vs_ + (wn * KEYS_W + kk * 16 + (mid & 1) * 8 + (lane & 7)) * LDS + (dt + (mid >> 1)) * 8);
+        mma_bf16(o[dt], pf[kk], vf[0], vf[1]);
+        mma_bf16(o[dt + 1], pf[kk], vf[2], vf[3]);
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+  }
+
+  // ---- merge the warps that shared rows, through shared memory (reuses the K/V stages)
+  __syncthreads();
+  float* red_o = reinterpret_cast<float*>(Ks);      // [WARPS_N][BM][D]
+  float* red_m = red_o + WARPS_N * BM * D;          // [WARPS_N][BM]
+  float* red_l = red_m + WARPS_N * BM;              // [WARPS_N][BM]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = wm * 16 + (lane >> 2) + h * 8;
+    if ((lane & 3) == 0) {
+      red_m[wn * BM + r] = m[h];
+      red_l[wn * BM + r] = l[h];
+    }
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      float* dst = red_o + ((long long)(wn * BM + r)) * D + i * 8 + (lane & 3) * 2;
+      dst[0] = o[i][h * 2 + 0];
+      dst[1] = o[i][h * 2 + 1];
+    }
+  }
+  __syncthreads();
+  const long long item = ((long long)tile * gridDim.y + kvh) * n_splits + split;
+  for (int i = threadIdx.x; i < BM * CHUNKS; i += NT_THREADS) {
+    const int r = i / CHUNKS, c = i % CHUNKS;
+    const int R = row0 + r;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS_N; ++w) M = fmaxf(M, red_m[w * BM + r]);
+    float L = 0.0f, acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (M != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < WARPS_N; ++w) {
+        const float f = exp2f(red_m[w * BM + r] - M);
+        L += red_l[w * BM + r] * f;
+        const float* src = red_o + ((long long)(w * BM + r)) * D + c * 8;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += src[e] * f;
+      }
+    }
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    if (n_splits == 1) {
+      if (R < n_rows) {
+        const int token = R / group, head = kvh * group + R % group;
+        uint4 packed;
+        packed.x = pack_bf16(acc[0] * inv, acc[1] * inv);
+        packed.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+        packed.z = pack_bf16(acc[4] * inv, acc[5] * inv);
+        packed.w = pack_bf16(acc[6] * inv, acc[7] * inv);
+        *reinterpret_cast<uint4*>(a.out + ((long long)(q_start + token) * a.q_heads + head) * D + c * 8) = packed;
+      }
+    } else {
+      float* dst = a.part_o + (item * BM + r) * D + c * 8;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dst[e] = acc[e] * inv;
+      if (c == 0) a.part_lse[item * BM + r] = L > 0.0f ? M + log2f(L) : -INFINITY;
+    }
+  }
+}
+
+// Merges the partial outputs of a tile's key splits: out = sum_z w_z o_z / sum_z w_z with
+// w_z = 2^(lse_z - max lse).  One thread block per (tile, kv head).
+template <int BM>
+__global__ void attention_combine_kernel(AttnArgs a, int n_splits) {
+  const int tile = blockIdx.x, kvh = blockIdx.y;
+  const int seq = a.tile_seq[tile];
+  if (seq < 0) return;
+  const int group = a.q_heads / a.cache.kv_heads;
+  const int q_start = a.seq_q_start[seq], n_rows = a.seq_q_len[seq] * group;
+  const int row0 = a.tile_index[tile] * BM;
+  const long long item0 = ((long long)tile * gridDim.y + kvh) * n_splits;
+  for (int i = threadIdx.x; i < BM * CHUNKS; i += blockDim.x) {
+    const int r = i / CHUNKS, c = i % CHUNKS;
+    const int R = row0 + r;
+    if (R >= n_rows) continue;
+    float M = -INFINITY;
+    for (int z = 0; z < n_splits; ++z) M = fmaxf(M, a.part_lse[(item0 + z) * BM + r]);
+    float W = 0.0f, acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (M != -INFINITY) {
+      for (int z = 0; z < n_splits; ++z) {
+        const float w = exp2f(a.part_lse[(item0 + z) * BM + r] - M);
+        if (w == 0.0f) continue;
+        W += w;
+        const float* src = a.part_o + ((item0 + z) * BM + r) * D + c * 8;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += w * src[e];
+      }
+    }
+    const float inv = W > 0.0f ? 1.0f / W : 0.0f;
+    const int token = R / group, head = kvh * group + R % group;
+    uint4 packed;
+    packed.x = pack_bf16(acc[0] * inv, acc[1] * inv);
+    packed.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+    packed.z = pack_bf16(acc[4] * inv, acc[5] * inv);
+    packed.w = pack_bf16(acc[6] * inv, acc[7] * inv);
+    *reinterpret_cast<uint4*>(a.out + ((long long)(q_start + token) * a.q_heads + head) * D + c * 8) = packed;
+  }
+}
+
+template <int WARPS_M, int WARPS_N>
+constexpr size_t smem_bytes() {
+  constexpr int BM = 16 * WARPS_M;
+  constexpr size_t tiles = (size_t)(BM + 4 * BN) * LDS * 2;
+  constexpr size_t merge = (size_t)BM * LDS * 2 + (size_t)WARPS_N * BM * (D + 2) * 4;
+  return tiles > merge ? tiles : merge;
+}
+
+template <int WARPS_M, int WARPS_N>
+int launch(const AttnArgs& a, int n_tiles, int kv_heads, int n_splits, cudaStream_t stream) {
+  auto kern = attention_mma_kernel<WARPS_M, WARPS_N>;
+  constexpr size_t smem = smem_bytes<WARPS_M, WARPS_N>();
+  static bool configured = false;
+  if (!configured) {
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return launch_status();
+    configured = true;
+  }
+  dim3 grid(n_tiles, kv_heads, n_splits);
+  kern<<<grid, WARPS_M * WARPS_N * 32, smem, stream>>>(a);
+  if (n_splits > 1) {
+    dim3 cgrid(n_tiles, kv_heads);
+    attention_combine_kernel<16 * WARPS_M><<<cgrid, 128, 0, stream>>>(a, n_splits);
+  }
+  return launch_status();
+}
+
+}  // namespace
+
+extern "C" int llm_attention_head_dim() { return D; }
+
+// Floats of scratch that `n_tiles` tiles of `rows_per_tile` rows need when split `n_splits` ways:
+// partial outputs, then their log-sum-exps.
+extern "C" long long llm_attention_scratch_floats(int n_tiles, int kv_heads, int n_splits, int rows_per_tile) {
+  return (long long)n_tiles * kv_heads * n_splits * rows_per_tile * (D + 1);
+}
+
+// rows_per_tile: 64 (prefill shape) or 16 (decode shape).  `scratch` is needed when n_splits > 1.
+extern "C" int llm_attention_mma(const void* q, void* out, void* k_base, void* v_base, const int32_t* block_table,
+                                 long long page_stride, int table_stride, int page_tokens, int kv_heads,
+                                 int head_dim, const int32_t* seq_q_start, const int32_t* seq_q_len,
+                                 const int32_t* seq_kv_len, const int32_t* tile_seq, const int32_t* tile_index,
+                                 int n_tiles, int rows_per_tile, int n_splits, float* scratch, int q_heads,
+                                 float scale, int window, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (head_dim != D || q_heads % kv_heads || n_splits < 1 || n_splits > 65535 || kv_heads > 65535) return ERR_BAD_SIZE;
+  if (n_splits > 1 && !scratch) return ERR_BAD_SIZE;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(k_base) |
+       reinterpret_cast<uintptr_t>(v_base)) & 15)
+    return ERR_BAD_ALIGN;
+  AttnArgs a;
+  a.q = reinterpret_cast<const __nv_bfloat16*>(q);
+  a.out = reinterpret_cast<__nv_bfloat16*>(out);
+  a.cache = PagedCache{k_base, v_base, block_table, page_stride, table_stride, page_tokens, kv_heads, head_dim};
+  a.seq_q_start = seq_q_start;
+  a.seq_q_len = seq_q_len;
+  a.seq_kv_len = seq_kv_len;
+  a.tile_seq = tile_seq;
+  a.tile_index = tile_index;
+  a.part_o = scratch;
+  a.part_lse = scratch ? scratch + (long long)n_tiles * kv_heads * n_splits * rows_per_tile * D : nullptr;
+  a.q_heads = q_heads;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.window = window;
+  if (rows_per_tile == 64) return launch<4, 1>(a, n_tiles, kv_heads, n_splits, stream);
+  if (rows_per_tile == 16) return launch<1, 4>(a, n_tiles, kv_heads, n_splits, stream);
+  return ERR_BAD_SIZE;
+}

@@ -56,6 +56,7 @@ class Model:
                 raise ConfigError(f"run order entry {i} names layer {call.layer}; the model has {len(self.blocks)}")
         self.dtype: Optional[torch.dtype] = None
         self.device: Optional[torch.device] = None
+        self._planners = [p for p in self.all_parts() if hasattr(p, "plan_step")]
 
     # ------------------------------------------------------------------ structure
     def all_parts(self) -> List[Part]:
@@ -103,6 +104,11 @@ class Model:
                     yield v.weight
 
     # ------------------------------------------------------------------ one step
+    def plan_step(self, ctx) -> None:
+        """Host-side planning of the parts that need it (never captured in a CUDA graph)."""
+        for part in self._planners:
+            part.plan_step(ctx)
+
     def forward(self, ctx) -> Optional[torch.Tensor]:
         """Runs ctx's tokens; returns float32 logits [wanted rows, vocab] (None if none is wanted)."""
         x = self.embed.forward(ctx)

@@ -22,6 +22,7 @@ import torch
 
 from ..cache.manager import CacheManager
 from ..errors import EngineError
+from ..kernels import lib as K
 from ..parts.base import CallContext
 
 
@@ -65,9 +66,12 @@ class StepContext:
     """What the parts see of a step."""
 
     def __init__(self):
-        self.n_tokens = 0
+        self.n_tokens = 0          # rows the kernels run (a padded decode step runs a few idle rows)
         self.n_seqs = 0
         self.n_want = 0
+        self.pad_seqs = 0          # idle sequences appended to reach a graph-friendly batch size
+        self.max_rows = 0          # the most rows any step brings
+        self.max_seqs = 0
         self.dtype = torch.float32
         self.stream = 0
         self.ws: Optional[Workspace] = None
@@ -81,29 +85,44 @@ class StepContext:
         self.host_kv_len: List[int] = []
         self.max_q_len = 0
         self.max_kv_len = 0
-        self.extras: Dict[str, object] = {}
+        self.extras: Dict[object, object] = {}
+
+
+def padded_batch(n: int) -> int:
+    """Decode batches are padded to 1, 2, 4, 8 and then multiples of 8, so few graphs cover all sizes."""
+    for b in (1, 2, 4, 8):
+        if n <= b:
+            return b
+    return -(-n // 8) * 8
 
 
 class StepRunner:
+    MAX_GRAPHS = 64
+
     def __init__(self, model, cache: CacheManager, *, max_step_tokens: int, max_batch_seqs: Optional[int] = None,
                  use_fast_gemm: bool = True, use_fast_attention: bool = True, use_cuda_graphs: bool = True):
         if model.device is None or model.device.type != "cuda":
             raise EngineError("the step function needs a model bound on a CUDA device; there is no CPU path")
         self.model, self.cache = model, cache
         self.device = model.device
-        self.max_step_tokens = int(max_step_tokens)
         self.max_batch_seqs = int(max_batch_seqs or cache.max_seqs)
+        self.max_step_tokens = max(int(max_step_tokens), padded_batch(self.max_batch_seqs))
         self.vocab = model.spec.vocab_size
         self.ws = Workspace(self.device, self.max_step_tokens)
-        T, S, P, G = self.max_step_tokens, self.max_batch_seqs, cache.max_blocks, len(cache.groups)
+        self.use_cuda_graphs = use_cuda_graphs
+        self._graphs: Dict[object, object] = {}
+        self._seen = set()
+        T, S, P, G = self.max_step_tokens, padded_batch(self.max_batch_seqs), cache.max_blocks, len(cache.groups)
         self._sizes = (T, S, P, G)
         total = 4 * T + 4 * S + G * S * P
         self._host = torch.empty(total, dtype=torch.int32).pin_memory()
         self._host_np = self._host.numpy()
-        self._dev = torch.empty(total, dtype=torch.int32, device=self.device)
+        self._host_np.fill(0)
+        self._dev = torch.zeros(total, dtype=torch.int32, device=self.device)
         self.ctx = StepContext()
         self.ctx.ws = self.ws
         self.ctx.dtype = model.dtype
+        self.ctx.max_rows, self.ctx.max_seqs = T, S
         self.ctx.use_fast_gemm, self.ctx.use_fast_attention = use_fast_gemm, use_fast_attention
         off = 0
 
@@ -113,15 +132,19 @@ class StepRunner:
             off += n
             return view
 
-        self._token_ids, self._positions, self._row_seq, self._want = take(T), take(T), take(T), take(T)
+        # small per-sequence arrays and block tables first, per-row arrays last: a decode step then
+        # sends one short prefix of the block instead of all of it
         self._seq_slot, self._seq_q_start, self._seq_q_len, self._seq_kv_len = take(S), take(S), take(S), take(S)
         self._tables = []
         for _ in range(G):
             h, d = take(S * P)
             self._tables.append((h.reshape(S, P), d.view(S, P)))
+        self._rows_offset = off
+        self._row_capacity = T
+        rows_h, rows_d = take(4 * T)
+        # the four per-row arrays are interleaved in blocks sized for the step at hand; see _row_views
+        self._rows_h, self._rows_d = rows_h, rows_d
         c = self.ctx
-        c.token_ids, c.positions, c.row_seq, c.want_rows = (self._token_ids[1], self._positions[1],
-                                                            self._row_seq[1], self._want[1])
         c.seq_slot, c.seq_q_start, c.seq_q_len, c.seq_kv_len = (self._seq_slot[1], self._seq_q_start[1],
                                                                 self._seq_q_len[1], self._seq_kv_len[1])
         c.calls = []
@@ -129,6 +152,16 @@ class StepRunner:
             table = self._tables[cache.cache_group[i][0]][1] if i in cache.cache_group else None
             view = cache.cache_view(i, table) if table is not None else None
             c.calls.append(CallContext(i, view, call.cache_from is None, cache.states.get(i)))
+
+    def _row_views(self, rows: int):
+        """token ids, positions, batch sequence of a row, wanted rows: four arrays of `rows` entries at
+        the start of the per-row region (so the upload is one prefix of the block)."""
+        h, d = self._rows_h, self._rows_d
+        return [(h[i * rows: (i + 1) * rows], d[i * rows: (i + 1) * rows]) for i in range(4)]
+
+    def metadata_bytes(self, n_tokens: int, n_seqs: int) -> int:
+        """Bytes of step metadata sent to the device for a batch of this shape."""
+        return (self._rows_offset + 4 * n_tokens) * 4
 
     # ------------------------------------------------------------------
     def validate(self, entries: Sequence[StepEntry]) -> Tuple[int, int]:
@@ -172,16 +205,24 @@ class StepRunner:
         for e in entries:
             self.cache.reserve(e.slot, len(e.tokens))
         c = self.ctx
+        n_seqs = len(entries)
+        # a pure decode step (one token and its logits per request) is padded to a few fixed batch
+        # sizes with idle rows, so that one captured graph serves every step of that size
+        decode = self.use_cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+        pad = padded_batch(n_seqs) - n_seqs if decode else 0
+        rows, seqs, wanted = total + pad, n_seqs + pad, n_want + pad
+        (tok_h, tok_d), (pos_h, pos_d), (rs_h, rs_d), (want_h, want_d) = self._row_views(rows)
+        c.token_ids, c.positions, c.row_seq, c.want_rows = tok_d, pos_d, rs_d, want_d
         row = w = 0
         c.host_q_len, c.host_kv_len = [], []
         for s, e in enumerate(entries):
             n = len(e.tokens)
             length = self.cache.length(e.slot)
-            self._token_ids[0][row: row + n] = e.tokens
-            self._positions[0][row: row + n] = np.arange(length, length + n, dtype=np.int32)
-            self._row_seq[0][row: row + n] = s
+            tok_h[row: row + n] = e.tokens
+            pos_h[row: row + n] = np.arange(length, length + n, dtype=np.int32)
+            rs_h[row: row + n] = s
             for place in e.want:
-                self._want[0][w] = row + int(place)
+                want_h[w] = row + int(place)
                 w += 1
             self._seq_slot[0][s] = e.slot
             self._seq_q_start[0][s] = row
@@ -193,12 +234,57 @@ class StepRunner:
         slots = [e.slot for e in entries]
         for gi in range(len(self.cache.groups)):
             self.cache.block_table_rows(gi, slots, self._tables[gi][0])
-        self._dev.copy_(self._host, non_blocking=True)
-        c.n_tokens, c.n_seqs, c.n_want = total, len(entries), n_want
+        for i in range(pad):      # idle rows: token 0 at position 0 of a sequence that holds no page
+            s = n_seqs + i
+            tok_h[row], pos_h[row], rs_h[row], want_h[w] = 0, 0, s, row
+            self._seq_slot[0][s], self._seq_q_start[0][s] = 0, row
+            self._seq_q_len[0][s], self._seq_kv_len[0][s] = 0, 0
+            for gi in range(len(self.cache.groups)):
+                self._tables[gi][0][s].fill(-1)
+            row += 1
+            w += 1
+        used = self._rows_offset + 4 * rows
+        self._dev[:used].copy_(self._host[:used], non_blocking=True)
+        c.n_tokens, c.n_seqs, c.n_want, c.pad_seqs = rows, seqs, wanted, pad
         c.max_q_len, c.max_kv_len = max(c.host_q_len), max(c.host_kv_len)
         c.stream = torch.cuda.current_stream().cuda_stream
         c.extras.clear()
-        logits = self.model.forward(c)
+        self.model.plan_step(c)
+        logits = self._run(c, decode, entries)
         for e in entries:
             self.cache.commit(e.slot, len(e.tokens))
+        return None if logits is None else logits[:n_want]
+
+    # ------------------------------------------------------------------ CUDA graphs
+    def _graph_key(self, c: StepContext, decode: bool, entries) -> Optional[tuple]:
+        plans = tuple(sorted((str(k), v[2:]) for k, v in c.extras.items()
+                             if isinstance(k, tuple) and k and k[0] == "attention_tiles"))
+        if decode:
+            return ("decode", c.n_seqs, plans)
+        return ("general", tuple(c.host_q_len), tuple(tuple(e.want) for e in entries), plans)
+
+    def _run(self, c: StepContext, decode: bool, entries):
+        if not self.use_cuda_graphs:
+            return self.model.forward(c)
+        key = self._graph_key(c, decode, entries)
+        held = self._graphs.get(key)
+        if held is not None:
+            held[0].replay()
+            K.LAUNCHES[0] += held[2]              # the kernels the graph launches
+            return held[1]
+        if key not in self._seen or len(self._graphs) >= self.MAX_GRAPHS:
+            if len(self._seen) < 4096:
+                self._seen.add(key)
+            return self.model.forward(c)          # first time: run directly (also sizes the workspace)
+        graph = torch.cuda.CUDAGraph()
+        before = K.LAUNCHES[0]
+        with torch.cuda.graph(graph):
+            c.stream = torch.cuda.current_stream().cuda_stream
+            logits = self.model.forward(c)
+        launched = K.LAUNCHES[0] - before
+        K.LAUNCHES[0] = before
+        c.stream = torch.cuda.current_stream().cuda_stream
+        self._graphs[key] = (graph, logits, launched)
+        graph.replay()
+        K.LAUNCHES[0] += launched
         return logits

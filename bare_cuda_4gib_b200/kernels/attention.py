@@ -1,5 +1,115 @@
-"""Launcher of the tensor-core paged attention (filled in with the fast kernel)."""
+"""Launcher of the tensor-core paged attention (csrc/attention_mma.cu): one library per head
+size, the per-step list of row tiles, and the choice of how many thread blocks split a tile's keys."""
+
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Dict, Optional
+
+import numpy as np
+import torch
+
+from . import build
+from .lib import CacheView, _check
+
+KEY_BLOCK = 64
+TARGET_BLOCKS = 148 * 2
+_libs: Dict[int, object] = {}
 
 
-def plan_for(head_dim, heads, kv_heads):
-    return None
+def supports(head_dim: int) -> bool:
+    return head_dim % 16 == 0 and 16 <= head_dim <= 128
+
+
+def defines(head_dim: int):
+    return (f"-DHEAD_DIM={head_dim}",)
+
+
+def lib(head_dim: int):
+    l = _libs.get(head_dim)
+    if l is None:
+        l = build.load_library("attention_mma.cu", defines(head_dim))
+        P, I, L, F = c_void_p, c_int, c_longlong, c_float
+        l.llm_attention_mma.argtypes = [P, P, P, P, P, L, I, I, I, I, P, P, P, P, P, I, I, I, P, I, F, I, P]
+        l.llm_attention_mma.restype = c_int
+        l.llm_attention_scratch_floats.argtypes = [I, I, I, I]
+        l.llm_attention_scratch_floats.restype = c_longlong
+        _libs[head_dim] = l
+    return l
+
+
+class AttentionPlan:
+    def __init__(self, head_dim: int, heads: int, kv_heads: int):
+        self.head_dim, self.heads, self.kv_heads = head_dim, heads, kv_heads
+        self.group = heads // kv_heads
+        self.lib = lib(head_dim)
+        self._host = None
+        self._dev = None
+        self._scratch = None
+
+    def buffers(self, ctx, n: int, device):
+        """Pinned and device int32 buffers for the tile list, sized once for the largest step so
+        that their addresses never change (captured CUDA graphs keep them)."""
+        if self._host is None or self._host.numel() < 2 * n:
+            most = -(-ctx.max_rows * self.group // 16) + ctx.max_seqs + 8
+            cap = 2 * max(n, most)
+            self._host = torch.empty(cap, dtype=torch.int32).pin_memory()
+            self._dev = torch.empty(cap, dtype=torch.int32, device=device)
+        return self._host, self._dev
+
+    def scratch(self, ctx, floats: int, device) -> torch.Tensor:
+        """Scratch for split keys; a split step has at most TARGET_BLOCKS + tiles * kv_heads items."""
+        if self._scratch is None or self._scratch.numel() < floats:
+            most = (TARGET_BLOCKS + (ctx.max_seqs + 8) * self.kv_heads) * 16 * (self.head_dim + 1)
+            self._scratch = torch.empty(max(floats, most), dtype=torch.float32, device=device)
+        return self._scratch
+
+
+def plan_for(head_dim: int, heads: int, kv_heads: int) -> Optional[AttentionPlan]:
+    if not supports(head_dim):
+        return None
+    return AttentionPlan(head_dim, heads, kv_heads)
+
+
+def step_tiles(ctx, plan: AttentionPlan):
+    """The step's row tiles for this head grouping: built once per step and shared by all layers."""
+    key = ("attention_tiles", plan.group, plan.kv_heads, plan.head_dim)
+    cached = ctx.extras.get(key)
+    if cached is not None:
+        return cached
+    g = plan.group
+    rows_per_tile = 16 if ctx.max_q_len * g <= 16 else 64
+    counts = [-(-q * g // rows_per_tile) for q in ctx.host_q_len]
+    pad = ctx.pad_seqs if rows_per_tile == 16 else 0     # padded decode steps keep a fixed grid
+    n_tiles = sum(counts) + pad
+    host, dev = plan.buffers(ctx, n_tiles, ctx.token_ids.device)
+    h = host.numpy()
+    at = 0
+    for s, c in enumerate(counts):
+        h[at: at + c] = s
+        h[n_tiles + at: n_tiles + at + c] = np.arange(c, dtype=np.int32)
+        at += c
+    h[at: n_tiles] = -1
+    h[n_tiles + at: 2 * n_tiles] = 0
+    dev[: 2 * n_tiles].copy_(host[: 2 * n_tiles], non_blocking=True)
+    n_splits = 1
+    if rows_per_tile == 16:
+        key_blocks = -(-ctx.max_kv_len // KEY_BLOCK)
+        n_splits = max(1, min(key_blocks, -(-TARGET_BLOCKS // (n_tiles * plan.kv_heads))))
+    out = (dev[:n_tiles], dev[n_tiles: 2 * n_tiles], n_tiles, rows_per_tile, n_splits)
+    ctx.extras[key] = out
+    return out
+
+
+def run(ctx, plan: AttentionPlan, q: torch.Tensor, out: torch.Tensor, cache: CacheView, scale: float,
+        window: int) -> None:
+    tile_seq, tile_index, n_tiles, rows_per_tile, n_splits = step_tiles(ctx, plan)
+    scratch_ptr = 0
+    if n_splits > 1:
+        floats = plan.lib.llm_attention_scratch_floats(n_tiles, plan.kv_heads, n_splits, rows_per_tile)
+        scratch_ptr = plan.scratch(ctx, int(floats), q.device).data_ptr()
+    _check(plan.lib.llm_attention_mma(
+        q.data_ptr(), out.data_ptr(), cache.k_ptr, cache.v_ptr, cache.block_table.data_ptr(), cache.page_stride,
+        cache.table_stride, cache.page_tokens, cache.kv_heads, cache.head_dim, ctx.seq_q_start.data_ptr(),
+        ctx.seq_q_len.data_ptr(), ctx.seq_kv_len.data_ptr(), tile_seq.data_ptr(), tile_index.data_ptr(), n_tiles,
+        rows_per_tile, n_splits, scratch_ptr, plan.heads, scale, window, ctx.stream), "attention_mma")

@@ -45,8 +45,18 @@ def _nvcc() -> str:
                            "nvcc on PATH); there is no fallback path")
 
 
+_build_dir: Optional[pathlib.Path] = None
+
+
 def build_dir() -> pathlib.Path:
     """The folder libraries are written to: in-tree when writable, else per-user temporary."""
+    global _build_dir
+    if _build_dir is None:
+        _build_dir = _pick_build_dir()
+    return _build_dir
+
+
+def _pick_build_dir() -> pathlib.Path:
     override = os.environ.get("BARE_CUDA_B200_BUILD_DIR")
     candidates = [pathlib.Path(override)] if override else []
     candidates.append(_PACKAGE_BUILD)
@@ -54,7 +64,7 @@ def build_dir() -> pathlib.Path:
     for c in candidates:
         try:
             c.mkdir(parents=True, exist_ok=True)
-            probe = c / f".writable-{os.getpid()}"
+            probe = c / f".writable-{os.getpid()}-{threading.get_ident()}"
             probe.write_text("")
             probe.unlink()
             return c

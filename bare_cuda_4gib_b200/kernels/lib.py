@@ -31,12 +31,17 @@ def dtype_code(dtype: torch.dtype) -> int:
         raise KernelLaunchError(f"element type {dtype} is not supported (float32 or bfloat16)") from None
 
 
+LAUNCHES = [0]   # launcher calls so far (each launches one kernel; the sampler launches two)
+
+
 def _check(status: int, what: str) -> None:
+    LAUNCHES[0] += 1
     if status == 0:
         return
+    if status >= 2000:
+        raise KernelLaunchError(f"{what}: CUDA driver error {status - 2000}")
     if status >= 1000:
-        raise KernelLaunchError(f"{what}: CUDA error {status - 1000} "
-                                f"({torch.cuda.cudart().cudaGetErrorString(status - 1000) if hasattr(torch.cuda.cudart(), 'cudaGetErrorString') else ''})")
+        raise KernelLaunchError(f"{what}: CUDA runtime error {status - 1000}")
     raise KernelLaunchError(f"{what}: {_STATUS_TEXT.get(status, f'status {status}')}")
 
 

@@ -66,6 +66,11 @@ class Attention(Part):
         else:
             self.fast = None
 
+    def plan_step(self, ctx) -> None:
+        if self.fast is not None and ctx.use_fast_attention:
+            from ..kernels import attention as fast
+            fast.step_tiles(ctx, self.fast)
+
     def forward(self, ctx, call, h: torch.Tensor) -> K.Partials:
         n = ctx.n_tokens
         qd = self.heads * self.head_dim

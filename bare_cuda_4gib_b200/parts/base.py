@@ -78,6 +78,10 @@ class Part:
     def prepare(self, dtype: torch.dtype, device: torch.device) -> None:
         """Called once after binding, on the device: fuse tensors, build tables, compile kernels."""
 
+    # A part that must look at the batch on the host before its kernels run (to build work lists
+    # and upload them) defines `plan_step(ctx)`; it is called once per step before `forward`, and
+    # is NOT part of a captured CUDA graph, while `forward` may be.
+
 
 class CallContext:
     """One run of a layer inside a step: its index in the run order, the cache it reads (and

@@ -15,8 +15,8 @@ DEV = "cuda"
 
 def _ctx(max_rows=4096):
     from bare_cuda_4gib_b200.engine.step import Workspace
-    return types.SimpleNamespace(ws=Workspace(torch.device(DEV), max_rows),
-                                 stream=torch.cuda.current_stream().cuda_stream)
+    return types.SimpleNamespace(ws=Workspace(torch.device(DEV), max_rows), max_rows=max_rows, max_seqs=64,
+                                 pad_seqs=0, stream=torch.cuda.current_stream().cuda_stream)
 
 
 def _close(got, want, rtol, atol):
@@ -254,3 +254,96 @@ def test_gemm_tcgen05_swiglu(m, inter, k):
     g, u = gu[:, :inter], gu[:, inter:]
     want = g / (1 + torch.exp(-g)) * u
     _close(res.tensor, want, 2 ** -7, 1e-3)
+
+
+# ------------------------------------------------------------------------------ tensor-core attention
+
+def _attention_case(seqs, heads, kv_heads, d, page, window, seed, far_key=False):
+    """seqs: [(q_len, kv_len)].  Fills a scrambled paged cache, runs attention_mma and the dense reference."""
+    from bare_cuda_4gib_b200.kernels import attention as fast
+    from bare_cuda_4gib_b200.kernels.lib import CacheView
+
+    torch.manual_seed(seed)
+    g = heads // kv_heads
+    max_blocks = max(-(-kv // page) for _, kv in seqs)
+    n_pages = sum(-(-kv // page) for _, kv in seqs) + 3
+    elems = 2 * kv_heads * page * d
+    storage = torch.zeros(n_pages, elems, device=DEV, dtype=torch.bfloat16)
+    storage[-1].fill_(float("nan"))           # a page nobody owns: reading it would poison the result
+    table = torch.full((len(seqs), max_blocks + 1), -1, dtype=torch.int32, device=DEV)
+    perm = list(range(n_pages - 1))
+    random.Random(seed).shuffle(perm)
+    ks, vs, at = [], [], 0
+    for s, (q_len, kv_len) in enumerate(seqs):
+        k = torch.randn(kv_len, kv_heads, d, device=DEV).to(torch.bfloat16)
+        v = torch.randn(kv_len, kv_heads, d, device=DEV).to(torch.bfloat16)
+        if far_key:
+            k = (0.05 * k.float()).to(torch.bfloat16)
+            k[3 % kv_len] = 0
+            k[3 % kv_len, :, 0] = 60.0
+        nb = -(-kv_len // page)
+        pages = perm[at: at + nb]
+        at += nb
+        table[s, :nb] = torch.tensor(pages, dtype=torch.int32)
+        sv = storage.view(n_pages, 2, kv_heads, page, d)
+        for b, pg in enumerate(pages):
+            lo, hi = b * page, min(kv_len, (b + 1) * page)
+            sv[pg, 0, :, : hi - lo] = k[lo:hi].transpose(0, 1)
+            sv[pg, 1, :, : hi - lo] = v[lo:hi].transpose(0, 1)
+        ks.append(k)
+        vs.append(v)
+    esize = 2
+    view = CacheView(storage.data_ptr(), storage.data_ptr() + (elems // 2) * esize, table, elems, table.shape[1],
+                     page, kv_heads, d, torch.bfloat16)
+    n = sum(q for q, _ in seqs)
+    q = torch.randn(n, heads, d, device=DEV).to(torch.bfloat16)
+    if far_key:
+        q = torch.zeros_like(q)
+        q[:, :, 0] = 4.0
+    starts = [sum(x for x, _ in seqs[:i]) for i in range(len(seqs))]
+    ctx = _ctx()
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len = i32(starts), i32([a for a, _ in seqs]), i32([b for _, b in seqs])
+    ctx.token_ids = i32([0])
+    ctx.host_q_len, ctx.host_kv_len = [a for a, _ in seqs], [b for _, b in seqs]
+    ctx.max_q_len, ctx.max_kv_len = max(ctx.host_q_len), max(ctx.host_kv_len)
+    ctx.extras = {}
+    out = torch.full((n, heads * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+    plan = fast.plan_for(d, heads, kv_heads)
+    scale = 1.0 / math.sqrt(d)
+    fast.run(ctx, plan, q.view(n, heads * d), out, view, scale, window)
+    want = torch.zeros(n, heads, d, dtype=torch.float64, device=DEV)
+    for s, (q_len, kv_len) in enumerate(seqs):
+        for i in range(q_len):
+            pos = kv_len - q_len + i
+            lo = max(0, pos - window + 1) if window > 0 else 0
+            for h in range(heads):
+                sc = (ks[s][lo: pos + 1, h // g].double() @ q[starts[s] + i, h].double()) * scale
+                want[starts[s] + i, h] = torch.softmax(sc, 0) @ vs[s][lo: pos + 1, h // g].double()
+    return out.view(n, heads, d), want, ctx
+
+
+@pytest.mark.parametrize("heads,kv_heads,d,page", [(8, 1, 64, 64), (6, 2, 32, 16), (4, 4, 128, 32), (32, 2, 16, 16),
+                                                   (5, 5, 64, 64), (12, 4, 64, 16)])
+def test_attention_mma_prefill_and_mixed(heads, kv_heads, d, page):
+    # whole prompts, a portion after a cached prefix, and single decode rows beside them
+    seqs = [(37, 37), (5, 133), (1, 70), (64, 64), (2, 2), (1, 1), (19, 300)]
+    got, want, _ = _attention_case(seqs, heads, kv_heads, d, page, 0, seed=heads + d)
+    _close(got, want, 2 ** -7, 4e-3)
+
+
+@pytest.mark.parametrize("heads,kv_heads,d,page", [(32, 4, 64, 64), (3, 1, 32, 32), (16, 16, 128, 16), (16, 1, 64, 64)])
+def test_attention_mma_decode_split(heads, kv_heads, d, page):
+    seqs = [(1, 2048), (1, 1), (1, 65), (1, 700)]
+    got, want, ctx = _attention_case(seqs, heads, kv_heads, d, page, 0, seed=d)
+    if heads // kv_heads <= 16:
+        assert any(v[3] == 16 and v[4] > 1 for k, v in ctx.extras.items())   # the split shape ran
+    _close(got, want, 2 ** -7, 4e-3)
+
+
+def test_attention_mma_window_and_far_key():
+    got, want, _ = _attention_case([(40, 200), (1, 150), (90, 90)], 4, 2, 64, 16, 50, seed=1)
+    _close(got, want, 2 ** -7, 4e-3)
+    # one early key dominates every query: the output must be that key's value row
+    got, want, _ = _attention_case([(1, 900), (33, 500)], 8, 2, 64, 64, 0, seed=2, far_key=True)
+    _close(got, want, 2 ** -7, 4e-3)
