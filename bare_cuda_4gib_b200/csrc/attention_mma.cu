@@ -425,3 +425,46 @@ extern "C" int llm_attention_mma(const void* q, void* out, void* k_base, void* v
   if (rows_per_tile == 16) return launch<1, 4>(a, n_tiles, kv_heads, n_splits, stream);
   return ERR_BAD_SIZE;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Entry point that allocates nothing (declared in attention_no_alloc.h; it has no counterpart in
+// cuongvng/bare-cuda-4gib).  Same computation as llm_attention_mma, but the scratch memory for
+// split keys is a fixed array inside this library instead of a buffer the caller allocates.
+
+#include "attention_no_alloc.h"
+
+static __device__ __align__(256) float g_static_scratch[LLM_ATTENTION_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+// Device address of g_static_scratch, looked up once per device.  In host code the array's name
+// is only a handle for the runtime, never an address a kernel may be given.
+float* g_static_scratch_address[MAX_DEVICES] = {};
+}  // namespace
+
+extern "C" int llm_attention_mma_static_scratch(const void* q, void* out, void* k_base, void* v_base,
+                                                const int32_t* block_table, long long page_stride,
+                                                int table_stride, int page_tokens, int kv_heads, int head_dim,
+                                                const int32_t* seq_q_start, const int32_t* seq_q_len,
+                                                const int32_t* seq_kv_len, const int32_t* tile_seq,
+                                                const int32_t* tile_index, int n_tiles, int rows_per_tile,
+                                                int n_splits, int q_heads, float scale, int window,
+                                                cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (n_splits < 1 || kv_heads < 1 || (rows_per_tile != 16 && rows_per_tile != 64)) return ERR_BAD_SIZE;
+  const long long need = llm_attention_scratch_floats(n_tiles, kv_heads, n_splits, rows_per_tile);
+  if (n_splits > 1 && need > (long long)LLM_ATTENTION_STATIC_SCRATCH_FLOATS) return LLM_ERR_STATIC_SCRATCH_TOO_SMALL;
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return 1000 + (int)e;
+  if (device < 0 || device >= MAX_DEVICES) return ERR_BAD_SIZE;
+  if (!g_static_scratch_address[device]) {
+    float* address = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&address), g_static_scratch);
+    if (e != cudaSuccess) return 1000 + (int)e;
+    g_static_scratch_address[device] = address;
+  }
+  return llm_attention_mma(q, out, k_base, v_base, block_table, page_stride, table_stride, page_tokens, kv_heads,
+                           head_dim, seq_q_start, seq_q_len, seq_kv_len, tile_seq, tile_index, n_tiles,
+                           rows_per_tile, n_splits, g_static_scratch_address[device], q_heads, scale, window, stream);
+}
