@@ -57,6 +57,9 @@ class Model:
         self.dtype: Optional[torch.dtype] = None
         self.device: Optional[torch.device] = None
         self._planners = [p for p in self.all_parts() if hasattr(p, "plan_step")]
+        # a part whose forward does host-dependent work sets `graph_safe = False`; steps of such a
+        # model are never captured as CUDA graphs
+        self.graph_safe = all(getattr(p, "graph_safe", True) for p in self.all_parts())
 
     # ------------------------------------------------------------------ structure
     def all_parts(self) -> List[Part]:
@@ -140,9 +143,14 @@ def load_model(folder, dtype="bfloat16", device="cuda") -> Tuple[Model, object]:
     cfg_dict = read_config_json(folder)
     arch = resolve_architecture(cfg_dict)
     config = arch.config_class.from_dict(cfg_dict)
-    spec = arch.build_spec(config)
+    return load_model_with_spec(folder, arch.build_spec(config), dtype, device), config
+
+
+def load_model_with_spec(folder, spec: ModelSpec, dtype="bfloat16", device="cuda") -> Model:
+    """Builds the model a spec describes and binds the folder's tensors to it (the spec need not come
+    from a registered architecture)."""
     expected, model = expected_weights(spec)
     dt = run_dtype(dtype)
     tensors = load_weights(folder, expected, spec.aliases, spec.ignorable, dt, torch.device(device))
     model.bind(tensors, dt, device)
-    return model, config
+    return model

@@ -81,6 +81,7 @@ class StepContext:
         self.use_fast_gemm = True
         self.use_fast_attention = True
         # host copies, for parts that plan their launches from the batch's shape
+        self.host_slots: List[int] = []
         self.host_q_len: List[int] = []
         self.host_kv_len: List[int] = []
         self.max_q_len = 0
@@ -109,7 +110,7 @@ class StepRunner:
         self.max_step_tokens = max(int(max_step_tokens), padded_batch(self.max_batch_seqs))
         self.vocab = model.spec.vocab_size
         self.ws = Workspace(self.device, self.max_step_tokens)
-        self.use_cuda_graphs = use_cuda_graphs
+        self.use_cuda_graphs = use_cuda_graphs and model.graph_safe
         self._graphs: Dict[object, object] = {}
         self._seen = set()
         T, S, P, G = self.max_step_tokens, padded_batch(self.max_batch_seqs), cache.max_blocks, len(cache.groups)
@@ -197,6 +198,19 @@ class StepRunner:
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Runs the batch; returns float32 logits [wanted, vocab] on the device, in the order of
         the entries and of each entry's `want` (None if nothing is wanted)."""
+        decode, n_want = self.begin(entries)
+        logits = self._run(self.ctx, decode, entries)
+        self.finish(entries)
+        return None if logits is None else logits[:n_want]
+
+    def finish(self, entries: Sequence[StepEntry]) -> None:
+        """Moves the requests' lengths once every layer has written the step's keys and values."""
+        for e in entries:
+            self.cache.commit(e.slot, len(e.tokens))
+
+    def begin(self, entries: Sequence[StepEntry]) -> Tuple[bool, int]:
+        """Validates the batch, takes its pages, builds and sends the step's metadata and lets the
+        parts plan; after this `self.ctx` describes the step.  Returns (pure decode step, wanted rows)."""
         total, n_want = self.validate(entries)
         if not self.cache.can_reserve([(e.slot, len(e.tokens)) for e in entries]):
             from ..errors import OutOfPages
@@ -247,13 +261,11 @@ class StepRunner:
         self._dev[:used].copy_(self._host[:used], non_blocking=True)
         c.n_tokens, c.n_seqs, c.n_want, c.pad_seqs = rows, seqs, wanted, pad
         c.max_q_len, c.max_kv_len = max(c.host_q_len), max(c.host_kv_len)
+        c.host_slots = slots
         c.stream = torch.cuda.current_stream().cuda_stream
         c.extras.clear()
         self.model.plan_step(c)
-        logits = self._run(c, decode, entries)
-        for e in entries:
-            self.cache.commit(e.slot, len(e.tokens))
-        return None if logits is None else logits[:n_want]
+        return decode, n_want
 
     # ------------------------------------------------------------------ CUDA graphs
     def _graph_key(self, c: StepContext, decode: bool, entries) -> Optional[tuple]:

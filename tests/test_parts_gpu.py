@@ -1,0 +1,292 @@
+"""Parts alone against the plain implementation, and the generality of the layer machinery:
+a toy mixer with state of its own registered from this file, a layer that runs twice, a run that
+reads another run's cache, and a windowed mixer in one layer only - none of them a model of anyone's."""
+
+import random
+
+import pytest
+import torch
+
+import helpers as H
+import plain_llama as pl
+
+pytestmark = pytest.mark.gpu
+F64 = torch.float64
+
+
+def _runner(model, page_tokens, max_tokens, max_live=4, num_pages=None, **opts):
+    from bare_cuda_4gib_b200.cache.manager import CacheManager
+    from bare_cuda_4gib_b200.engine.step import StepRunner
+
+    cap = -(-max_tokens // page_tokens) * page_tokens
+    cache = CacheManager(model.cache_demands(), page_tokens=page_tokens, max_seqs=max_live, max_tokens=cap,
+                         num_pages=num_pages or (max_live * cap // page_tokens), dtype=model.dtype, device="cuda")
+    return StepRunner(model, cache, max_step_tokens=cap, max_batch_seqs=max_live, **opts), cache
+
+
+def _llama(name, dtype, mutate=None):
+    """The tiny configuration's model, optionally with its spec changed before the parts are built."""
+    import bare_cuda_4gib_b200.models  # noqa: F401
+    from bare_cuda_4gib_b200.config import LlamaConfig, resolve_architecture
+    from bare_cuda_4gib_b200.engine.model import load_model_with_spec
+
+    cfg = LlamaConfig.from_dict(H.TINY[name][0])
+    spec = resolve_architecture(H.TINY[name][0]).build_spec(cfg)
+    if mutate:
+        mutate(spec)
+    return load_model_with_spec(H.model_folder(name), spec, dtype, "cuda"), cfg
+
+
+def _tol(dtype):
+    return 1e-5 if dtype == "float32" else 3e-2
+
+
+def _err(got, want):
+    got, want = got.double().cpu(), want.double().cpu()
+    return float((got - want).abs().max() / want.abs().max())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_each_part_alone(name, dtype):
+    """norm, mixer, feed-forward, block, embedding and head, each called by itself on given inputs."""
+    from bare_cuda_4gib_b200.engine.step import StepEntry
+    from bare_cuda_4gib_b200.kernels.lib import Partials
+
+    model, cfg = _llama(name, dtype)
+    plain = H.plain_model(H.model_folder(name))
+    page = H.TINY[name][1]
+    runner, cache = _runner(model, page, 64, use_cuda_graphs=False)
+    rng = random.Random(2)
+    lens = [23, 9]
+    ids = [H.random_ids(rng, n, cfg.vocab_size) for n in lens]
+    slots = [cache.acquire_slot() for _ in lens]
+    entries = [StepEntry(s, t, [len(t) - 1]) for s, t in zip(slots, ids)]
+    runner.begin(entries)
+    ctx, n, hid = runner.ctx, sum(lens), cfg.hidden_size
+    act = model.dtype
+    layer, pl_layer = model.blocks[1], plain.layers[1]
+    positions = torch.cat([torch.arange(k) for k in lens])
+
+    # embedding
+    x = model.embed.forward(ctx)
+    want_x = pl.embedding(plain.embed, torch.tensor(ids[0] + ids[1]))
+    assert torch.equal(x[:n].cpu().double(), want_x)
+
+    # norm with a pending contribution in two partial results
+    res = torch.randn(n, hid, device="cuda")
+    delta = torch.randn(2, n, hid, device="cuda")
+    res_in = res.clone()
+    h = layer.mixer_norm.forward(ctx, res, Partials(delta, 2), n)
+    want_res = res_in.double().cpu() + delta.double().sum(0).cpu()
+    assert _err(res, want_res) < 1e-6
+    assert _err(h, pl.rms_norm(want_res, pl_layer.input_norm, plain.rms_norm_eps)) < (1e-5 if dtype == "float32" else 8e-3)
+
+    # mixer (attention over the cache it has just written), one request after the other in the plain version
+    hin = (0.5 * torch.randn(n, hid, device="cuda")).to(act)
+    mixed = layer.mixer.forward(ctx, ctx.calls[1], hin)
+    got = mixed.tensor.float().sum(0) if mixed.n > 1 else mixed.tensor.float()
+    want, at = [], 0
+    for k in lens:
+        out, _ = pl.attention_mixer(plain, pl_layer, hin[at: at + k].double().cpu(), torch.arange(k))
+        want.append(out)
+        at += k
+    assert _err(got[:n], torch.cat(want)) < _tol(dtype)
+
+    # feed-forward
+    ff = layer.ffn.forward(ctx, hin)
+    got = ff.tensor.float().sum(0) if ff.n > 1 else ff.tensor.float()
+    assert _err(got[:n], pl.feed_forward(pl_layer, hin.double().cpu())) < _tol(dtype)
+
+    # block: residual in, residual + both contributions out (the last one still pending)
+    res = (0.5 * torch.randn(n, hid, device="cuda"))
+    res_in = res.clone()
+    pending = layer.forward(ctx, ctx.calls[1], res, None)
+    got = res.double() + (pending.tensor.double().sum(0) if pending.n > 1 else pending.tensor.double())
+    want, at = [], 0
+    for k in lens:
+        out, _ = pl.decoder_block(plain, pl_layer, res_in[at: at + k].double().cpu(), torch.arange(k))
+        want.append(out)
+        at += k
+    assert _err(got[:n], torch.cat(want)) < _tol(dtype)
+
+    # final norm on the wanted rows + head
+    res = torch.randn(n, hid, device="cuda")
+    normed = model.final_norm.forward(ctx, res, None, ctx.n_want, ctx.want_rows, buffer="final_normed")
+    logits = model.head.forward(ctx, normed, ctx.n_want)
+    rows = [lens[0] - 1, n - 1]
+    want = pl.output_head(plain, res[rows].double().cpu())
+    assert _err(logits[:2], want) < _tol(dtype)
+
+
+# ------------------------------------------------------------------------------ run order as data
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layer_named_twice_and_borrowed_cache(dtype):
+    from bare_cuda_4gib_b200.parts.spec import LayerCall
+
+    order = [(0, None), (1, None), (0, None), (1, 1)]
+
+    def mutate(spec):
+        spec.order = [LayerCall(l, c) for l, c in order]
+
+    model, cfg = _llama("A", dtype, mutate)
+    assert len(model.cache_demands()) == 4
+    runner, cache = _runner(model, 16, 96)
+    assert len(cache.groups) == 1 and cache.groups[0].members == [0, 1, 2]     # the fourth run owns no cache
+    plain = pl.read_model_folder(H.model_folder("A"))
+    plain.order = order
+    rng = random.Random(4)
+    ids = H.random_ids(rng, 70, cfg.vocab_size)
+    want = pl.forward_logits(plain, ids)
+    from bare_cuda_4gib_b200.engine.step import StepEntry
+    slot = cache.acquire_slot()
+    got, fed = [], 0
+    for size in (19, 2, 30, 1, 1, 17):
+        got.append(runner.step([StepEntry(slot, ids[fed: fed + size], list(range(size)))]).float().cpu().clone())
+        fed += size
+    got = torch.cat(got)
+    for p in range(70):
+        assert H.row_error(got[p], want[p]) < H.TOLERANCE[dtype], p
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_window_in_one_layer_gives_pages_back(dtype):
+    window = 24
+
+    def mutate(spec):
+        spec.layers[1].mixer.params["window"] = window          # layer 1 only: two cache groups
+
+    model, cfg = _llama("B", dtype, mutate)
+    runner, cache = _runner(model, 16, 240, max_live=2, num_pages=30)
+    assert len(cache.groups) == 2
+    plain = pl.read_model_folder(H.model_folder("B"))
+    plain.layers[1].window = window
+    rng = random.Random(6)
+    ids = H.random_ids(rng, 200, cfg.vocab_size)
+    want = pl.forward_logits(plain, ids)
+    from bare_cuda_4gib_b200.engine.step import StepEntry
+    slot = cache.acquire_slot()
+    got, fed, sizes = [], 0, [50, 3, 40, 1, 1, 1, 33, 2, 60, 9]
+    held = []
+    for size in sizes:
+        got.append(runner.step([StepEntry(slot, ids[fed: fed + size], list(range(size)))]).float().cpu().clone())
+        fed += size
+        cache.check_consistency()
+        held.append(cache.pages_in_use())
+    got = torch.cat(got)
+    for p in range(fed):
+        assert H.row_error(got[p], want[p]) < H.TOLERANCE[dtype], p
+    windowed = [g for g in cache.groups if g.request.window == window][0]
+    full = [g for g in cache.groups if g.request.window is None][0]
+    assert full.pool.pages_in_use == -(-200 // 16)
+    assert windowed.pool.pages_in_use <= -(-(window + 9) // 16) + 1     # only the window's pages remain
+    assert windowed.pool.acquired_total > windowed.pool.pages_in_use
+
+
+# ------------------------------------------------------------------------------ a toy mixer with state
+
+
+def test_toy_mixer_with_state_is_registered_built_and_stepped():
+    """A mixer defined here - an exponential moving average of its inputs, kept per request in a
+    state slot - is registered, put into one layer of a model beside attention layers, and stepped
+    in portions and in a batch; the engine's files are not touched."""
+    from bare_cuda_4gib_b200.config import LlamaConfig
+    from bare_cuda_4gib_b200.engine.model import expected_weights, Model
+    from bare_cuda_4gib_b200.engine.step import StepEntry
+    from bare_cuda_4gib_b200.kernels.lib import Partials
+    from bare_cuda_4gib_b200.models.llama import llama_spec
+    from bare_cuda_4gib_b200.parts import Part, PartSpec, StateRequest, register_mixer
+    from bare_cuda_4gib_b200.weights import random_tensors
+
+    @register_mixer("toy_moving_average")
+    class MovingAverage(Part):
+        graph_safe = False        # its forward loops over requests on the host
+
+        def local_weights(self):
+            h = self.params["hidden"]
+            return {"out": ((h, h), "matrix")}
+
+        def cache_request(self):
+            return None           # no pages
+
+        def state_request(self):
+            return StateRequest((self.params["hidden"],), torch.float32)
+
+        def forward(self, ctx, call, h):
+            decay = self.params["decay"]
+            out = torch.zeros(ctx.n_tokens, self.params["hidden"], device=h.device)
+            row = 0
+            for slot, n in zip(ctx.host_slots, ctx.host_q_len):
+                state = call.state[slot]
+                for t in range(n):
+                    state.mul_(decay).add_(h[row].float(), alpha=1.0 - decay)
+                    out[row] = self.tensors["out"].float() @ state
+                    row += 1
+            return Partials(out)
+
+    cfg = LlamaConfig.from_dict(H.TINY_A)
+    spec = llama_spec(cfg)
+    decay = 0.75
+    spec.layers[0].mixer = PartSpec("toy_moving_average", {"hidden": cfg.hidden_size, "decay": decay},
+                                    {"out": "model.layers.0.toy.out.weight"})
+    expected, model = expected_weights(spec)
+    assert "model.layers.0.toy.out.weight" in expected and "model.layers.0.self_attn.q_proj.weight" not in expected
+    tensors = {k: v.to("cuda", torch.float32) for k, v in random_tensors(expected, seed=5).items()}
+    model.bind(tensors, torch.float32, "cuda")
+    assert not model.graph_safe
+    demands = model.cache_demands()
+    assert demands[0].kv is None and demands[0].state is not None and demands[1].kv is not None
+    runner, cache = _runner(model, 16, 64)
+    assert 0 in cache.states and len(cache.groups) == 1 and cache.groups[0].members == [1]
+
+    # the same model, plainly: layer 0 with the moving average, layer 1 as the plain Llama layer
+    t64 = {k: v.double().cpu() for k, v in tensors.items()}
+    plain = pl.PlainModel(cfg.vocab_size, cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads,
+                          cfg.head_dim, cfg.intermediate_size, cfg.rope_theta, cfg.rms_norm_eps,
+                          t64["model.embed_tokens.weight"], t64["model.norm.weight"], t64["lm_head.weight"])
+
+    def layer_of(i):
+        p = f"model.layers.{i}."
+        g = lambda n: t64.get(p + n)
+        return pl.PlainLayer(g("input_layernorm.weight"), g("self_attn.q_proj.weight"), g("self_attn.k_proj.weight"),
+                             g("self_attn.v_proj.weight"), g("self_attn.o_proj.weight"),
+                             g("post_attention_layernorm.weight"), g("mlp.gate_proj.weight"),
+                             g("mlp.up_proj.weight"), g("mlp.down_proj.weight"))
+
+    def plain_forward(ids):
+        x = pl.embedding(plain.embed, torch.tensor(ids))
+        l0, l1 = layer_of(0), layer_of(1)
+        h = pl.rms_norm(x, l0.input_norm, plain.rms_norm_eps)
+        state, mixed = torch.zeros(cfg.hidden_size, dtype=F64), []
+        for t in range(len(ids)):
+            state = decay * state + (1 - decay) * h[t].float().double()   # the toy keeps float32 state
+            mixed.append(t64["model.layers.0.toy.out.weight"] @ state)
+        x = x + torch.stack(mixed)
+        x = x + pl.feed_forward(l0, pl.rms_norm(x, l0.post_norm, plain.rms_norm_eps))
+        x, _ = pl.decoder_block(plain, l1, x, torch.arange(len(ids)))
+        return pl.output_head(plain, x)
+
+    rng = random.Random(12)
+    a, b = H.random_ids(rng, 30, cfg.vocab_size), H.random_ids(rng, 21, cfg.vocab_size)
+    want_a, want_b = plain_forward(a), plain_forward(b)
+    sa, sb = cache.acquire_slot(), cache.acquire_slot()
+    got_a = [runner.step([StepEntry(sa, a[:11], list(range(11)))]).float().cpu().clone()]
+    mix = runner.step([StepEntry(sa, a[11:13], [0, 1]), StepEntry(sb, b[:20], list(range(20)))]).float().cpu().clone()
+    got_a.append(mix[:2])
+    got_b = [mix[2:]]
+    both = runner.step([StepEntry(sb, b[20:], [0]), StepEntry(sa, a[13:], list(range(17)))]).float().cpu().clone()
+    got_b.append(both[:1])
+    got_a.append(both[1:])
+    got_a, got_b = torch.cat(got_a), torch.cat(got_b)
+    for p in range(30):
+        assert H.row_error(got_a[p], want_a[p]) < 2e-5, p
+    for p in range(21):
+        assert H.row_error(got_b[p], want_b[p]) < 2e-5, p
+    # a new request in a used slot starts from a zeroed state
+    cache.release_slot(sa)
+    sc = cache.acquire_slot()
+    assert sc == sa
+    again = runner.step([StepEntry(sc, a, list(range(30)))]).float().cpu()
+    assert H.row_error(again[29], want_a[29]) < 2e-5
