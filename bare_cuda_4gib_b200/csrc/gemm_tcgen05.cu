@@ -4,20 +4,25 @@
 // (engine/kernels/gemm_tiled.cuh:36-96 for m > 16, engine/kernels/gemv_fp16.cu:21-101 for
 // m <= 16) with one kernel for prefill and decode.
 //
-// Orientation.  The weight matrix is the 128-row MMA operand (A) and the activations are the
-// N operand (B): one thread block computes 128 output features for BN tokens, BN in
-// {16, 32, 64, 128, 256}.  A decode step with few tokens therefore still fills the 128 MMA
-// rows with weights, which is what has to be streamed from memory; a prefill step uses BN=256.
-// In tensor memory, lane = feature and column = token, so an epilogue warp stores 32
-// consecutive features of one token with one coalesced store.
+// Two orientations of the same kernel.
+// ORIENT 0 (few tokens): the weight matrix is the 128-row MMA operand (A) and the activations are
+// the N operand (B): one thread block computes 128 output features for BN tokens, BN in
+// {16, 32, 64, 128, 256}.  A decode step therefore still fills the 128 MMA rows with weights,
+// which is what has to be streamed from memory.  In tensor memory lane = feature and column =
+// token, so an epilogue warp stores 32 consecutive features of one token with one store.
+// ORIENT 1 (many tokens): 128 tokens are the MMA rows and BN (128 or 256) output features the
+// N operand; lane = token, column = feature, so an epilogue thread stores 16 consecutive
+// features of its token with vector stores.
 //
 // Split K.  gridDim.z thread blocks share the K range of a tile; each writes its float32 partial
 // result to out + z * partial_stride.  The consumer kernels (residual add + norm, rotation,
 // SwiGLU) add the partials in index order, so no atomics and no reduction pass are needed and
 // the result does not depend on timing.
 //
-// MODE 1 (SwiGLU): w is [gate rows; up rows]; the block accumulates gate and up for the same
-// 128 features in two accumulators and stores silu(gate) * up.
+// MODE 1 (SwiGLU): w is [gate rows; up rows] and the block stores silu(gate) * up.  ORIENT 0
+// accumulates gate and up for the same 128 features in two accumulators; ORIENT 1 loads BN/2 gate
+// rows and the matching BN/2 up rows as one N operand, so a thread finds gate in column c and up
+// in column BN/2 + c.
 //
 // Warps: 0 = TMA producer, 1 = tensor memory allocation + MMA issue, 2..5 = epilogue.
 // Every wait on an mbarrier is bounded: after about a second without progress the thread sets
@@ -134,14 +139,14 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr));
 }
 
-template <int BN, int MODE>
+template <int BN, int MODE, int ORIENT>
 struct Layout {
-  static constexpr int A_TILES = MODE == 1 ? 2 : 1;
+  static constexpr int A_TILES = (MODE == 1 && ORIENT == 0) ? 2 : 1;
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
   // small token tiles are the weight-streaming case: two blocks per SM keep more tiles resident
-  static constexpr int BLOCKS_PER_SM = (BN <= 64 && MODE == 0) ? 2 : 1;
+  static constexpr int BLOCKS_PER_SM = (BN <= 64 && MODE == 0 && ORIENT == 0) ? 2 : 1;
   static constexpr int SMEM_BUDGET = (BLOCKS_PER_SM == 2 ? 104 : 200) * 1024;
   static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
@@ -150,13 +155,13 @@ struct Layout {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
-template <int BN, int MODE>
-__global__ void __launch_bounds__(NUM_THREADS, (Layout<BN, MODE>::BLOCKS_PER_SM))
+template <int BN, int MODE, int ORIENT>
+__global__ void __launch_bounds__(NUM_THREADS, (Layout<BN, MODE, ORIENT>::BLOCKS_PER_SM))
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                     void* __restrict__ out, int out_is_f32, int n_tokens, int n_features, int k_blocks,
                     int k_blocks_per_split, long long ld_out, long long partial_stride, int up_row_offset,
                     int* __restrict__ error_word) {
-  using L = Layout<BN, MODE>;
+  using L = Layout<BN, MODE, ORIENT>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::STAGES * L::STAGE_BYTES);
@@ -166,8 +171,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int f0 = blockIdx.x * BM;
-  const int t0 = blockIdx.y * BN;
+  // ORIENT 0: 128 features x BN tokens.  ORIENT 1: 128 tokens x BN features (MODE 1: BN/2 outputs).
+  constexpr int F_TILE = ORIENT == 0 ? BM : (MODE == 1 ? BN / 2 : BN);
+  const int f0 = blockIdx.x * F_TILE;
+  const int t0 = blockIdx.y * (ORIENT == 0 ? BN : BM);
   const int kb_begin = blockIdx.z * k_blocks_per_split;
   const int kb_end = min(k_blocks, kb_begin + k_blocks_per_split);
   const int n_kb = max(0, kb_end - kb_begin);
@@ -207,9 +214,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         uint8_t* stage = smem + s * L::STAGE_BYTES;
         mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
         const int k0 = (kb_begin + i) * BK;
-        tma_load_2d(stage, &map_w, &full_bar[s], k0, f0);
-        if (MODE == 1) tma_load_2d(stage + L::A_BYTES, &map_w, &full_bar[s], k0, up_row_offset + f0);
-        tma_load_2d(stage + L::A_TILES * L::A_BYTES, &map_a, &full_bar[s], k0, t0);
+        if (ORIENT == 0) {
+          tma_load_2d(stage, &map_w, &full_bar[s], k0, f0);
+          if (MODE == 1) tma_load_2d(stage + L::A_BYTES, &map_w, &full_bar[s], k0, up_row_offset + f0);
+          tma_load_2d(stage + L::A_TILES * L::A_BYTES, &map_a, &full_bar[s], k0, t0);
+        } else {
+          tma_load_2d(stage, &map_a, &full_bar[s], k0, t0);
+          uint8_t* b_tile = stage + L::A_BYTES;
+          if (MODE == 1) {  // map_w's box has BN/2 rows: gate rows, then the matching up rows
+            tma_load_2d(b_tile, &map_w, &full_bar[s], k0, f0);
+            tma_load_2d(b_tile + L::B_BYTES / 2, &map_w, &full_bar[s], k0, up_row_offset + f0);
+          } else {
+            tma_load_2d(b_tile, &map_w, &full_bar[s], k0, f0);
+          }
+        }
         armed = i + 1;
       }
       if (*abort_flag) {
@@ -246,7 +264,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
           const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);
           umma_bf16(tmem_base, desc_a + koff, desc_b + koff, idesc, acc);
-          if (MODE == 1) {
+          if (MODE == 1 && ORIENT == 0) {
             const uint64_t desc_up = smem_desc_sw128(a_addr + L::A_BYTES);
             umma_bf16(tmem_base + BN, desc_up + koff, desc_b + koff, idesc, acc);
           }
@@ -258,7 +276,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5)
     const int quad = warp & 3;  // tensor-memory lanes 32 * quad .. + 31 belong to this warp
-    const int f = f0 + quad * 32 + lane;
     bool ok = mbar_wait(tmem_full_bar, 0, abort_flag);
     if (!ok) {
       *abort_flag = 1;
@@ -270,26 +287,80 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
       float* out_f32 = reinterpret_cast<float*>(out) + (long long)blockIdx.z * partial_stride;
       __nv_bfloat16* out_bf16 = reinterpret_cast<__nv_bfloat16*>(out) + (long long)blockIdx.z * partial_stride;
+      if (ORIENT == 0) {
+        const int f = f0 + quad * 32 + lane;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        if (t0 + c0 >= n_tokens) break;  // uniform across the warp
-        uint32_t g[16], u[16];
-        if (n_kb > 0) {
-          tmem_load16(lane_base + c0, g);
-          if (MODE == 1) tmem_load16(lane_base + BN + c0, u);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        } else {
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          if (t0 + c0 >= n_tokens) break;  // uniform across the warp
+          uint32_t g[16], u[16];
+          if (n_kb > 0) {
+            tmem_load16(lane_base + c0, g);
+            if (MODE == 1) tmem_load16(lane_base + BN + c0, u);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) g[j] = u[j] = 0u;
+            for (int j = 0; j < 16; ++j) g[j] = u[j] = 0u;
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int t = t0 + c0 + j;
+            if (t < n_tokens && f < n_features) {
+              float v = __uint_as_float(g[j]);
+              if (MODE == 1) v = v / (1.0f + expf(-v)) * __uint_as_float(u[j]);
+              if (out_is_f32) out_f32[(long long)t * ld_out + f] = v;
+              else out_bf16[(long long)t * ld_out + f] = __float2bfloat16_rn(v);
+            }
+          }
         }
+      } else {
+        const int t = t0 + quad * 32 + lane;
+        const bool vec_ok = out_is_f32 ? (ld_out % 4 == 0 && (reinterpret_cast<uintptr_t>(out_f32) & 15) == 0)
+                                       : (ld_out % 8 == 0 && (reinterpret_cast<uintptr_t>(out_bf16) & 15) == 0);
+#pragma unroll 1
+        for (int c0 = 0; c0 < F_TILE; c0 += 16) {
+          if (f0 + c0 >= n_features) break;  // uniform across the block
+          uint32_t g[16], u[16];
+          if (n_kb > 0) {
+            tmem_load16(lane_base + c0, g);
+            if (MODE == 1) tmem_load16(lane_base + BN / 2 + c0, u);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          } else {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int t = t0 + c0 + j;
-          if (t < n_tokens && f < n_features) {
-            float v = __uint_as_float(g[j]);
-            if (MODE == 1) v = v / (1.0f + expf(-v)) * __uint_as_float(u[j]);
-            if (out_is_f32) out_f32[(long long)t * ld_out + f] = v;
-            else out_bf16[(long long)t * ld_out + f] = __float2bfloat16_rn(v);
+            for (int j = 0; j < 16; ++j) g[j] = u[j] = 0u;
+          }
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            v[j] = __uint_as_float(g[j]);
+            if (MODE == 1) v[j] = v[j] / (1.0f + expf(-v[j])) * __uint_as_float(u[j]);
+          }
+          if (t >= n_tokens) continue;
+          const int f = f0 + c0;
+          const long long at = (long long)t * ld_out + f;
+          if (vec_ok && f + 16 <= n_features) {
+            if (out_is_f32) {
+              float4* dst = reinterpret_cast<float4*>(out_f32 + at);
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) dst[q4] = make_float4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
+            } else {
+              uint32_t pk[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                pk[j] = *reinterpret_cast<uint32_t*>(&b);
+              }
+              uint4* dst = reinterpret_cast<uint4*>(out_bf16 + at);
+              dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+              dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (f + j < n_features) {
+                if (out_is_f32) out_f32[at + j] = v[j];
+                else out_bf16[at + j] = __float2bfloat16_rn(v[j]);
+              }
+            }
           }
         }
       }
@@ -321,13 +392,13 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-template <int BN, int MODE>
+template <int BN, int MODE, int ORIENT>
 int launch(const CUtensorMap* map_w, const CUtensorMap* map_a, void* out, int out_is_f32, int n_tokens,
            int n_features, int K, long long ld_out, long long partial_stride, int splits, int up_row_offset,
            int* error_word, cudaStream_t stream) {
-  using L = Layout<BN, MODE>;
+  using L = Layout<BN, MODE, ORIENT>;
   static bool configured = false;
-  auto kern = gemm_tcgen05_kernel<BN, MODE>;
+  auto kern = gemm_tcgen05_kernel<BN, MODE, ORIENT>;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES) != cudaSuccess)
       return launch_status();
@@ -335,7 +406,9 @@ int launch(const CUtensorMap* map_w, const CUtensorMap* map_a, void* out, int ou
   }
   const int k_blocks = (K + BK - 1) / BK;
   const int per_split = (k_blocks + splits - 1) / splits;
-  dim3 grid((n_features + BM - 1) / BM, (n_tokens + BN - 1) / BN, splits);
+  constexpr int F_TILE = ORIENT == 0 ? BM : (MODE == 1 ? BN / 2 : BN);
+  constexpr int T_TILE = ORIENT == 0 ? BN : BM;
+  dim3 grid((n_features + F_TILE - 1) / F_TILE, (n_tokens + T_TILE - 1) / T_TILE, splits);
   kern<<<grid, NUM_THREADS, L::SMEM_BYTES, stream>>>(*map_w, *map_a, out, out_is_f32, n_tokens, n_features,
                                                       k_blocks, per_split, ld_out, partial_stride,
                                                       up_row_offset, error_word);
@@ -366,10 +439,13 @@ extern "C" int llm_gemm_tensor_map(void* map_out, const void* base, long long ro
 
 // out[z][t, f] (z < splits) = partial sums of act[t, :] . w[f, :]; mode 1: silu(gate) * up with
 // w = [gate; up], the up rows starting at `up_row_offset` (splits must be 1 then).
-// `bn` is the token tile (16, 32, 64, 128, 256); map_a's box must have bn rows, map_w's 128.
+// orient 0: `bn` is the token tile (16, 32, 64, 128, 256); map_a's box must have bn rows, map_w's 128.
+// orient 1: `bn` is the feature tile (128 or 256); map_a's box must have 128 rows, map_w's bn rows
+// (bn / 2 in mode 1).
 extern "C" int llm_gemm_bf16(const void* map_w, const void* map_a, void* out, int out_dtype, int n_tokens,
                              int n_features, int K, long long ld_out, long long partial_stride, int splits,
-                             int bn, int mode, int up_row_offset, int* error_word, cudaStream_t stream) {
+                             int bn, int mode, int orient, int up_row_offset, int* error_word,
+                             cudaStream_t stream) {
   if (n_tokens <= 0 || n_features <= 0) return 0;
   if (K <= 0 || splits <= 0 || (mode == 1 && splits != 1)) return ERR_BAD_SIZE;
   if (splits > 1 && out_dtype != DT_F32) return ERR_BAD_DTYPE;
@@ -380,20 +456,27 @@ extern "C" int llm_gemm_bf16(const void* map_w, const void* map_a, void* out, in
   const CUtensorMap* mw = &mw_copy;
   const CUtensorMap* ma = &ma_copy;
   const int f32 = out_dtype == DT_F32;
-#define GEMM_CASE(BN_)                                                                                   \
-  case BN_:                                                                                              \
-    return mode == 1 ? launch<BN_, 1>(mw, ma, out, f32, n_tokens, n_features, K, ld_out, partial_stride, \
-                                      splits, up_row_offset, error_word, stream)                         \
-                     : launch<BN_, 0>(mw, ma, out, f32, n_tokens, n_features, K, ld_out, partial_stride, \
-                                      splits, up_row_offset, error_word, stream)
-  switch (bn) {
-    GEMM_CASE(16);
-    GEMM_CASE(32);
-    GEMM_CASE(64);
-    GEMM_CASE(128);
-    GEMM_CASE(256);
-    default:
-      return ERR_BAD_SIZE;
+#define GEMM_CASE(BN_, ORIENT_)                                                                              \
+  return mode == 1 ? launch<BN_, 1, ORIENT_>(mw, ma, out, f32, n_tokens, n_features, K, ld_out, partial_stride, \
+                                             splits, up_row_offset, error_word, stream)                         \
+                   : launch<BN_, 0, ORIENT_>(mw, ma, out, f32, n_tokens, n_features, K, ld_out, partial_stride, \
+                                             splits, up_row_offset, error_word, stream)
+  if (orient == 0) {
+    switch (bn) {
+      case 16: GEMM_CASE(16, 0);
+      case 32: GEMM_CASE(32, 0);
+      case 64: GEMM_CASE(64, 0);
+      case 128: GEMM_CASE(128, 0);
+      case 256: GEMM_CASE(256, 0);
+      default: return ERR_BAD_SIZE;
+    }
+  } else if (orient == 1) {
+    switch (bn) {
+      case 128: GEMM_CASE(128, 1);
+      case 256: GEMM_CASE(256, 1);
+      default: return ERR_BAD_SIZE;
+    }
   }
+  return ERR_BAD_SIZE;
 #undef GEMM_CASE
 }

@@ -27,7 +27,7 @@ def lib():
         P, I, L = c_void_p, c_int, c_longlong
         l.llm_gemm_tensor_map.argtypes = [P, P, L, L, L, I]
         l.llm_gemm_tensor_map.restype = c_int
-        l.llm_gemm_bf16.argtypes = [P, P, P, I, I, I, I, L, L, I, I, I, I, P, P]
+        l.llm_gemm_bf16.argtypes = [P, P, P, I, I, I, I, L, L, I, I, I, I, I, P, P]
         l.llm_gemm_bf16.restype = c_int
         _lib = l
     return _lib
@@ -70,10 +70,19 @@ class GemmPlan:
     def __init__(self, weight: torch.Tensor):
         self.weight = weight
         self.n, self.k = weight.shape
-        self.map_w = tensor_map(weight.data_ptr(), self.n, self.k, self.k, BM)
+        self.weight_maps: Dict[int, ctypes.Array] = {}
+        self.map_w = self.weight_map(BM)
         self.act_maps: Dict[Tuple[int, int, int], ctypes.Array] = {}
 
+    def weight_map(self, box_rows: int) -> ctypes.Array:
+        m = self.weight_maps.get(box_rows)
+        if m is None:
+            m = tensor_map(self.weight.data_ptr(), self.n, self.k, self.k, box_rows)
+            self.weight_maps[box_rows] = m
+        return m
+
     def act_map(self, a: torch.Tensor, bn: int) -> ctypes.Array:
+        """`bn`: rows of the box (the token tile)."""
         key = (a.data_ptr(), bn, a.stride(0))
         m = self.act_maps.get(key)
         if m is None:
@@ -112,14 +121,41 @@ def choose_splits(rows: int, n: int, k: int, bn: int) -> int:
     return -(-k_blocks // per)
 
 
+TOKENS_ON_ROWS_ABOVE = 256    # steps with more rows put 128 tokens on the MMA rows (orientation 1)
+N_SMS = 148
+
+
+def feature_tile(rows: int, n_out: int, swiglu: bool) -> int:
+    """Orientation 1: 256 or 128 weight rows per tile, whichever needs less time over whole waves
+    of thread blocks (a 128-wide tile costs a little more than half of a 256-wide one)."""
+    best, best_cost = 256, None
+    for bn, cost in ((256, 1.0), (128, 0.58)):
+        out_per_tile = bn // 2 if swiglu else bn
+        tiles = -(-rows // BM) * -(-n_out // out_per_tile)
+        total = -(-tiles // N_SMS) * cost
+        if best_cost is None or total < best_cost:
+            best, best_cost = bn, total
+    return best
+
+
 def run(ctx, plan: GemmPlan, a: torch.Tensor, rows: int, out_dtype: torch.dtype, buffer: str,
         allow_partials: bool, swiglu: bool) -> Partials:
     if a.dtype != torch.bfloat16 or a.stride(-1) != 1 or a.shape[-1] != plan.k or a.data_ptr() % 16 or a.stride(0) % 8:
         raise KernelLaunchError(f"gemm_tcgen05: activations {tuple(a.shape)} {a.dtype} do not fit weight "
                                 f"[{plan.n}, {plan.k}]")
-    bn = token_tile(rows)
     err = error_word(a.device)
     l = lib()
+    code = DT_BF16 if out_dtype == torch.bfloat16 else DT_F32
+    if rows > TOKENS_ON_ROWS_ABOVE:
+        n_out = plan.n // 2 if swiglu else plan.n
+        bn = feature_tile(rows, n_out, swiglu)
+        out = ctx.ws.get(buffer, (rows, n_out), out_dtype)
+        _check(l.llm_gemm_bf16(ctypes.addressof(plan.weight_map(bn // 2 if swiglu else bn)),
+                               ctypes.addressof(plan.act_map(a, BM)), out.data_ptr(), code, rows, n_out, plan.k,
+                               out.stride(0), 0, 1, bn, 1 if swiglu else 0, 1, n_out if swiglu else 0,
+                               err.data_ptr(), ctx.stream), "gemm_tcgen05 (tokens on rows)")
+        return Partials(out)
+    bn = token_tile(rows)
     if swiglu:
         inter = plan.n // 2
         tiles = -(-inter // BM) * -(-rows // bn)
@@ -127,7 +163,7 @@ def run(ctx, plan: GemmPlan, a: torch.Tensor, rows: int, out_dtype: torch.dtype,
             out = ctx.ws.get(buffer, (rows, inter), out_dtype)
             _check(l.llm_gemm_bf16(ctypes.addressof(plan.map_w), ctypes.addressof(plan.act_map(a, bn)),
                                    out.data_ptr(), DT_BF16 if out_dtype == torch.bfloat16 else DT_F32, rows,
-                                   inter, plan.k, out.stride(0), 0, 1, bn, 1, inter, err.data_ptr(), ctx.stream),
+                                   inter, plan.k, out.stride(0), 0, 1, bn, 1, 0, inter, err.data_ptr(), ctx.stream),
                    "gemm_tcgen05 (swiglu)")
             return Partials(out)
         # few tiles: stream [gate; up] as one product split over K, then reduce inside SwiGLU
@@ -145,6 +181,6 @@ def run(ctx, plan: GemmPlan, a: torch.Tensor, rows: int, out_dtype: torch.dtype,
         stride = 0
     _check(l.llm_gemm_bf16(ctypes.addressof(plan.map_w), ctypes.addressof(plan.act_map(a, bn)), out.data_ptr(),
                            DT_BF16 if out_dtype == torch.bfloat16 else DT_F32, rows, plan.n, plan.k,
-                           out.stride(-2), stride, splits, bn, 0, 0, err.data_ptr(), ctx.stream),
+                           out.stride(-2), stride, splits, bn, 0, 0, 0, err.data_ptr(), ctx.stream),
            "gemm_tcgen05")
     return Partials(out, splits)

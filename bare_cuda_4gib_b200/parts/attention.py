@@ -74,7 +74,9 @@ class Attention(Part):
     def forward(self, ctx, call, h: torch.Tensor) -> K.Partials:
         n = ctx.n_tokens
         qd = self.heads * self.head_dim
-        qkv = self.qkv.forward(ctx, h, n, ctx.dtype, "qkv", allow_partials=True)
+        # few rows: float32 partial results let the product split its inner dimension over more SMs
+        qkv_dtype = torch.float32 if n <= 256 else ctx.dtype
+        qkv = self.qkv.forward(ctx, h, n, qkv_dtype, "qkv", allow_partials=True)
         q = ctx.ws.get("q", (n, qd), ctx.dtype)
         inv_freq = self.position.fused_rotation()
         K.rope_cache_write(qkv, q, call.cache, ctx.positions, ctx.row_seq, inv_freq, self.heads,

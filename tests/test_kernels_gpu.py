@@ -215,7 +215,8 @@ def test_sample_rows_matches_inverse_cdf_walk():
 # ------------------------------------------------------------------------------ tcgen05 GEMM
 
 GEMM_SHAPES = [(1, 2560, 2048), (7, 96, 96), (16, 300, 176), (17, 128, 64), (33, 1000, 128),
-               (64, 2048, 5632), (100, 512, 256), (200, 640, 320), (257, 384, 192), (700, 256, 512)]
+               (64, 2048, 5632), (100, 512, 256), (200, 640, 320), (257, 384, 192), (700, 256, 512),
+               (300, 1000, 96), (1000, 2560, 264), (513, 130, 176), (2048, 2048, 512)]
 
 
 @pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
@@ -239,7 +240,8 @@ def test_gemm_tcgen05(m, n, k, out_dtype):
         _close(got, want, 2 ** -8, 1e-4 * math.sqrt(k))
 
 
-@pytest.mark.parametrize("m,inter,k", [(3, 176, 64), (40, 5632, 256), (130, 256, 96), (300, 200, 128), (9, 2816, 512)])
+@pytest.mark.parametrize("m,inter,k", [(3, 176, 64), (40, 5632, 256), (130, 256, 96), (300, 200, 128), (9, 2816, 512),
+                                       (700, 176, 64), (2048, 5632, 128), (257, 1000, 96)])
 def test_gemm_tcgen05_swiglu(m, inter, k):
     from bare_cuda_4gib_b200.kernels import gemm
     torch.manual_seed(m)
