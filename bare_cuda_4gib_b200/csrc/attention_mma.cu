@@ -14,8 +14,10 @@
 //   WARPS_M = 1, WARPS_N = 4: 16 rows, each warp 16 of the 64 keys of a block (decode); the
 //   warps' partial softmax states are merged through shared memory.
 // gridDim.z > 1 splits a tile's key blocks over several thread blocks; each writes a
-// normalised partial output and its log-sum-exp to scratch memory and `attention_combine`
-// merges them.  Softmax runs in base 2: scores are multiplied by scale * log2(e).
+// normalised partial output and its log-sum-exp to scratch memory and counts itself done; the
+// block that counts last merges the tile's partial results in split order (so the sum does not
+// depend on which block that is) and sets the counter back to zero.  No block waits for another.
+// Softmax runs in base 2: scores are multiplied by scale * log2(e).
 //
 // HEAD_DIM is a compile-time constant (-DHEAD_DIM=64): a multiple of 16 up to 128.
 
@@ -79,6 +81,7 @@ struct AttnArgs {
   const int32_t* tile_index;   // per tile: which BM-row tile of the sequence's packed rows
   float* part_o;               // scratch for split keys: [tile][kv head][split][BM][D], normalised
   float* part_lse;             // [tile][kv head][split][BM], base-2 log-sum-exp (-inf: no keys)
+  int* counters;               // [tile][kv head]: splits done; zero before and after every launch
   int q_heads;
   float scale_log2;
   int window;                  // <= 0: every key
@@ -315,34 +318,34 @@ attention_mma_kernel(AttnArgs a) {
       if (c == 0) a.part_lse[item * BM + r] = L > 0.0f ? M + log2f(L) : -INFINITY;
     }
   }
-}
+  if (n_splits == 1) return;
 
-// Merges the partial outputs of a tile's key splits: out = sum_z w_z o_z / sum_z w_z with
-// w_z = 2^(lse_z - max lse).  One thread block per (tile, kv head).
-template <int BM>
-__global__ void attention_combine_kernel(AttnArgs a, int n_splits) {
-  const int tile = blockIdx.x, kvh = blockIdx.y;
-  const int seq = a.tile_seq[tile];
-  if (seq < 0) return;
-  const int group = a.q_heads / a.cache.kv_heads;
-  const int q_start = a.seq_q_start[seq], n_rows = a.seq_q_len[seq] * group;
-  const int row0 = a.tile_index[tile] * BM;
+  // ---- the last block of this tile to get here merges the splits
+  __shared__ int is_last;
+  __threadfence();
+  __syncthreads();
+  int* counter = a.counters + (long long)tile * gridDim.y + kvh;
+  if (threadIdx.x == 0) is_last = atomicAdd(counter, 1) == n_splits - 1;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
   const long long item0 = ((long long)tile * gridDim.y + kvh) * n_splits;
-  for (int i = threadIdx.x; i < BM * CHUNKS; i += blockDim.x) {
+  for (int i = threadIdx.x; i < BM * CHUNKS; i += NT_THREADS) {
     const int r = i / CHUNKS, c = i % CHUNKS;
     const int R = row0 + r;
     if (R >= n_rows) continue;
     float M = -INFINITY;
-    for (int z = 0; z < n_splits; ++z) M = fmaxf(M, a.part_lse[(item0 + z) * BM + r]);
+    for (int z = 0; z < n_splits; ++z) M = fmaxf(M, __ldcg(a.part_lse + (item0 + z) * BM + r));
     float W = 0.0f, acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (M != -INFINITY) {
       for (int z = 0; z < n_splits; ++z) {
-        const float w = exp2f(a.part_lse[(item0 + z) * BM + r] - M);
+        const float w = exp2f(__ldcg(a.part_lse + (item0 + z) * BM + r) - M);
         if (w == 0.0f) continue;
         W += w;
-        const float* src = a.part_o + ((item0 + z) * BM + r) * D + c * 8;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] += w * src[e];
+        const float4* src = reinterpret_cast<const float4*>(a.part_o + ((item0 + z) * BM + r) * D + c * 8);
+        const float4 lo = __ldcg(src), hi = __ldcg(src + 1);
+        acc[0] += w * lo.x; acc[1] += w * lo.y; acc[2] += w * lo.z; acc[3] += w * lo.w;
+        acc[4] += w * hi.x; acc[5] += w * hi.y; acc[6] += w * hi.z; acc[7] += w * hi.w;
       }
     }
     const float inv = W > 0.0f ? 1.0f / W : 0.0f;
@@ -354,6 +357,7 @@ __global__ void attention_combine_kernel(AttnArgs a, int n_splits) {
     packed.w = pack_bf16(acc[6] * inv, acc[7] * inv);
     *reinterpret_cast<uint4*>(a.out + ((long long)(q_start + token) * a.q_heads + head) * D + c * 8) = packed;
   }
+  if (threadIdx.x == 0) *counter = 0;
 }
 
 template <int WARPS_M, int WARPS_N>
@@ -377,10 +381,6 @@ int launch(const AttnArgs& a, int n_tiles, int kv_heads, int n_splits, cudaStrea
   }
   dim3 grid(n_tiles, kv_heads, n_splits);
   kern<<<grid, WARPS_M * WARPS_N * 32, smem, stream>>>(a);
-  if (n_splits > 1) {
-    dim3 cgrid(n_tiles, kv_heads);
-    attention_combine_kernel<16 * WARPS_M><<<cgrid, 128, 0, stream>>>(a, n_splits);
-  }
   return launch_status();
 }
 
@@ -388,13 +388,17 @@ int launch(const AttnArgs& a, int n_tiles, int kv_heads, int n_splits, cudaStrea
 
 extern "C" int llm_attention_head_dim() { return D; }
 
-// Floats of scratch that `n_tiles` tiles of `rows_per_tile` rows need when split `n_splits` ways:
-// partial outputs, then their log-sum-exps.
+// 32-bit words of scratch that `n_tiles` tiles of `rows_per_tile` rows need when split `n_splits`
+// ways: LLM_ATTENTION_COUNTER_WORDS counters (one per tile and kv head; they must be zero before
+// the first launch and every launch leaves them zero), then partial outputs, then their
+// log-sum-exps.
+#define LLM_ATTENTION_COUNTER_WORDS 4096
 extern "C" long long llm_attention_scratch_floats(int n_tiles, int kv_heads, int n_splits, int rows_per_tile) {
-  return (long long)n_tiles * kv_heads * n_splits * rows_per_tile * (D + 1);
+  return LLM_ATTENTION_COUNTER_WORDS + (long long)n_tiles * kv_heads * n_splits * rows_per_tile * (D + 1);
 }
 
-// rows_per_tile: 64 (prefill shape) or 16 (decode shape).  `scratch` is needed when n_splits > 1.
+// rows_per_tile: 64 (prefill shape) or 16 (decode shape).  `scratch` (llm_attention_scratch_floats
+// words, its first LLM_ATTENTION_COUNTER_WORDS zero) is needed when n_splits > 1.
 extern "C" int llm_attention_mma(const void* q, void* out, void* k_base, void* v_base, const int32_t* block_table,
                                  long long page_stride, int table_stride, int page_tokens, int kv_heads,
                                  int head_dim, const int32_t* seq_q_start, const int32_t* seq_q_len,
@@ -404,6 +408,7 @@ extern "C" int llm_attention_mma(const void* q, void* out, void* k_base, void* v
   if (n_tiles <= 0) return 0;
   if (head_dim != D || q_heads % kv_heads || n_splits < 1 || n_splits > 65535 || kv_heads > 65535) return ERR_BAD_SIZE;
   if (n_splits > 1 && !scratch) return ERR_BAD_SIZE;
+  if (n_splits > 1 && (long long)n_tiles * kv_heads > LLM_ATTENTION_COUNTER_WORDS) return ERR_BAD_SIZE;
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(k_base) |
        reinterpret_cast<uintptr_t>(v_base)) & 15)
     return ERR_BAD_ALIGN;
@@ -416,8 +421,9 @@ extern "C" int llm_attention_mma(const void* q, void* out, void* k_base, void* v
   a.seq_kv_len = seq_kv_len;
   a.tile_seq = tile_seq;
   a.tile_index = tile_index;
-  a.part_o = scratch;
-  a.part_lse = scratch ? scratch + (long long)n_tiles * kv_heads * n_splits * rows_per_tile * D : nullptr;
+  a.counters = reinterpret_cast<int*>(scratch);
+  a.part_o = scratch ? scratch + LLM_ATTENTION_COUNTER_WORDS : nullptr;
+  a.part_lse = scratch ? a.part_o + (long long)n_tiles * kv_heads * n_splits * rows_per_tile * D : nullptr;
   a.q_heads = q_heads;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.window = window;

@@ -16,16 +16,19 @@
 //   * The array holds LLM_ATTENTION_STATIC_SCRATCH_FLOATS floats (4 MiB).  Every GPU on which the
 //     library is loaded keeps that much memory until the process exits, used or not, and each
 //     head-size build of the library has an array of its own.
-//   * A call needs n_tiles * kv_heads * n_splits * rows_per_tile * (head_dim + 1) floats
+//   * A call needs 4096 + n_tiles * kv_heads * n_splits * rows_per_tile * (head_dim + 1) words
 //     (llm_attention_scratch_floats).  If that is more than the array holds, the call launches
 //     nothing and returns LLM_ERR_STATIC_SCRATCH_TOO_SMALL: use fewer splits, or the ordinary
 //     entry point.  With n_splits == 1 no scratch is used and any size is accepted.
 //   * All calls share the one array.  Two calls whose kernels can overlap on the GPU (different
 //     streams, or several host threads) race on it and give wrong results: keep calls that use
-//     it on one stream, or order them yourself.  The array keeps whatever the last call wrote;
-//     nothing in it has to start at zero, because every entry a call reads was written by the same
-//     call before (each split writes its whole partial output and its log-sum-exp, and only then
-//     does the merge kernel of that call read them).
+//     it on one stream, or order them yourself.  The array keeps whatever the last call wrote.
+//     Only its first 4096 words have to be zero when a call starts: they count, per tile, the
+//     splits that have finished.  They are zero when the library is loaded, and the thread block
+//     that merges a tile sets that tile's counter back to zero, so a call that ran to its end
+//     leaves them zero for the next one.  Everything else a call reads was written by the same
+//     call before (each split writes its whole partial output and its log-sum-exp before it counts
+//     itself done).
 //
 // Set-up.  The first call on each device looks up the array's device address
 // (cudaGetSymbolAddress, with that device current) and remembers it; this makes the first call

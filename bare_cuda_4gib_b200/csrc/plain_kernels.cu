@@ -51,6 +51,8 @@ extern "C" int llm_embed_gather(const void* table, int table_dtype, const int32_
 // One block per output row.  If `delta` is given, residual[row] += sum over `n_partials` partial
 // results (added in index order) before the norm; the updated residual is written back.
 // `row_index` (optional, distinct entries) picks which residual row each output row works on.
+// Each element's sum and the order of the row's sum of squares depend on the block size only,
+// which the launcher picks from `hidden`, never from the number of rows.
 template <typename TD, typename TW, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
                                    int n_partials, long long partial_stride,
@@ -77,6 +79,60 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
     TO* dst = out + (long long)r * hidden;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x)
       dst[i] = from_float<TO>(row_cache[i] * scale * to_float(weight[i]));
+  }
+}
+
+// The same with 16-byte accesses: float32 delta, bfloat16 weight and output, hidden a multiple of 4.
+// A thread keeps its elements in registers (at most 4 float4: hidden <= 16 * blockDim.x).
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const float* __restrict__ delta,
+                                       int n_partials, long long partial_stride,
+                                       const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ out,
+                                       const int32_t* __restrict__ row_index, int hidden, float eps) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const long long src = row_index ? row_index[r] : r;
+  float4* x = reinterpret_cast<float4*>(residual + src * hidden);
+  const int n4 = hidden / 4;
+  float4 v[4];
+  float sq = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    if (i < n4) {
+      float4 a = x[i];
+      if (delta) {
+        for (int p = 0; p < n_partials; ++p) {
+          const float4 d = reinterpret_cast<const float4*>(delta + p * partial_stride + src * hidden)[i];
+          a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
+        }
+        x[i] = a;
+      }
+      v[j] = a;
+      sq += a.x * a.x;
+      sq += a.y * a.y;
+      sq += a.z * a.z;
+      sq += a.w * a.w;
+    }
+  }
+  const float total = block_sum(sq, scratch);
+  const float scale = 1.0f / sqrtf(total / (float)hidden + eps);
+  if (out) {
+    uint2* dst = reinterpret_cast<uint2*>(out + (long long)r * hidden);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < n4) {
+        const uint2 wraw = reinterpret_cast<const uint2*>(weight)[i];
+        const __nv_bfloat162 w01 = *reinterpret_cast<const __nv_bfloat162*>(&wraw.x);
+        const __nv_bfloat162 w23 = *reinterpret_cast<const __nv_bfloat162*>(&wraw.y);
+        __nv_bfloat162 o01 = __floats2bfloat162_rn(v[j].x * scale * __low2float(w01), v[j].y * scale * __high2float(w01));
+        __nv_bfloat162 o23 = __floats2bfloat162_rn(v[j].z * scale * __low2float(w23), v[j].w * scale * __high2float(w23));
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&o01);
+        o.y = *reinterpret_cast<uint32_t*>(&o23);
+        dst[i] = o;
+      }
+    }
   }
 }
 
@@ -107,6 +163,21 @@ extern "C" int llm_add_rmsnorm(float* residual, const void* delta, int delta_dty
                                void* out, int out_dtype, const int32_t* row_index, int rows,
                                int hidden, float eps, cudaStream_t stream) {
   if (rows <= 0) return 0;
+  // the bfloat16 path's common case: vector accesses, block size from the width alone
+  const auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (delta_dtype == DT_F32 && weight_dtype == DT_BF16 && (out == nullptr || out_dtype == DT_BF16) &&
+      hidden % 4 == 0 && hidden <= 16 * 1024 && aligned16(residual) && aligned16(delta) &&
+      (partial_stride % 4 == 0) && (reinterpret_cast<uintptr_t>(weight) & 7) == 0 &&
+      (reinterpret_cast<uintptr_t>(out) & 7) == 0) {
+    const int n4 = hidden / 4;
+    int threads = 128;
+    while (threads < 1024 && threads * 2 <= n4) threads *= 2;   // <= 2 float4 per thread when wide
+    while (threads * 4 < n4) threads *= 2;
+    add_rmsnorm_vec_kernel<<<rows, threads, 0, stream>>>(residual, (const float*)delta, n_partials,
+                                                          partial_stride, (const __nv_bfloat16*)weight,
+                                                          (__nv_bfloat16*)out, row_index, hidden, eps);
+    return launch_status();
+  }
   if (delta_dtype == DT_F32 && weight_dtype == DT_F32)
     return add_rmsnorm_out<float, float>(residual, delta, n_partials, partial_stride, weight, out,
                                          out_dtype, row_index, rows, hidden, eps, stream);
@@ -213,62 +284,53 @@ extern "C" int llm_matmul_plain(const void* a, int a_dtype, const void* w, int w
 
 // ------------------------------------------------------------- rotation + cache write
 
-// One block per token.  Reads the token's fused projection row [q heads | k heads | v heads]
-// (optionally as a sum of partial results), rotates q and k by the token's position and writes q
-// to q_out and k, v into the request's cache pages.  The angle is float(pos) * inv_freq[p], a
+// One warp per (token, head) of the token's fused projection row [q heads | k heads | v heads]
+// (optionally a sum of partial results): q and k heads are rotated by the token's position, q goes
+// to q_out, k and v into the request's cache pages.  The angle is float(pos) * inv_freq[p], a
 // float32 product; sin and cos are the precise functions.  inv_freq == nullptr means no rotation.
+constexpr int ROPE_HEADS_PER_BLOCK = 4;
+
 template <typename TI, typename TO>
-__global__ void rope_cache_write_kernel(const TI* __restrict__ qkv, int n_partials,
-                                        long long partial_stride, TO* __restrict__ q_out,
-                                        PagedCache cache, const int32_t* __restrict__ positions,
-                                        const int32_t* __restrict__ row_seq,
-                                        const float* __restrict__ inv_freq, int q_heads,
-                                        int write_cache) {
+__global__ void __launch_bounds__(ROPE_HEADS_PER_BLOCK * 32)
+rope_cache_write_kernel(const TI* __restrict__ qkv, int n_partials, long long partial_stride,
+                        TO* __restrict__ q_out, PagedCache cache, const int32_t* __restrict__ positions,
+                        const int32_t* __restrict__ row_seq, const float* __restrict__ inv_freq, int q_heads,
+                        int write_cache) {
   const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int h = blockIdx.y * ROPE_HEADS_PER_BLOCK + (threadIdx.x >> 5);
   const int d = cache.head_dim, half = d / 2;
   const int kvh_n = cache.kv_heads;
-  const int width = (q_heads + 2 * kvh_n) * d;
+  const int n_heads = q_heads + 2 * kvh_n;
+  if (h >= n_heads || (h >= q_heads && !write_cache)) return;
   const int pos = positions[t];
-  const int slot = row_seq[t];
-  const TI* row = qkv + (long long)t * width;
-  TO* kc = (TO*)cache.k;
-  TO* vc = (TO*)cache.v;
-
+  const TI* row = qkv + (long long)t * n_heads * d + (long long)h * d;
   auto load = [&](int i) {
     float v = 0.0f;
     for (int p = 0; p < n_partials; ++p) v += to_float(row[p * partial_stride + i]);
     return v;
   };
-
-  // rotated heads: q heads then k heads, one thread per (head, pair)
-  const int rot_heads = q_heads + (write_cache ? kvh_n : 0);
-  for (int i = threadIdx.x; i < rot_heads * half; i += blockDim.x) {
-    const int h = i / half, p = i % half;
-    const float lo = load(h * d + p), hi = load(h * d + p + half);
-    float c = 1.0f, s = 0.0f;
-    if (inv_freq) {
-      const float angle = (float)pos * inv_freq[p];
-      sincosf(angle, &s, &c);
-    }
-    const float lo2 = lo * c - hi * s, hi2 = hi * c + lo * s;
+  if (h < q_heads + kvh_n) {  // rotated: a q head or a k head
+    TO* dst;
     if (h < q_heads) {
-      TO* dst = q_out + ((long long)t * q_heads + h) * d;
-      dst[p] = from_float<TO>(lo2);
-      dst[p + half] = from_float<TO>(hi2);
+      dst = q_out + ((long long)t * q_heads + h) * d;
     } else {
-      const long long off = cache_offset(cache, slot, pos, h - q_heads);
-      if (off >= 0) {
-        kc[off + p] = from_float<TO>(lo2);
-        kc[off + p + half] = from_float<TO>(hi2);
-      }
+      const long long off = cache_offset(cache, row_seq[t], pos, h - q_heads);
+      if (off < 0) return;
+      dst = (TO*)cache.k + off;
     }
-  }
-  if (write_cache) {
-    const int v0 = (q_heads + kvh_n) * d;
-    for (int i = threadIdx.x; i < kvh_n * d; i += blockDim.x) {
-      const long long off = cache_offset(cache, slot, pos, i / d);
-      if (off >= 0) vc[off + i % d] = from_float<TO>(load(v0 + i));
+    for (int p = lane; p < half; p += 32) {
+      const float lo = load(p), hi = load(p + half);
+      float c = 1.0f, s = 0.0f;
+      if (inv_freq) sincosf((float)pos * inv_freq[p], &s, &c);
+      dst[p] = from_float<TO>(lo * c - hi * s);
+      dst[p + half] = from_float<TO>(hi * c + lo * s);
     }
+  } else {
+    const long long off = cache_offset(cache, row_seq[t], pos, h - q_heads - kvh_n);
+    if (off < 0) return;
+    TO* dst = (TO*)cache.v + off;
+    for (int i = lane; i < d; i += 32) dst[i] = from_float<TO>(load(i));
   }
 }
 
@@ -282,8 +344,11 @@ extern "C" int llm_rope_cache_write(const void* qkv, int in_dtype, int n_partial
   if (n_tokens <= 0) return 0;
   if (head_dim % 2) return ERR_BAD_SIZE;
   PagedCache c{k_base, v_base, block_table, page_stride, table_stride, page_tokens, kv_heads, head_dim};
+  const int n_heads = q_heads + 2 * kv_heads;
+  dim3 grid(n_tokens, (n_heads + ROPE_HEADS_PER_BLOCK - 1) / ROPE_HEADS_PER_BLOCK);
+  if (grid.y > 65535) return ERR_BAD_SIZE;
 #define LAUNCH_ROPE(TI, TO)                                                                   \
-  rope_cache_write_kernel<TI, TO><<<n_tokens, 256, 0, stream>>>(                             \
+  rope_cache_write_kernel<TI, TO><<<grid, ROPE_HEADS_PER_BLOCK * 32, 0, stream>>>(            \
       (const TI*)qkv, n_partials, partial_stride, (TO*)q_out, c, positions, row_seq, inv_freq,  \
       q_heads, write_cache)
   if (in_dtype == DT_F32 && out_dtype == DT_F32) LAUNCH_ROPE(float, float);

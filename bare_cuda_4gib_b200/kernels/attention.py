@@ -14,6 +14,7 @@ from .lib import CacheView, _check
 
 KEY_BLOCK = 64
 TARGET_BLOCKS = 148 * 2
+COUNTER_WORDS = 4096          # per-tile split counters at the start of the scratch (see the kernel)
 _libs: Dict[int, object] = {}
 
 
@@ -60,8 +61,8 @@ class AttentionPlan:
     def scratch(self, ctx, floats: int, device) -> torch.Tensor:
         """Scratch for split keys; a split step has at most TARGET_BLOCKS + tiles * kv_heads items."""
         if self._scratch is None or self._scratch.numel() < floats:
-            most = (TARGET_BLOCKS + (ctx.max_seqs + 8) * self.kv_heads) * 16 * (self.head_dim + 1)
-            self._scratch = torch.empty(max(floats, most), dtype=torch.float32, device=device)
+            most = COUNTER_WORDS + (TARGET_BLOCKS + (ctx.max_seqs + 8) * self.kv_heads) * 16 * (self.head_dim + 1)
+            self._scratch = torch.zeros(max(floats, most), dtype=torch.float32, device=device)   # counters start at zero
         return self._scratch
 
 
@@ -96,6 +97,8 @@ def step_tiles(ctx, plan: AttentionPlan):
     if rows_per_tile == 16:
         key_blocks = -(-ctx.max_kv_len // KEY_BLOCK)
         n_splits = max(1, min(key_blocks, -(-TARGET_BLOCKS // (n_tiles * plan.kv_heads))))
+        if n_tiles * plan.kv_heads > COUNTER_WORDS:
+            n_splits = 1
     out = (dev[:n_tiles], dev[n_tiles: 2 * n_tiles], n_tiles, rows_per_tile, n_splits)
     ctx.extras[key] = out
     return out

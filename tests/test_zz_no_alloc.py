@@ -80,7 +80,7 @@ def test_static_scratch_entry_point_matches_the_ordinary_one_twice():
     for round_, (kv_lens, n_splits) in enumerate([([700, 64, 1, 333], 7), ([90, 1500, 257], 11)]):
         case = _decode_case(10 + round_, kv_lens, heads, kv_heads, d, page)
         floats = lib.llm_attention_scratch_floats(case["n"], kv_heads, n_splits, 16)
-        scratch = torch.empty(floats, dtype=torch.float32, device=DEV)
+        scratch = torch.zeros(floats, dtype=torch.float32, device=DEV)    # its leading counters must be zero
         rc, want = _call(lib, case, heads, kv_heads, d, page, n_splits, static=False, scratch=scratch)
         assert rc == 0
         rc, got = _call(lib, case, heads, kv_heads, d, page, n_splits, static=True)
