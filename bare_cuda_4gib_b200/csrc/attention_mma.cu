@@ -7,7 +7,8 @@
 // packed row R of a request = (token R / group, head R % group).  A thread block owns one tile
 // of BM packed rows of one request and one key/value head, so a key block loaded once serves
 // every head of the group.  Keys are visited in blocks of 64 positions, copied from the
-// request's pages into padded shared memory with cp.async (two stages).
+// request's pages into padded shared memory with cp.async (two stages for the prefill shape, four
+// for the decode shape, whose few rows leave the loads' latency exposed).
 //
 // Two shapes of the same kernel:
 //   WARPS_M = 4, WARPS_N = 1: 64 rows, each warp 16 rows and all 64 keys of a block (prefill);
@@ -96,12 +97,15 @@ attention_mma_kernel(AttnArgs a) {
   constexpr int KEYS_W = BN / WARPS_N;  // keys of a block that one warp handles
   constexpr int NT = KEYS_W / 8;        // score n-tiles per warp
   static_assert(NT % 2 == 0, "a warp handles keys in pairs of n-tiles");
+  constexpr int STAGES = WARPS_N > 1 ? 4 : 2;  // key/value blocks in flight
 
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [BM][LDS]
-  __nv_bfloat16* Ks = Qs + BM * LDS;                                   // [2][BN][LDS]
-  __nv_bfloat16* Vs = Ks + 2 * BN * LDS;                               // [2][BN][LDS]
+  __nv_bfloat16* Ks = Qs + BM * LDS;                                   // [STAGES][BN][LDS]
+  __nv_bfloat16* Vs = Ks + STAGES * BN * LDS;                          // [STAGES][BN][LDS]
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, n_splits = gridDim.z;
   const int seq = a.tile_seq[tile];
   if (seq < 0) return;
@@ -139,10 +143,11 @@ attention_mma_kernel(AttnArgs a) {
 
   const __nv_bfloat16* kc = reinterpret_cast<const __nv_bfloat16*>(a.cache.k);
   const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(a.cache.v);
+  // copies block kb into its stage (nothing if kb is past the end) and closes one cp.async group
   auto load_block = [&](int kb, int stage) {
     __nv_bfloat16* ks = Ks + stage * BN * LDS;
     __nv_bfloat16* vs = Vs + stage * BN * LDS;
-    for (int i = threadIdx.x; i < BN * CHUNKS; i += NT_THREADS) {
+    for (int i = threadIdx.x; kb < kb_end && i < BN * CHUNKS; i += NT_THREADS) {
       const int r = i / CHUNKS, c = i % CHUNKS;
       const int key = kb * BN + r;
       long long off = -1;
@@ -155,7 +160,8 @@ attention_mma_kernel(AttnArgs a) {
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
 
-  if (kb_begin < kb_end) load_block(kb_begin, 0);
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) load_block(kb_begin + st, st);
   __syncthreads();  // Q staged
 
   // ---- Q fragments stay in registers
@@ -177,10 +183,10 @@ attention_mma_kernel(AttnArgs a) {
   for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
 
   for (int kb = kb_begin; kb < kb_end; ++kb) {
-    const int stage = (kb - kb_begin) & 1;
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncthreads();  // block kb has landed; everyone is done with the other stage
-    if (kb + 1 < kb_end) load_block(kb + 1, stage ^ 1);
+    const int stage = (kb - kb_begin) % STAGES;
+    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+    __syncthreads();  // block kb has landed; everyone is done with the stage used one block ago
+    load_block(kb + STAGES - 1, (kb - kb_begin + STAGES - 1) % STAGES);
     const __nv_bfloat16* ks_ = Ks + stage * BN * LDS;
     const __nv_bfloat16* vs_ = Vs + stage * BN * LDS;
     const int key0 = kb * BN + wn * KEYS_W;  // first key this warp scores
@@ -363,7 +369,8 @@ attention_mma_kernel(AttnArgs a) {
 template <int WARPS_M, int WARPS_N>
 constexpr size_t smem_bytes() {
   constexpr int BM = 16 * WARPS_M;
-  constexpr size_t tiles = (size_t)(BM + 4 * BN) * LDS * 2;
+  constexpr int STAGES = WARPS_N > 1 ? 4 : 2;
+  constexpr size_t tiles = (size_t)(BM + 2 * STAGES * BN) * LDS * 2;
   constexpr size_t merge = (size_t)BM * LDS * 2 + (size_t)WARPS_N * BM * (D + 2) * 4;
   return tiles > merge ? tiles : merge;
 }
@@ -380,7 +387,7 @@ int launch(const AttnArgs& a, int n_tiles, int kv_heads, int n_splits, cudaStrea
     configured = true;
   }
   dim3 grid(n_tiles, kv_heads, n_splits);
-  kern<<<grid, WARPS_M * WARPS_N * 32, smem, stream>>>(a);
+  launch_kernel(kern, grid, WARPS_M * WARPS_N * 32, smem, stream, a);
   return launch_status();
 }
 

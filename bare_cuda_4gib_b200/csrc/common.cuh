@@ -7,6 +7,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define DT_F32 0
 #define DT_BF16 1
@@ -20,6 +21,41 @@
 #define ERR_BAD_DTYPE 1
 #define ERR_BAD_SIZE 2
 #define ERR_BAD_ALIGN 3
+
+// Programmatic dependent launch.  Every kernel of the engine is launched with the attribute that
+// lets it start while the kernel before it in the stream is still running.  In return every
+// kernel calls pdl_wait() before it touches global memory that another kernel may have written
+// or may still read (it returns once all earlier kernels have finished and their writes are
+// visible), and pdl_launch_dependents() at its start, which lets the next kernel begin its own
+// preamble.  What runs before pdl_wait() may only touch shared memory, tensor memory, and global
+// memory that no kernel writes (weights).  Set BARE_CUDA_B200_NO_PDL=1 to launch without it.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline bool pdl_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* v = getenv("BARE_CUDA_B200_NO_PDL");
+    enabled = (v && v[0] && v[0] != '0') ? 0 : 1;
+  }
+  return enabled == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 static inline int launch_status() {
   cudaError_t e = cudaGetLastError();

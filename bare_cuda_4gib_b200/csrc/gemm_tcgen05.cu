@@ -179,7 +179,37 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const int kb_end = min(k_blocks, kb_begin + k_blocks_per_split);
   const int n_kb = max(0, kb_end - kb_begin);
 
+  // One stage's loads, in two halves: the weight tiles depend on no other kernel and may be
+  // fetched before pdl_wait(); the activation tile is another kernel's output and may not.
+  // The first half arms the stage's barrier with the bytes of both.
+  auto issue_weights = [&](int i) {
+    const int s = i % L::STAGES;
+    uint8_t* stage = smem + s * L::STAGE_BYTES;
+    mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+    const int k0 = (kb_begin + i) * BK;
+    if (ORIENT == 0) {
+      tma_load_2d(stage, &map_w, &full_bar[s], k0, f0);
+      if (MODE == 1) tma_load_2d(stage + L::A_BYTES, &map_w, &full_bar[s], k0, up_row_offset + f0);
+    } else {
+      uint8_t* b_tile = stage + L::A_BYTES;
+      tma_load_2d(b_tile, &map_w, &full_bar[s], k0, f0);
+      // MODE 1: map_w's box has BN/2 rows: gate rows above, the matching up rows below
+      if (MODE == 1) tma_load_2d(b_tile + L::B_BYTES / 2, &map_w, &full_bar[s], k0, up_row_offset + f0);
+    }
+  };
+  auto issue_activations = [&](int i) {
+    const int s = i % L::STAGES;
+    uint8_t* stage = smem + s * L::STAGE_BYTES;
+    const int k0 = (kb_begin + i) * BK;
+    if (ORIENT == 0) tma_load_2d(stage + L::A_TILES * L::A_BYTES, &map_a, &full_bar[s], k0, t0);
+    else tma_load_2d(stage, &map_a, &full_bar[s], k0, t0);
+  };
+  const int n_early = min(n_kb, L::STAGES);  // stages that are free from the start
+
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
     for (int s = 0; s < L::STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
@@ -187,6 +217,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     mbar_init(tmem_full_bar, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    for (int i = 0; i < n_early; ++i) issue_weights(i);   // overlaps the tail of the kernel before
+    pdl_wait();
+    for (int i = 0; i < n_early; ++i) issue_activations(i);
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)),
@@ -194,6 +228,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  pdl_wait();  // every thread: nothing below may run ahead of the kernels before this one
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -202,8 +237,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      int armed = 0;
-      for (int i = 0; i < n_kb; ++i) {
+      int armed = n_early;
+      for (int i = n_early; i < n_kb; ++i) {
         const int s = i % L::STAGES;
         const uint32_t phase = (i / L::STAGES) & 1;
         if (!mbar_wait(&empty_bar[s], phase ^ 1, abort_flag)) {
@@ -211,23 +246,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           atomicCAS(error_word, 0, ERR_TIMEOUT_PRODUCER);
           break;
         }
-        uint8_t* stage = smem + s * L::STAGE_BYTES;
-        mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
-        const int k0 = (kb_begin + i) * BK;
-        if (ORIENT == 0) {
-          tma_load_2d(stage, &map_w, &full_bar[s], k0, f0);
-          if (MODE == 1) tma_load_2d(stage + L::A_BYTES, &map_w, &full_bar[s], k0, up_row_offset + f0);
-          tma_load_2d(stage + L::A_TILES * L::A_BYTES, &map_a, &full_bar[s], k0, t0);
-        } else {
-          tma_load_2d(stage, &map_a, &full_bar[s], k0, t0);
-          uint8_t* b_tile = stage + L::A_BYTES;
-          if (MODE == 1) {  // map_w's box has BN/2 rows: gate rows, then the matching up rows
-            tma_load_2d(b_tile, &map_w, &full_bar[s], k0, f0);
-            tma_load_2d(b_tile + L::B_BYTES / 2, &map_w, &full_bar[s], k0, up_row_offset + f0);
-          } else {
-            tma_load_2d(b_tile, &map_w, &full_bar[s], k0, f0);
-          }
-        }
+        issue_weights(i);
+        issue_activations(i);
         armed = i + 1;
       }
       if (*abort_flag) {
@@ -409,9 +429,8 @@ int launch(const CUtensorMap* map_w, const CUtensorMap* map_a, void* out, int ou
   constexpr int F_TILE = ORIENT == 0 ? BM : (MODE == 1 ? BN / 2 : BN);
   constexpr int T_TILE = ORIENT == 0 ? BN : BM;
   dim3 grid((n_features + F_TILE - 1) / F_TILE, (n_tokens + T_TILE - 1) / T_TILE, splits);
-  kern<<<grid, NUM_THREADS, L::SMEM_BYTES, stream>>>(*map_w, *map_a, out, out_is_f32, n_tokens, n_features,
-                                                      k_blocks, per_split, ld_out, partial_stride,
-                                                      up_row_offset, error_word);
+  launch_kernel(kern, grid, NUM_THREADS, L::SMEM_BYTES, stream, *map_w, *map_a, out, out_is_f32, n_tokens,
+                n_features, k_blocks, per_split, ld_out, partial_stride, up_row_offset, error_word);
   return launch_status();
 }
 

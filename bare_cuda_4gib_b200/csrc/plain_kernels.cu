@@ -26,6 +26,8 @@
 template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int32_t* __restrict__ ids,
                                     float* __restrict__ out, int hidden) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const TW* row = table + (long long)ids[t] * hidden;
   float* dst = out + (long long)t * hidden;
@@ -36,10 +38,10 @@ extern "C" int llm_embed_gather(const void* table, int table_dtype, const int32_
                                 int n_tokens, int hidden, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (table_dtype == DT_F32) {
-    embed_gather_kernel<float><<<n_tokens, 256, 0, stream>>>((const float*)table, ids, out, hidden);
+    launch_kernel(embed_gather_kernel<float>, n_tokens, 256, 0, stream, (const float*)table, ids, out, hidden);
   } else if (table_dtype == DT_BF16) {
-    embed_gather_kernel<__nv_bfloat16>
-        <<<n_tokens, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden);
+    launch_kernel(embed_gather_kernel<__nv_bfloat16>, n_tokens, 256, 0, stream, (const __nv_bfloat16*)table, ids, out,
+                  hidden);
   } else {
     return ERR_BAD_DTYPE;
   }
@@ -58,6 +60,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
                                    int n_partials, long long partial_stride,
                                    const TW* __restrict__ weight, TO* __restrict__ out,
                                    const int32_t* __restrict__ row_index, int hidden, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float row_cache[];  // hidden floats + 32 scratch
   float* scratch = row_cache + hidden;
   const int r = blockIdx.x;
@@ -88,6 +92,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const float
                                        int n_partials, long long partial_stride,
                                        const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ out,
                                        const int32_t* __restrict__ row_index, int hidden, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   const long long src = row_index ? row_index[r] : r;
@@ -148,8 +154,8 @@ static int add_rmsnorm_out(float* residual, const void* delta, int n_partials,
     auto kern = add_rmsnorm_kernel<TD, TW, TO>;                                                 \
     if (smem > 48 * 1024)                                                                       \
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
-    kern<<<rows, 256, smem, stream>>>(residual, (const TD*)delta, n_partials, partial_stride,   \
-                                      (const TW*)weight, (TO*)out, row_index, hidden, eps);     \
+    launch_kernel(kern, rows, 256, smem, stream, residual, (const TD*)delta, n_partials,        \
+                  partial_stride, (const TW*)weight, (TO*)out, row_index, hidden, eps);         \
   } while (0)
   if (out_dtype == DT_F32) LAUNCH_NORM(float);
   else if (out_dtype == DT_BF16) LAUNCH_NORM(__nv_bfloat16);
@@ -173,9 +179,8 @@ extern "C" int llm_add_rmsnorm(float* residual, const void* delta, int delta_dty
     int threads = 128;
     while (threads < 1024 && threads * 2 <= n4) threads *= 2;   // <= 2 float4 per thread when wide
     while (threads * 4 < n4) threads *= 2;
-    add_rmsnorm_vec_kernel<<<rows, threads, 0, stream>>>(residual, (const float*)delta, n_partials,
-                                                          partial_stride, (const __nv_bfloat16*)weight,
-                                                          (__nv_bfloat16*)out, row_index, hidden, eps);
+    launch_kernel(add_rmsnorm_vec_kernel, rows, threads, 0, stream, residual, (const float*)delta, n_partials,
+                  partial_stride, (const __nv_bfloat16*)weight, (__nv_bfloat16*)out, row_index, hidden, eps);
     return launch_status();
   }
   if (delta_dtype == DT_F32 && weight_dtype == DT_F32)
@@ -205,6 +210,8 @@ template <typename TA, typename TW, typename TO>
 __global__ void __launch_bounds__(256)
 matmul_plain_kernel(const TA* __restrict__ a, const TW* __restrict__ w, TO* __restrict__ out, int M,
                     int N, int K, long long lda, long long ldo) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float as[GK][GT + 1];
   __shared__ float ws[GK][GT + 1];
   const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
@@ -255,11 +262,11 @@ static int matmul_plain_out(const void* a, const void* w, void* out, int out_dty
   dim3 grid((N + GT - 1) / GT, (M + GT - 1) / GT);
   if (grid.y > 65535) return ERR_BAD_SIZE;
   if (out_dtype == DT_F32)
-    matmul_plain_kernel<TA, TW, float>
-        <<<grid, 256, 0, stream>>>((const TA*)a, (const TW*)w, (float*)out, M, N, K, lda, ldo);
+    launch_kernel(matmul_plain_kernel<TA, TW, float>, grid, 256, 0, stream, (const TA*)a, (const TW*)w, (float*)out,
+                  M, N, K, lda, ldo);
   else if (out_dtype == DT_BF16)
-    matmul_plain_kernel<TA, TW, __nv_bfloat16><<<grid, 256, 0, stream>>>(
-        (const TA*)a, (const TW*)w, (__nv_bfloat16*)out, M, N, K, lda, ldo);
+    launch_kernel(matmul_plain_kernel<TA, TW, __nv_bfloat16>, grid, 256, 0, stream, (const TA*)a, (const TW*)w,
+                  (__nv_bfloat16*)out, M, N, K, lda, ldo);
   else
     return ERR_BAD_DTYPE;
   return launch_status();
@@ -296,6 +303,8 @@ rope_cache_write_kernel(const TI* __restrict__ qkv, int n_partials, long long pa
                         TO* __restrict__ q_out, PagedCache cache, const int32_t* __restrict__ positions,
                         const int32_t* __restrict__ row_seq, const float* __restrict__ inv_freq, int q_heads,
                         int write_cache) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31;
   const int h = blockIdx.y * ROPE_HEADS_PER_BLOCK + (threadIdx.x >> 5);
@@ -348,9 +357,9 @@ extern "C" int llm_rope_cache_write(const void* qkv, int in_dtype, int n_partial
   dim3 grid(n_tokens, (n_heads + ROPE_HEADS_PER_BLOCK - 1) / ROPE_HEADS_PER_BLOCK);
   if (grid.y > 65535) return ERR_BAD_SIZE;
 #define LAUNCH_ROPE(TI, TO)                                                                   \
-  rope_cache_write_kernel<TI, TO><<<grid, ROPE_HEADS_PER_BLOCK * 32, 0, stream>>>(            \
-      (const TI*)qkv, n_partials, partial_stride, (TO*)q_out, c, positions, row_seq, inv_freq,  \
-      q_heads, write_cache)
+  launch_kernel(rope_cache_write_kernel<TI, TO>, grid, ROPE_HEADS_PER_BLOCK * 32, 0, stream,   \
+                (const TI*)qkv, n_partials, partial_stride, (TO*)q_out, c, positions, row_seq,  \
+                inv_freq, q_heads, write_cache)
   if (in_dtype == DT_F32 && out_dtype == DT_F32) LAUNCH_ROPE(float, float);
   else if (in_dtype == DT_F32 && out_dtype == DT_BF16) LAUNCH_ROPE(float, __nv_bfloat16);
   else if (in_dtype == DT_BF16 && out_dtype == DT_BF16) LAUNCH_ROPE(__nv_bfloat16, __nv_bfloat16);
@@ -374,6 +383,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_plain_kernel(const T* __restrict__ q, T* __restrict__ out, PagedCache cache,
                        const int32_t* __restrict__ positions, const int32_t* __restrict__ row_seq,
                        int q_heads, int n_tokens, float scale, int window) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float q_smem[];  // ATT_WARPS * head_dim
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * ATT_WARPS + warp;
@@ -450,12 +461,12 @@ extern "C" int llm_attention_plain(const void* q, void* out, int dtype, void* k_
   const unsigned blocks = (unsigned)((items + ATT_WARPS - 1) / ATT_WARPS);
   const size_t smem = (size_t)ATT_WARPS * head_dim * sizeof(float);
   if (dtype == DT_F32)
-    attention_plain_kernel<float><<<blocks, ATT_WARPS * 32, smem, stream>>>(
-        (const float*)q, (float*)out, c, positions, row_seq, q_heads, n_tokens, scale, window);
+    launch_kernel(attention_plain_kernel<float>, blocks, ATT_WARPS * 32, smem, stream, (const float*)q, (float*)out,
+                  c, positions, row_seq, q_heads, n_tokens, scale, window);
   else if (dtype == DT_BF16)
-    attention_plain_kernel<__nv_bfloat16><<<blocks, ATT_WARPS * 32, smem, stream>>>(
-        (const __nv_bfloat16*)q, (__nv_bfloat16*)out, c, positions, row_seq, q_heads, n_tokens,
-        scale, window);
+    launch_kernel(attention_plain_kernel<__nv_bfloat16>, blocks, ATT_WARPS * 32, smem, stream,
+                  (const __nv_bfloat16*)q, (__nv_bfloat16*)out, c, positions, row_seq, q_heads, n_tokens, scale,
+                  window);
   else
     return ERR_BAD_DTYPE;
   return launch_status();
@@ -468,6 +479,8 @@ extern "C" int llm_attention_plain(const void* q, void* out, int dtype, void* k_
 template <typename TI, typename TO>
 __global__ void swiglu_kernel(const TI* __restrict__ in, int n_partials, long long partial_stride,
                               TO* __restrict__ out, long long total, int inter) {
+  pdl_launch_dependents();
+  pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     const long long t = i / inter;
@@ -487,8 +500,8 @@ extern "C" int llm_swiglu(const void* in, int in_dtype, int n_partials, long lon
   if (total <= 0) return 0;
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
 #define LAUNCH_SWIGLU(TI, TO)                                                                    \
-  swiglu_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)in, n_partials, partial_stride,   \
-                                                    (TO*)out, total, inter)
+  launch_kernel(swiglu_kernel<TI, TO>, blocks, 256, 0, stream, (const TI*)in, n_partials,        \
+                partial_stride, (TO*)out, total, inter)
   if (in_dtype == DT_F32 && out_dtype == DT_F32) LAUNCH_SWIGLU(float, float);
   else if (in_dtype == DT_F32 && out_dtype == DT_BF16) LAUNCH_SWIGLU(float, __nv_bfloat16);
   else if (in_dtype == DT_BF16 && out_dtype == DT_BF16) LAUNCH_SWIGLU(__nv_bfloat16, __nv_bfloat16);
@@ -502,6 +515,8 @@ extern "C" int llm_swiglu(const void* in, int in_dtype, int n_partials, long lon
 // One block per row: the index of the largest logit; the lowest index wins a tie.
 __global__ void argmax_rows_kernel(const float* __restrict__ logits, int32_t* __restrict__ out,
                                    int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float best_v[32];
   __shared__ int best_i[32];
   const float* row = logits + (long long)blockIdx.x * vocab;
@@ -538,7 +553,7 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, int32_t* __
 extern "C" int llm_argmax_rows(const float* logits, int32_t* out, int rows, int vocab,
                                cudaStream_t stream) {
   if (rows <= 0) return 0;
-  argmax_rows_kernel<<<rows, 256, 0, stream>>>(logits, out, vocab);
+  launch_kernel(argmax_rows_kernel, rows, 256, 0, stream, logits, out, vocab);
   return launch_status();
 }
 
@@ -550,6 +565,8 @@ __global__ void sample_rows_kernel(const float* __restrict__ logits,
                                    const float* __restrict__ temperature,
                                    const float* __restrict__ uniform, int32_t* __restrict__ out,
                                    int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[32];
   __shared__ float span_sum[256];
   __shared__ int chosen_thread;
@@ -606,7 +623,7 @@ __global__ void sample_rows_kernel(const float* __restrict__ logits,
 extern "C" int llm_sample_rows(const float* logits, const float* temperature, const float* uniform,
                                int32_t* out, int rows, int vocab, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  argmax_rows_kernel<<<rows, 256, 0, stream>>>(logits, out, vocab);
-  sample_rows_kernel<<<rows, 256, 0, stream>>>(logits, temperature, uniform, out, vocab);
+  launch_kernel(argmax_rows_kernel, rows, 256, 0, stream, logits, out, vocab);
+  launch_kernel(sample_rows_kernel, rows, 256, 0, stream, logits, temperature, uniform, out, vocab);
   return launch_status();
 }
