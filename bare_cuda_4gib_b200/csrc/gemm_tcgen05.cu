@@ -139,40 +139,57 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr));
 }
 
-template <int BN, int MODE, int ORIENT>
-struct Layout {
-  static constexpr int A_TILES = (MODE == 1 && ORIENT == 0) ? 2 : 1;
-  static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
-  static constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
-  // small token tiles are the weight-streaming case: two blocks per SM keep more tiles resident
-  static constexpr int BLOCKS_PER_SM = (BN <= 64 && MODE == 0 && ORIENT == 0) ? 2 : 1;
-  static constexpr int SMEM_BUDGET = (BLOCKS_PER_SM == 2 ? 104 : 200) * 1024;
-  static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-  static constexpr int TMEM_COLS_RAW = BN * A_TILES;
-  static constexpr int TMEM_COLS = TMEM_COLS_RAW < 32 ? 32 : TMEM_COLS_RAW;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+// Sizes of a launch that depend on the N tile `bn` (a run-time value: any multiple of 16 up to
+// 256, so that the number of tiles can be matched to the number of SMs).
+struct Geometry {
+  int bn;           // MMA N: tokens (ORIENT 0) or weight rows (ORIENT 1) per tile
+  int a_tiles;      // 128-row operand tiles per stage (2 for ORIENT 0 SwiGLU)
+  int b_bytes;      // bytes of the N operand tile
+  int stage_bytes;
+  int stages;
+  int tmem_cols;    // power of two >= bn * a_tiles, at least 32
+  uint32_t idesc;
 };
 
-template <int BN, int MODE, int ORIENT>
-__global__ void __launch_bounds__(NUM_THREADS, (Layout<BN, MODE, ORIENT>::BLOCKS_PER_SM))
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int MAX_STAGES = 8;
+
+static Geometry make_geometry(int bn, int mode, int orient, int blocks_per_sm) {
+  Geometry g;
+  g.bn = bn;
+  g.a_tiles = (mode == 1 && orient == 0) ? 2 : 1;
+  g.b_bytes = bn * BK * 2;
+  g.stage_bytes = g.a_tiles * A_BYTES + g.b_bytes;
+  const int budget = (blocks_per_sm == 2 ? 110 : 200) * 1024;
+  g.stages = budget / g.stage_bytes;
+  if (g.stages > MAX_STAGES) g.stages = MAX_STAGES;
+  int cols = 32;
+  while (cols < bn * g.a_tiles) cols *= 2;
+  g.tmem_cols = cols;
+  g.idesc = instr_desc_bf16(BM, bn);
+  return g;
+}
+
+static size_t smem_bytes(const Geometry& g) { return (size_t)g.stages * g.stage_bytes + 1024 + 256; }
+
+template <int MODE, int ORIENT, int BLOCKS_PER_SM>
+__global__ void __launch_bounds__(NUM_THREADS, BLOCKS_PER_SM)
+gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                     void* __restrict__ out, int out_is_f32, int n_tokens, int n_features, int k_blocks,
                     int k_blocks_per_split, long long ld_out, long long partial_stride, int up_row_offset,
                     int* __restrict__ error_word) {
-  using L = Layout<BN, MODE, ORIENT>;
+  const int BN = geo.bn;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::STAGES * L::STAGE_BYTES);
-  uint64_t* empty_bar = full_bar + L::STAGES;
-  uint64_t* tmem_full_bar = empty_bar + L::STAGES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + geo.stages * geo.stage_bytes);
+  uint64_t* empty_bar = full_bar + geo.stages;
+  uint64_t* tmem_full_bar = empty_bar + geo.stages;
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // ORIENT 0: 128 features x BN tokens.  ORIENT 1: 128 tokens x BN features (MODE 1: BN/2 outputs).
-  constexpr int F_TILE = ORIENT == 0 ? BM : (MODE == 1 ? BN / 2 : BN);
+  const int F_TILE = ORIENT == 0 ? BM : (MODE == 1 ? BN / 2 : BN);
   const int f0 = blockIdx.x * F_TILE;
   const int t0 = blockIdx.y * (ORIENT == 0 ? BN : BM);
   const int kb_begin = blockIdx.z * k_blocks_per_split;
@@ -182,35 +199,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   // One stage's loads, in two halves: the weight tiles depend on no other kernel and may be
   // fetched before pdl_wait(); the activation tile is another kernel's output and may not.
   // The first half arms the stage's barrier with the bytes of both.
-  auto issue_weights = [&](int i) {
-    const int s = i % L::STAGES;
-    uint8_t* stage = smem + s * L::STAGE_BYTES;
-    mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+  auto issue_weights = [&](int i, int s) {   // k block i of this split into stage s
+    uint8_t* stage = smem + s * geo.stage_bytes;
+    mbar_expect_tx(&full_bar[s], geo.stage_bytes);
     const int k0 = (kb_begin + i) * BK;
     if (ORIENT == 0) {
       tma_load_2d(stage, &map_w, &full_bar[s], k0, f0);
-      if (MODE == 1) tma_load_2d(stage + L::A_BYTES, &map_w, &full_bar[s], k0, up_row_offset + f0);
+      if (MODE == 1) tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], k0, up_row_offset + f0);
     } else {
-      uint8_t* b_tile = stage + L::A_BYTES;
+      uint8_t* b_tile = stage + A_BYTES;
       tma_load_2d(b_tile, &map_w, &full_bar[s], k0, f0);
       // MODE 1: map_w's box has BN/2 rows: gate rows above, the matching up rows below
-      if (MODE == 1) tma_load_2d(b_tile + L::B_BYTES / 2, &map_w, &full_bar[s], k0, up_row_offset + f0);
+      if (MODE == 1) tma_load_2d(b_tile + geo.b_bytes / 2, &map_w, &full_bar[s], k0, up_row_offset + f0);
     }
   };
-  auto issue_activations = [&](int i) {
-    const int s = i % L::STAGES;
-    uint8_t* stage = smem + s * L::STAGE_BYTES;
+  auto issue_activations = [&](int i, int s) {
+    uint8_t* stage = smem + s * geo.stage_bytes;
     const int k0 = (kb_begin + i) * BK;
-    if (ORIENT == 0) tma_load_2d(stage + L::A_TILES * L::A_BYTES, &map_a, &full_bar[s], k0, t0);
+    if (ORIENT == 0) tma_load_2d(stage + geo.a_tiles * A_BYTES, &map_a, &full_bar[s], k0, t0);
     else tma_load_2d(stage, &map_a, &full_bar[s], k0, t0);
   };
-  const int n_early = min(n_kb, L::STAGES);  // stages that are free from the start
+  const int n_early = min(n_kb, geo.stages);  // stages that are free from the start
 
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
-    for (int s = 0; s < L::STAGES; ++s) {
+    for (int s = 0; s < geo.stages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
@@ -218,13 +233,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    for (int i = 0; i < n_early; ++i) issue_weights(i);   // overlaps the tail of the kernel before
+    for (int i = 0; i < n_early; ++i) issue_weights(i, i);   // overlaps the tail of the kernel before
     pdl_wait();
-    for (int i = 0; i < n_early; ++i) issue_activations(i);
+    for (int i = 0; i < n_early; ++i) issue_activations(i, i);
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)),
-                 "r"(L::TMEM_COLS)
+                 "r"(geo.tmem_cols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -238,23 +253,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       int armed = n_early;
+      // stage and phase advance by counting: a division per k block would slow the issue down
+      int s = n_early == geo.stages ? 0 : n_early;
+      uint32_t phase = n_early == geo.stages ? 1 : 0;
       for (int i = n_early; i < n_kb; ++i) {
-        const int s = i % L::STAGES;
-        const uint32_t phase = (i / L::STAGES) & 1;
         if (!mbar_wait(&empty_bar[s], phase ^ 1, abort_flag)) {
           *abort_flag = 1;
           atomicCAS(error_word, 0, ERR_TIMEOUT_PRODUCER);
           break;
         }
-        issue_weights(i);
-        issue_activations(i);
+        issue_weights(i, s);
+        issue_activations(i, s);
         armed = i + 1;
+        if (++s == geo.stages) { s = 0; phase ^= 1; }
       }
       if (*abort_flag) {
         // copies already issued still land in shared memory: wait for them (bounded) before leaving
-        for (int i = max(0, armed - L::STAGES); i < armed; ++i) {
+        for (int i = max(0, armed - geo.stages); i < armed; ++i) {
           const unsigned long long start = global_timer();
-          while (!mbar_try_wait(&full_bar[i % L::STAGES], (i / L::STAGES) & 1) &&
+          while (!mbar_try_wait(&full_bar[i % geo.stages], (i / geo.stages) & 1) &&  // rare path
                  global_timer() - start < WAIT_LIMIT_NS / 10) {
           }
         }
@@ -263,11 +280,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc_bf16(BM, BN);
+      const uint32_t idesc = geo.idesc;
       bool ok = true;
+      int s = 0;
+      uint32_t phase = 0;
+      const uint32_t smem_base = smem_u32(smem);
       for (int i = 0; i < n_kb && ok; ++i) {
-        const int s = i % L::STAGES;
-        const uint32_t phase = (i / L::STAGES) & 1;
         if (!mbar_wait(&full_bar[s], phase, abort_flag)) {
           *abort_flag = 1;
           atomicCAS(error_word, 0, ERR_TIMEOUT_MMA);
@@ -275,8 +293,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = smem_u32(smem + s * L::STAGE_BYTES);
-        const uint32_t b_addr = a_addr + L::A_TILES * L::A_BYTES;
+        const uint32_t a_addr = smem_base + s * geo.stage_bytes;
+        const uint32_t b_addr = a_addr + geo.a_tiles * A_BYTES;
         const uint64_t desc_a = smem_desc_sw128(a_addr);
         const uint64_t desc_b = smem_desc_sw128(b_addr);
 #pragma unroll
@@ -285,11 +303,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);
           umma_bf16(tmem_base, desc_a + koff, desc_b + koff, idesc, acc);
           if (MODE == 1 && ORIENT == 0) {
-            const uint64_t desc_up = smem_desc_sw128(a_addr + L::A_BYTES);
+            const uint64_t desc_up = smem_desc_sw128(a_addr + A_BYTES);
             umma_bf16(tmem_base + BN, desc_up + koff, desc_b + koff, idesc, acc);
           }
         }
         umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+        if (++s == geo.stages) { s = 0; phase ^= 1; }
       }
       umma_commit(tmem_full_bar);    // accumulator complete (or, after giving up, releases the epilogue)
     }
@@ -391,7 +410,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::TMEM_COLS)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(geo.tmem_cols)
                  : "memory");
   }
 }
@@ -412,25 +431,28 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-template <int BN, int MODE, int ORIENT>
-int launch(const CUtensorMap* map_w, const CUtensorMap* map_a, void* out, int out_is_f32, int n_tokens,
+template <int MODE, int ORIENT, int BLOCKS_PER_SM>
+int launch(int bn, const CUtensorMap* map_w, const CUtensorMap* map_a, void* out, int out_is_f32, int n_tokens,
            int n_features, int K, long long ld_out, long long partial_stride, int splits, int up_row_offset,
            int* error_word, cudaStream_t stream) {
-  using L = Layout<BN, MODE, ORIENT>;
-  static bool configured = false;
-  auto kern = gemm_tcgen05_kernel<BN, MODE, ORIENT>;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES) != cudaSuccess)
+  const Geometry g = make_geometry(bn, MODE, ORIENT, BLOCKS_PER_SM);
+  if (g.stages < 1 || g.tmem_cols * BLOCKS_PER_SM > 512) return ERR_BAD_SIZE;
+  auto kern = gemm_tcgen05_kernel<MODE, ORIENT, BLOCKS_PER_SM>;
+  static size_t configured = 0;
+  const size_t smem = smem_bytes(g);
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return launch_status();
-    configured = true;
+    configured = smem;
   }
   const int k_blocks = (K + BK - 1) / BK;
   const int per_split = (k_blocks + splits - 1) / splits;
-  constexpr int F_TILE = ORIENT == 0 ? BM : (MODE == 1 ? BN / 2 : BN);
-  constexpr int T_TILE = ORIENT == 0 ? BN : BM;
-  dim3 grid((n_features + F_TILE - 1) / F_TILE, (n_tokens + T_TILE - 1) / T_TILE, splits);
-  launch_kernel(kern, grid, NUM_THREADS, L::SMEM_BYTES, stream, *map_w, *map_a, out, out_is_f32, n_tokens,
-                n_features, k_blocks, per_split, ld_out, partial_stride, up_row_offset, error_word);
+  const int f_tile = ORIENT == 0 ? BM : (MODE == 1 ? bn / 2 : bn);
+  const int t_tile = ORIENT == 0 ? bn : BM;
+  dim3 grid((n_features + f_tile - 1) / f_tile, (n_tokens + t_tile - 1) / t_tile, splits);
+  if (grid.y > 65535 || grid.z > 65535) return ERR_BAD_SIZE;
+  launch_kernel(kern, grid, NUM_THREADS, smem, stream, g, *map_w, *map_a, out, out_is_f32, n_tokens, n_features,
+                k_blocks, per_split, ld_out, partial_stride, up_row_offset, error_word);
   return launch_status();
 }
 
@@ -458,9 +480,9 @@ extern "C" int llm_gemm_tensor_map(void* map_out, const void* base, long long ro
 
 // out[z][t, f] (z < splits) = partial sums of act[t, :] . w[f, :]; mode 1: silu(gate) * up with
 // w = [gate; up], the up rows starting at `up_row_offset` (splits must be 1 then).
-// orient 0: `bn` is the token tile (16, 32, 64, 128, 256); map_a's box must have bn rows, map_w's 128.
-// orient 1: `bn` is the feature tile (128 or 256); map_a's box must have 128 rows, map_w's bn rows
-// (bn / 2 in mode 1).
+// `bn` is the N tile, a multiple of 16 up to 256 (of 32 for orient 1 with mode 1).
+// orient 0: bn tokens per tile; map_a's box must have bn rows, map_w's 128.
+// orient 1: bn weight rows per tile; map_a's box must have 128 rows, map_w's bn rows (bn / 2 in mode 1).
 extern "C" int llm_gemm_bf16(const void* map_w, const void* map_a, void* out, int out_dtype, int n_tokens,
                              int n_features, int K, long long ld_out, long long partial_stride, int splits,
                              int bn, int mode, int orient, int up_row_offset, int* error_word,
@@ -475,27 +497,24 @@ extern "C" int llm_gemm_bf16(const void* map_w, const void* map_a, void* out, in
   const CUtensorMap* mw = &mw_copy;
   const CUtensorMap* ma = &ma_copy;
   const int f32 = out_dtype == DT_F32;
-#define GEMM_CASE(BN_, ORIENT_)                                                                              \
-  return mode == 1 ? launch<BN_, 1, ORIENT_>(mw, ma, out, f32, n_tokens, n_features, K, ld_out, partial_stride, \
-                                             splits, up_row_offset, error_word, stream)                         \
-                   : launch<BN_, 0, ORIENT_>(mw, ma, out, f32, n_tokens, n_features, K, ld_out, partial_stride, \
-                                             splits, up_row_offset, error_word, stream)
-  if (orient == 0) {
-    switch (bn) {
-      case 16: GEMM_CASE(16, 0);
-      case 32: GEMM_CASE(32, 0);
-      case 64: GEMM_CASE(64, 0);
-      case 128: GEMM_CASE(128, 0);
-      case 256: GEMM_CASE(256, 0);
-      default: return ERR_BAD_SIZE;
-    }
-  } else if (orient == 1) {
-    switch (bn) {
-      case 128: GEMM_CASE(128, 1);
-      case 256: GEMM_CASE(256, 1);
-      default: return ERR_BAD_SIZE;
-    }
-  }
+  if (bn < 16 || bn > 256 || bn % 16 || (mode == 1 && orient == 1 && bn % 32)) return ERR_BAD_SIZE;
+  // Two thread blocks per SM let one block's epilogue overlap the other's main loop, at the price
+  // of half the pipeline depth each: worth it only when there are more tiles than SMs and at
+  // least three stages still fit (two for the SwiGLU tiles, whose long epilogue gains most).
+  const Geometry two = make_geometry(bn, mode, orient, 2);
+  const long long f_tile = orient == 0 ? BM : (mode == 1 ? bn / 2 : bn), t_tile = orient == 0 ? bn : BM;
+  const long long tiles = ((n_features + f_tile - 1) / f_tile) * ((n_tokens + t_tile - 1) / t_tile) * splits;
+  const bool pair = tiles > 148 && two.tmem_cols <= 256 && two.stages >= ((orient == 1 && mode == 1) ? 2 : 3);
+#define GEMM_CASE(MODE_, ORIENT_)                                                                            \
+  if (mode == MODE_ && orient == ORIENT_)                                                                    \
+    return pair ? launch<MODE_, ORIENT_, 2>(bn, mw, ma, out, f32, n_tokens, n_features, K, ld_out,           \
+                                            partial_stride, splits, up_row_offset, error_word, stream)      \
+                : launch<MODE_, ORIENT_, 1>(bn, mw, ma, out, f32, n_tokens, n_features, K, ld_out,           \
+                                            partial_stride, splits, up_row_offset, error_word, stream)
+  GEMM_CASE(0, 0);
+  GEMM_CASE(1, 0);
+  GEMM_CASE(0, 1);
+  GEMM_CASE(1, 1);
   return ERR_BAD_SIZE;
 #undef GEMM_CASE
 }

@@ -4,6 +4,7 @@ the token tile and of the K split, and the device error word that bounded waits 
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_int, c_longlong, c_void_p
 from typing import Dict, Optional, Tuple
 
@@ -126,15 +127,25 @@ N_SMS = 148
 
 
 def feature_tile(rows: int, n_out: int, swiglu: bool) -> int:
-    """Orientation 1: 256 or 128 weight rows per tile, whichever needs less time over whole waves
-    of thread blocks (a 128-wide tile costs a little more than half of a 256-wide one)."""
+    """Orientation 1: how many weight rows a tile takes (a multiple of 16 up to 256; of 32 with
+    SwiGLU, whose tile is half gate rows and half up rows).  Every SM works through
+    ceil(tiles / SMs) tiles and a tile's time grows with its width, so the product of the two is
+    minimised; a small fixed cost per tile breaks ties towards wider tiles."""
+    forced = os.environ.get("BARE_CUDA_B200_GEMM_BN")     # experiments only
+    if forced:
+        return int(forced)
+    step = 32 if swiglu else 16
     best, best_cost = 256, None
-    for bn, cost in ((256, 1.0), (128, 0.58)):
+    for bn in range(256, 63, -step):
+        # between 160 and 256 a tile is too big for two blocks per SM with three stages each, yet
+        # more than one tile per SM needs that overlap: only SwiGLU tiles (two stages) use the range
+        if not swiglu and 160 < bn < 256:
+            continue
         out_per_tile = bn // 2 if swiglu else bn
         tiles = -(-rows // BM) * -(-n_out // out_per_tile)
-        total = -(-tiles // N_SMS) * cost
-        if best_cost is None or total < best_cost:
-            best, best_cost = bn, total
+        cost = -(-tiles // N_SMS) * (bn / 256.0 + 0.12)
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = bn, cost
     return best
 
 
