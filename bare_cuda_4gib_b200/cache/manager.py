@@ -69,10 +69,15 @@ class CacheGroup:
     def blocks_to_take(self, slot: int, length: int, n: int) -> List[int]:
         table = self.tables.get(slot, [])
         last = (length + n - 1) // self.page_tokens
+        if self.request.window is None:
+            # every block below len(table) is held: only new blocks can be missing
+            return list(range(len(table), last + 1)) if last >= len(table) else []
         first = self.first_needed_block(length)
         return [b for b in range(first, last + 1) if b >= len(table) or table[b] < 0]
 
     def blocks_to_drop(self, slot: int, length: int) -> List[int]:
+        if self.request.window is None:
+            return []
         table = self.tables.get(slot, [])
         return [b for b in range(min(self.first_needed_block(length), len(table))) if table[b] >= 0]
 
@@ -179,15 +184,25 @@ class CacheManager:
 
     def reserve(self, slot: int, n: int) -> None:
         """Makes sure positions length .. length + n - 1 have pages in every group; all or nothing."""
-        length = self.length(slot)
-        if n <= 0:
-            raise CacheError("reserve needs a positive token count")
-        if length + n > self.max_tokens:
-            raise CacheError(f"request of {length + n} tokens exceeds the cache's limit of "
-                             f"{self.max_tokens} per request")
-        if not self.can_reserve([(slot, n)]):
-            raise OutOfPages(f"out of pages: slot {slot} needs {self.pages_needed(slot, n)} more page(s) "
-                             f"per group, free are {[g.pool.free_pages for g in self.groups]}")
+        self.reserve_batch([(slot, n)])
+
+    def reserve_batch(self, wants: Sequence[Tuple[int, int]]) -> None:
+        """`reserve` for several (slot, tokens) at once: either every request gets its pages or none does."""
+        for slot, n in wants:
+            length = self.length(slot)
+            if n <= 0:
+                raise CacheError("reserve needs a positive token count")
+            if length + n > self.max_tokens:
+                raise CacheError(f"request of {length + n} tokens exceeds the cache's limit of "
+                                 f"{self.max_tokens} per request")
+        if not self.can_reserve(wants):
+            raise OutOfPages(f"out of pages: the pools have {[g.pool.free_pages for g in self.groups]} page(s) "
+                             f"free per group, the batch needs more")
+        for slot, n in wants:
+            self._take(slot, n)
+
+    def _take(self, slot: int, n: int) -> None:
+        length = self.lengths[slot]
         for g in self.groups:
             table = g.tables[slot]
             for b in g.blocks_to_drop(slot, length):

@@ -34,16 +34,30 @@ def _peaks():
     return hbm, tf
 
 
+GRAPH = [True]   # time a CUDA graph of `iters` launches, so that host launch cost does not hide short kernels
+
+
 def _time(fn, iters, warmup):
     import torch
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(iters):
-        fn()
-    end.record()
+    if GRAPH[0]:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(iters):
+                fn()
+        graph.replay()
+        torch.cuda.synchronize()
+        start.record()
+        graph.replay()
+        end.record()
+    else:
+        start.record()
+        for _ in range(iters):
+            fn()
+        end.record()
     torch.cuda.synchronize()
     return start.elapsed_time(end) / iters * 1e3   # microseconds
 
@@ -51,8 +65,12 @@ def _time(fn, iters, warmup):
 def _ctx(max_rows, max_seqs=256):
     import torch
     from ..engine.step import Workspace
-    return types.SimpleNamespace(ws=Workspace(torch.device("cuda"), max_rows), max_rows=max_rows, max_seqs=max_seqs,
-                                 pad_seqs=0, stream=torch.cuda.current_stream().cuda_stream, extras={})
+    class Ctx(types.SimpleNamespace):
+        @property
+        def stream(self):          # the current stream, which is the capture stream inside a graph capture
+            return torch.cuda.current_stream().cuda_stream
+    return Ctx(ws=Workspace(torch.device("cuda"), max_rows), max_rows=max_rows, max_seqs=max_seqs, pad_seqs=0,
+               extras={})
 
 
 def _report(name, us, bytes_moved, flops):
@@ -158,6 +176,7 @@ def main(argv=None) -> int:
     common = argparse.ArgumentParser(add_help=False)
     common.add_argument("--iters", type=int, default=50)
     common.add_argument("--warmup", type=int, default=5)
+    common.add_argument("--no-graph", action="store_true", help="time direct launches instead of one CUDA graph")
     g = sub.add_parser("gemm", parents=[common])
     g.add_argument("--rows", type=int, required=True)
     g.add_argument("--out", type=int, required=True, help="output features (per half with --swiglu)")
@@ -177,6 +196,7 @@ def main(argv=None) -> int:
     for name, default in (("rows", 2048), ("heads", 32), ("kv-heads", 4), ("head-dim", 64)):
         r.add_argument(f"--{name}", type=int, default=default)
     args = ap.parse_args(argv)
+    GRAPH[0] = not args.no_graph
     {"gemm": bench_gemm, "attention": bench_attention, "norm": bench_norm, "rope": bench_rope}[args.kernel](args)
     return 0
 

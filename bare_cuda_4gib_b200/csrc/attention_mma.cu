@@ -11,7 +11,9 @@
 // for the decode shape, whose few rows leave the loads' latency exposed).
 //
 // Two shapes of the same kernel:
-//   WARPS_M = 4, WARPS_N = 1: 64 rows, each warp 16 rows and all 64 keys of a block (prefill);
+//   WARPS_M = 4, WARPS_N = 1: each warp 16 * MT rows and all 64 keys of a block (prefill); MT = 2
+//   (128 rows per block) for head sizes up to 64, where the registers allow it: a key fragment
+//   read from shared memory then feeds two row tiles, which halves the shared-memory traffic;
 //   WARPS_M = 1, WARPS_N = 4: 16 rows, each warp 16 of the 64 keys of a block (decode); the
 //   warps' partial softmax states are merged through shared memory.
 // gridDim.z > 1 splits a tile's key blocks over several thread blocks; each writes a
@@ -88,12 +90,13 @@ struct AttnArgs {
   int window;                  // <= 0: every key
 };
 
-template <int WARPS_M, int WARPS_N>
+template <int WARPS_M, int WARPS_N, int MT>
 __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32)
 attention_mma_kernel(AttnArgs a) {
   constexpr int NW = WARPS_M * WARPS_N;
   constexpr int NT_THREADS = NW * 32;
-  constexpr int BM = 16 * WARPS_M;
+  constexpr int WR = 16 * MT;            // rows per warp
+  constexpr int BM = WR * WARPS_M;
   constexpr int KEYS_W = BN / WARPS_N;  // keys of a block that one warp handles
   constexpr int NT = KEYS_W / 8;        // score n-tiles per warp
   static_assert(NT % 2 == 0, "a warp handles keys in pairs of n-tiles");
@@ -106,7 +109,8 @@ attention_mma_kernel(AttnArgs a) {
 
   pdl_launch_dependents();
   pdl_wait();
-  const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, n_splits = gridDim.z;
+  // later tiles of a request see more keys: start them first
+  const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, n_splits = gridDim.z;
   const int seq = a.tile_seq[tile];
   if (seq < 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -143,6 +147,12 @@ attention_mma_kernel(AttnArgs a) {
 
   const __nv_bfloat16* kc = reinterpret_cast<const __nv_bfloat16*>(a.cache.k);
   const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(a.cache.v);
+  // Page lookups: a key block lies in one page (pages of 64 positions or more) or spans 64 / page
+  // pages.  With a power-of-two page size the position is split with a shift and a mask.
+  const int page_tokens = a.cache.page_tokens;
+  const int page_shift = (page_tokens & (page_tokens - 1)) == 0 ? __ffs(page_tokens) - 1 : -1;
+  const int32_t* table_row = a.cache.block_table + (long long)seq * a.cache.table_stride;
+  const long long head_offset = (long long)kvh * page_tokens * D;
   // copies block kb into its stage (nothing if kb is past the end) and closes one cp.async group
   auto load_block = [&](int kb, int stage) {
     __nv_bfloat16* ks = Ks + stage * BN * LDS;
@@ -150,10 +160,16 @@ attention_mma_kernel(AttnArgs a) {
     for (int i = threadIdx.x; kb < kb_end && i < BN * CHUNKS; i += NT_THREADS) {
       const int r = i / CHUNKS, c = i % CHUNKS;
       const int key = kb * BN + r;
-      long long off = -1;
-      if (key < kv_len) off = cache_offset(a.cache, seq, key, kvh);
-      const bool valid = off >= 0;
-      const long long src = valid ? off + c * 8 : 0;
+      long long src = 0;
+      bool valid = key < kv_len;
+      if (valid) {
+        const int block = page_shift >= 0 ? key >> page_shift : key / page_tokens;
+        const int in_page = page_shift >= 0 ? key & (page_tokens - 1) : key % page_tokens;
+        const int page = __ldg(table_row + block);
+        valid = page >= 0;
+        src = (long long)page * a.cache.page_stride + head_offset + (long long)in_page * D + c * 8;
+      }
+      if (!valid) src = 0;
       cp_async16(ks + r * LDS + c * 8, kc + src, valid);
       cp_async16(vs + r * LDS + c * 8, vc + src, valid);
     }
@@ -165,22 +181,29 @@ attention_mma_kernel(AttnArgs a) {
   __syncthreads();  // Q staged
 
   // ---- Q fragments stay in registers
-  uint32_t qf[D / 16][4];
+  uint32_t qf[MT][D / 16][4];
 #pragma unroll
-  for (int ks = 0; ks < D / 16; ++ks)
-    ldmatrix_x4(qf[ks], Qs + (wm * 16 + (lane & 15)) * LDS + ks * 16 + (lane >> 4) * 8);
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks)
+      ldmatrix_x4(qf[mt][ks], Qs + (wm * WR + mt * 16 + (lane & 15)) * LDS + ks * 16 + (lane >> 4) * 8);
 
-  // this thread's two rows
-  int row_pos[2];
+  // this thread's rows: two per row tile
+  int row_pos[MT][2];
+  float m[MT][2], l[MT][2];
+  float o[MT][D / 8][4];
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int R = row0 + wm * 16 + (lane >> 2) + h * 8;
-    row_pos[h] = R < n_rows ? pos0 + R / group : -1;  // -1: no key is visible
+  for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int R = row0 + wm * WR + mt * 16 + (lane >> 2) + h * 8;
+      row_pos[mt][h] = R < n_rows ? pos0 + R / group : -1;  // -1: no key is visible
+      m[mt][h] = -INFINITY;
+      l[mt][h] = 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[mt][i][0] = o[mt][i][1] = o[mt][i][2] = o[mt][i][3] = 0.0f;
   }
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
-  float o[D / 8][4];
-#pragma unroll
-  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
 
   for (int kb = kb_begin; kb < kb_end; ++kb) {
     const int stage = (kb - kb_begin) % STAGES;
@@ -191,9 +214,11 @@ attention_mma_kernel(AttnArgs a) {
     const __nv_bfloat16* vs_ = Vs + stage * BN * LDS;
     const int key0 = kb * BN + wn * KEYS_W;  // first key this warp scores
 
-    float s[NT][4];
+    float s[MT][NT][4];
 #pragma unroll
-    for (int i = 0; i < NT; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int i = 0; i < NT; ++i) s[mt][i][0] = s[mt][i][1] = s[mt][i][2] = s[mt][i][3] = 0.0f;
 #pragma unroll
     for (int ks = 0; ks < D / 16; ++ks) {
 #pragma unroll
@@ -201,53 +226,59 @@ attention_mma_kernel(AttnArgs a) {
         uint32_t kf[4];
         const int mid = lane >> 3;
         ldmatrix_x4(kf, ks_ + (wn * KEYS_W + (nt + (mid >> 1)) * 8 + (lane & 7)) * LDS + ks * 16 + (mid & 1) * 8);
-        mma_bf16(s[nt], qf[ks], kf[0], kf[1]);
-        mma_bf16(s[nt + 1], qf[ks], kf[2], kf[3]);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          mma_bf16(s[mt][nt], qf[mt][ks], kf[0], kf[1]);
+          mma_bf16(s[mt][nt + 1], qf[mt][ks], kf[2], kf[3]);
+        }
       }
     }
 
-    // scale, mask, running maximum
-    float mx[2] = {-INFINITY, -INFINITY};
+    uint32_t pf[MT][NT / 2][4];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
+    for (int mt = 0; mt < MT; ++mt) {
+      // scale, mask, running maximum
+      float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int h = e >> 1;
-        const int key = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-        const bool visible = key <= row_pos[h] && (a.window <= 0 || key > row_pos[h] - a.window);
-        const float v = visible ? s[nt][e] * a.scale_log2 : -INFINITY;
-        s[nt][e] = v;
-        mx[h] = fmaxf(mx[h], v);
+      for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int h = e >> 1;
+          const int key = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+          const bool visible = key <= row_pos[mt][h] && (a.window <= 0 || key > row_pos[mt][h] - a.window);
+          const float v = visible ? s[mt][nt][e] * a.scale_log2 : -INFINITY;
+          s[mt][nt][e] = v;
+          mx[h] = fmaxf(mx[h], v);
+        }
       }
-    }
-    float corr[2], m_use[2];
+      float corr[2], m_use[2];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
-      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-      const float m_new = fmaxf(m[h], mx[h]);
-      m_use[h] = m_new == -INFINITY ? 0.0f : m_new;
-      corr[h] = exp2f(m[h] - m_use[h]);  // m = -inf gives 0
-      m[h] = m_new;
-      l[h] *= corr[h];
-    }
+      for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        const float m_new = fmaxf(m[mt][h], mx[h]);
+        m_use[h] = m_new == -INFINITY ? 0.0f : m_new;
+        corr[h] = exp2f(m[mt][h] - m_use[h]);  // m = -inf gives 0
+        m[mt][h] = m_new;
+        l[mt][h] *= corr[h];
+      }
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) {
-      o[i][0] *= corr[0];
-      o[i][1] *= corr[0];
-      o[i][2] *= corr[1];
-      o[i][3] *= corr[1];
-    }
-    // probabilities, as A fragments for P V
-    uint32_t pf[NT / 2][4];
+      for (int i = 0; i < D / 8; ++i) {
+        o[mt][i][0] *= corr[0];
+        o[mt][i][1] *= corr[0];
+        o[mt][i][2] *= corr[1];
+        o[mt][i][3] *= corr[1];
+      }
+      // probabilities, as A fragments for P V
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      const float p0 = exp2f(s[nt][0] - m_use[0]), p1 = exp2f(s[nt][1] - m_use[0]);
-      const float p2 = exp2f(s[nt][2] - m_use[1]), p3 = exp2f(s[nt][3] - m_use[1]);
-      l[0] += p0 + p1;
-      l[1] += p2 + p3;
-      pf[nt / 2][(nt & 1) * 2 + 0] = pack_bf16(p0, p1);
-      pf[nt / 2][(nt & 1) * 2 + 1] = pack_bf16(p2, p3);
+      for (int nt = 0; nt < NT; ++nt) {
+        const float p0 = exp2f(s[mt][nt][0] - m_use[0]), p1 = exp2f(s[mt][nt][1] - m_use[0]);
+        const float p2 = exp2f(s[mt][nt][2] - m_use[1]), p3 = exp2f(s[mt][nt][3] - m_use[1]);
+        l[mt][0] += p0 + p1;
+        l[mt][1] += p2 + p3;
+        pf[mt][nt / 2][(nt & 1) * 2 + 0] = pack_bf16(p0, p1);
+        pf[mt][nt / 2][(nt & 1) * 2 + 1] = pack_bf16(p2, p3);
+      }
     }
 #pragma unroll
     for (int kk = 0; kk < KEYS_W / 16; ++kk) {
@@ -256,17 +287,22 @@ attention_mma_kernel(AttnArgs a) {
         uint32_t vf[4];
         const int mid = lane >> 3;
         ldmatrix_x4_trans(vf, vs_ + (wn * KEYS_W + kk * 16 + (mid & 1) * 8 + (lane & 7)) * LDS + (dt + (mid >> 1)) * 8);
-        mma_bf16(o[dt], pf[kk], vf[0], vf[1]);
-        mma_bf16(o[dt + 1], pf[kk], vf[2], vf[3]);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          mma_bf16(o[mt][dt], pf[mt][kk], vf[0], vf[1]);
+          mma_bf16(o[mt][dt + 1], pf[mt][kk], vf[2], vf[3]);
+        }
       }
     }
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
-    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
-  }
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      l[mt][h] += __shfl_xor_sync(0xffffffffu, l[mt][h], 1);
+      l[mt][h] += __shfl_xor_sync(0xffffffffu, l[mt][h], 2);
+    }
 
   // ---- merge the warps that shared rows, through shared memory (reuses the K/V stages)
   __syncthreads();
@@ -274,19 +310,21 @@ attention_mma_kernel(AttnArgs a) {
   float* red_m = red_o + WARPS_N * BM * D;          // [WARPS_N][BM]
   float* red_l = red_m + WARPS_N * BM;              // [WARPS_N][BM]
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int r = wm * 16 + (lane >> 2) + h * 8;
-    if ((lane & 3) == 0) {
-      red_m[wn * BM + r] = m[h];
-      red_l[wn * BM + r] = l[h];
-    }
+  for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) {
-      float* dst = red_o + ((long long)(wn * BM + r)) * D + i * 8 + (lane & 3) * 2;
-      dst[0] = o[i][h * 2 + 0];
-      dst[1] = o[i][h * 2 + 1];
+    for (int h = 0; h < 2; ++h) {
+      const int r = wm * WR + mt * 16 + (lane >> 2) + h * 8;
+      if ((lane & 3) == 0) {
+        red_m[wn * BM + r] = m[mt][h];
+        red_l[wn * BM + r] = l[mt][h];
+      }
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        float* dst = red_o + ((long long)(wn * BM + r)) * D + i * 8 + (lane & 3) * 2;
+        dst[0] = o[mt][i][h * 2 + 0];
+        dst[1] = o[mt][i][h * 2 + 1];
+      }
     }
-  }
   __syncthreads();
   const long long item = ((long long)tile * gridDim.y + kvh) * n_splits + split;
   for (int i = threadIdx.x; i < BM * CHUNKS; i += NT_THREADS) {
@@ -336,20 +374,30 @@ attention_mma_kernel(AttnArgs a) {
   if (!is_last) return;
   __threadfence();
   const long long item0 = ((long long)tile * gridDim.y + kvh) * n_splits;
+  // all log-sum-exps first, in one parallel pass, into shared memory (the K/V stages are free)
+  float* lse = reinterpret_cast<float*>(Ks);   // [n_splits][BM]
+  constexpr int LSE_CAPACITY = STAGES * BN * LDS * 2 * 2 / 4;
+  const bool lse_fits = n_splits * BM <= LSE_CAPACITY;
+  if (lse_fits) {
+    __syncthreads();  // everyone is done with red_o / red_m
+    for (int i = threadIdx.x; i < n_splits * BM; i += NT_THREADS) lse[i] = __ldcg(a.part_lse + item0 * BM + i);
+    __syncthreads();
+  }
   for (int i = threadIdx.x; i < BM * CHUNKS; i += NT_THREADS) {
     const int r = i / CHUNKS, c = i % CHUNKS;
     const int R = row0 + r;
     if (R >= n_rows) continue;
+    auto lse_at = [&](int z) { return lse_fits ? lse[z * BM + r] : __ldcg(a.part_lse + (item0 + z) * BM + r); };
     float M = -INFINITY;
-    for (int z = 0; z < n_splits; ++z) M = fmaxf(M, __ldcg(a.part_lse + (item0 + z) * BM + r));
+    for (int z = 0; z < n_splits; ++z) M = fmaxf(M, lse_at(z));
     float W = 0.0f, acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (M != -INFINITY) {
-      for (int z = 0; z < n_splits; ++z) {
-        const float w = exp2f(__ldcg(a.part_lse + (item0 + z) * BM + r) - M);
-        if (w == 0.0f) continue;
-        W += w;
+#pragma unroll 4
+      for (int z = 0; z < n_splits; ++z) {   // independent loads: several are in flight at once
+        const float w = exp2f(lse_at(z) - M);
         const float4* src = reinterpret_cast<const float4*>(a.part_o + ((item0 + z) * BM + r) * D + c * 8);
         const float4 lo = __ldcg(src), hi = __ldcg(src + 1);
+        W += w;
         acc[0] += w * lo.x; acc[1] += w * lo.y; acc[2] += w * lo.z; acc[3] += w * lo.w;
         acc[4] += w * hi.x; acc[5] += w * hi.y; acc[6] += w * hi.z; acc[7] += w * hi.w;
       }
@@ -366,19 +414,19 @@ attention_mma_kernel(AttnArgs a) {
   if (threadIdx.x == 0) *counter = 0;
 }
 
-template <int WARPS_M, int WARPS_N>
+template <int WARPS_M, int WARPS_N, int MT>
 constexpr size_t smem_bytes() {
-  constexpr int BM = 16 * WARPS_M;
+  constexpr int BM = 16 * MT * WARPS_M;
   constexpr int STAGES = WARPS_N > 1 ? 4 : 2;
   constexpr size_t tiles = (size_t)(BM + 2 * STAGES * BN) * LDS * 2;
   constexpr size_t merge = (size_t)BM * LDS * 2 + (size_t)WARPS_N * BM * (D + 2) * 4;
   return tiles > merge ? tiles : merge;
 }
 
-template <int WARPS_M, int WARPS_N>
+template <int WARPS_M, int WARPS_N, int MT>
 int launch(const AttnArgs& a, int n_tiles, int kv_heads, int n_splits, cudaStream_t stream) {
-  auto kern = attention_mma_kernel<WARPS_M, WARPS_N>;
-  constexpr size_t smem = smem_bytes<WARPS_M, WARPS_N>();
+  auto kern = attention_mma_kernel<WARPS_M, WARPS_N, MT>;
+  constexpr size_t smem = smem_bytes<WARPS_M, WARPS_N, MT>();
   static bool configured = false;
   if (!configured) {
     if (smem > 48 * 1024 &&
@@ -393,7 +441,12 @@ int launch(const AttnArgs& a, int n_tiles, int kv_heads, int n_splits, cudaStrea
 
 }  // namespace
 
+constexpr int PREFILL_MT = D <= 64 ? 2 : 1;   // row tiles per warp in the prefill shape
+
 extern "C" int llm_attention_head_dim() { return D; }
+
+// Rows of a tile in the prefill shape (the decode shape has 16).
+extern "C" int llm_attention_prefill_rows() { return 64 * PREFILL_MT; }
 
 // 32-bit words of scratch that `n_tiles` tiles of `rows_per_tile` rows need when split `n_splits`
 // ways: LLM_ATTENTION_COUNTER_WORDS counters (one per tile and kv head; they must be zero before
@@ -404,7 +457,7 @@ extern "C" long long llm_attention_scratch_floats(int n_tiles, int kv_heads, int
   return LLM_ATTENTION_COUNTER_WORDS + (long long)n_tiles * kv_heads * n_splits * rows_per_tile * (D + 1);
 }
 
-// rows_per_tile: 64 (prefill shape) or 16 (decode shape).  `scratch` (llm_attention_scratch_floats
+// rows_per_tile: llm_attention_prefill_rows() (prefill shape) or 16 (decode shape).  `scratch` (llm_attention_scratch_floats
 // words, its first LLM_ATTENTION_COUNTER_WORDS zero) is needed when n_splits > 1.
 extern "C" int llm_attention_mma(const void* q, void* out, void* k_base, void* v_base, const int32_t* block_table,
                                  long long page_stride, int table_stride, int page_tokens, int kv_heads,
@@ -434,8 +487,8 @@ extern "C" int llm_attention_mma(const void* q, void* out, void* k_base, void* v
   a.q_heads = q_heads;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.window = window;
-  if (rows_per_tile == 64) return launch<4, 1>(a, n_tiles, kv_heads, n_splits, stream);
-  if (rows_per_tile == 16) return launch<1, 4>(a, n_tiles, kv_heads, n_splits, stream);
+  if (rows_per_tile == 64 * PREFILL_MT) return launch<4, 1, PREFILL_MT>(a, n_tiles, kv_heads, n_splits, stream);
+  if (rows_per_tile == 16) return launch<1, 4, 1>(a, n_tiles, kv_heads, n_splits, stream);
   return ERR_BAD_SIZE;
 }
 
@@ -464,7 +517,7 @@ extern "C" int llm_attention_mma_static_scratch(const void* q, void* out, void* 
                                                 int n_splits, int q_heads, float scale, int window,
                                                 cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
-  if (n_splits < 1 || kv_heads < 1 || (rows_per_tile != 16 && rows_per_tile != 64)) return ERR_BAD_SIZE;
+  if (n_splits < 1 || kv_heads < 1 || (rows_per_tile != 16 && rows_per_tile != 64 * PREFILL_MT)) return ERR_BAD_SIZE;
   const long long need = llm_attention_scratch_floats(n_tiles, kv_heads, n_splits, rows_per_tile);
   if (n_splits > 1 && need > (long long)LLM_ATTENTION_STATIC_SCRATCH_FLOATS) return LLM_ERR_STATIC_SCRATCH_TOO_SMALL;
   int device = 0;

@@ -44,7 +44,7 @@ class ModelExecutor:
         logits = self.runner.step(entries)
         if logits is None:
             return []
-        return self.sampler.sample(logits, params, rngs)
+        return self.sampler.sample(logits, params, rngs, self.runner.argmax)
 
 
 class LLMEngine:

@@ -113,6 +113,8 @@ class StepRunner:
         self.use_cuda_graphs = use_cuda_graphs and model.graph_safe
         self._graphs: Dict[object, object] = {}
         self._seen = set()
+        self._iota = np.arange(self.max_step_tokens + 8, dtype=np.int32)
+        self.argmax = torch.zeros(self.max_step_tokens, dtype=torch.int32, device=self.device)   # per wanted row
         T, S, P, G = self.max_step_tokens, padded_batch(self.max_batch_seqs), cache.max_blocks, len(cache.groups)
         self._sizes = (T, S, P, G)
         total = 4 * T + 4 * S + G * S * P
@@ -183,12 +185,12 @@ class StepRunner:
             if length + n > self.cache.max_tokens:
                 raise EngineError(f"step: slot {e.slot} would hold {length + n} tokens, the cache holds "
                                   f"{self.cache.max_tokens} per request")
-            for t in e.tokens:
-                if not (0 <= int(t) < self.vocab):
-                    raise EngineError(f"step: token id {t} is outside the vocabulary (0..{self.vocab - 1})")
-            for w in e.want:
-                if not (0 <= int(w) < n):
-                    raise EngineError(f"step: wanted place {w} is outside the {n} tokens of slot {e.slot}")
+            if min(e.tokens) < 0 or max(e.tokens) >= self.vocab:
+                bad = next(t for t in e.tokens if not (0 <= int(t) < self.vocab))
+                raise EngineError(f"step: token id {bad} is outside the vocabulary (0..{self.vocab - 1})")
+            if e.want and (min(e.want) < 0 or max(e.want) >= n):
+                bad = next(w for w in e.want if not (0 <= int(w) < n))
+                raise EngineError(f"step: wanted place {bad} is outside the {n} tokens of slot {e.slot}")
             total += n
             n_want += len(e.want)
         if total > self.max_step_tokens:
@@ -212,12 +214,7 @@ class StepRunner:
         """Validates the batch, takes its pages, builds and sends the step's metadata and lets the
         parts plan; after this `self.ctx` describes the step.  Returns (pure decode step, wanted rows)."""
         total, n_want = self.validate(entries)
-        if not self.cache.can_reserve([(e.slot, len(e.tokens)) for e in entries]):
-            from ..errors import OutOfPages
-            raise OutOfPages("out of pages: the batch needs more pages than the pools have free "
-                             f"(free per group: {[g.pool.free_pages for g in self.cache.groups]})")
-        for e in entries:
-            self.cache.reserve(e.slot, len(e.tokens))
+        self.cache.reserve_batch([(e.slot, len(e.tokens)) for e in entries])     # all or nothing
         c = self.ctx
         n_seqs = len(entries)
         # a pure decode step (one token and its logits per request) is padded to a few fixed batch
@@ -228,23 +225,41 @@ class StepRunner:
         (tok_h, tok_d), (pos_h, pos_d), (rs_h, rs_d), (want_h, want_d) = self._row_views(rows)
         c.token_ids, c.positions, c.row_seq, c.want_rows = tok_d, pos_d, rs_d, want_d
         row = w = 0
-        c.host_q_len, c.host_kv_len = [], []
-        for s, e in enumerate(entries):
-            n = len(e.tokens)
-            length = self.cache.length(e.slot)
-            tok_h[row: row + n] = e.tokens
-            pos_h[row: row + n] = np.arange(length, length + n, dtype=np.int32)
-            rs_h[row: row + n] = s
-            for place in e.want:
-                want_h[w] = row + int(place)
-                w += 1
-            self._seq_slot[0][s] = e.slot
-            self._seq_q_start[0][s] = row
-            self._seq_q_len[0][s] = n
-            self._seq_kv_len[0][s] = length + n
-            c.host_q_len.append(n)
-            c.host_kv_len.append(length + n)
-            row += n
+        if all(len(e.tokens) == 1 for e in entries):
+            # one token per request (the decode step): fill whole arrays at once
+            lengths = [self.cache.lengths[e.slot] for e in entries]
+            tok_h[:n_seqs] = [e.tokens[0] for e in entries]
+            pos_h[:n_seqs] = lengths
+            rs_h[:n_seqs] = self._iota[:n_seqs]
+            self._seq_slot[0][:n_seqs] = [e.slot for e in entries]
+            self._seq_q_start[0][:n_seqs] = self._iota[:n_seqs]
+            self._seq_q_len[0][:n_seqs] = 1
+            c.host_kv_len = [k + 1 for k in lengths]
+            self._seq_kv_len[0][:n_seqs] = c.host_kv_len
+            c.host_q_len = [1] * n_seqs
+            for s, e in enumerate(entries):
+                if e.want:
+                    want_h[w] = s
+                    w += 1
+            row = n_seqs
+        else:
+            c.host_q_len, c.host_kv_len = [], []
+            for s, e in enumerate(entries):
+                n = len(e.tokens)
+                length = self.cache.length(e.slot)
+                tok_h[row: row + n] = e.tokens
+                pos_h[row: row + n] = np.arange(length, length + n, dtype=np.int32)
+                rs_h[row: row + n] = s
+                for place in e.want:
+                    want_h[w] = row + int(place)
+                    w += 1
+                self._seq_slot[0][s] = e.slot
+                self._seq_q_start[0][s] = row
+                self._seq_q_len[0][s] = n
+                self._seq_kv_len[0][s] = length + n
+                c.host_q_len.append(n)
+                c.host_kv_len.append(length + n)
+                row += n
         slots = [e.slot for e in entries]
         for gi in range(len(self.cache.groups)):
             self.cache.block_table_rows(gi, slots, self._tables[gi][0])
@@ -275,9 +290,17 @@ class StepRunner:
             return ("decode", c.n_seqs, plans)
         return ("general", tuple(c.host_q_len), tuple(tuple(e.want) for e in entries), plans)
 
+    def _forward(self, c: StepContext):
+        """The model's forward pass plus the argmax of every wanted row (greedy requests need
+        nothing else, so it rides in the same launch sequence or graph)."""
+        logits = self.model.forward(c)
+        if logits is not None:
+            K.argmax_rows(logits, self.argmax, c.n_want, c.stream)
+        return logits
+
     def _run(self, c: StepContext, decode: bool, entries):
         if not self.use_cuda_graphs:
-            return self.model.forward(c)
+            return self._forward(c)
         key = self._graph_key(c, decode, entries)
         held = self._graphs.get(key)
         if held is not None:
@@ -287,12 +310,12 @@ class StepRunner:
         if key not in self._seen or len(self._graphs) >= self.MAX_GRAPHS:
             if len(self._seen) < 4096:
                 self._seen.add(key)
-            return self.model.forward(c)          # first time: run directly (also sizes the workspace)
+            return self._forward(c)               # first time: run directly (also sizes the workspace)
         graph = torch.cuda.CUDAGraph()
         before = K.LAUNCHES[0]
         with torch.cuda.graph(graph):
             c.stream = torch.cuda.current_stream().cuda_stream
-            logits = self.model.forward(c)
+            logits = self._forward(c)
         launched = K.LAUNCHES[0] - before
         K.LAUNCHES[0] = before
         c.stream = torch.cuda.current_stream().cuda_stream

@@ -35,6 +35,7 @@ def lib(head_dim: int):
         l.llm_attention_mma.restype = c_int
         l.llm_attention_scratch_floats.argtypes = [I, I, I, I]
         l.llm_attention_scratch_floats.restype = c_longlong
+        l.llm_attention_prefill_rows.restype = c_int
         _libs[head_dim] = l
     return l
 
@@ -44,6 +45,7 @@ class AttentionPlan:
         self.head_dim, self.heads, self.kv_heads = head_dim, heads, kv_heads
         self.group = heads // kv_heads
         self.lib = lib(head_dim)
+        self.prefill_rows = int(self.lib.llm_attention_prefill_rows())
         self._host = None
         self._dev = None
         self._scratch = None
@@ -52,7 +54,7 @@ class AttentionPlan:
         """Pinned and device int32 buffers for the tile list, sized once for the largest step so
         that their addresses never change (captured CUDA graphs keep them)."""
         if self._host is None or self._host.numel() < 2 * n:
-            most = -(-ctx.max_rows * self.group // 16) + ctx.max_seqs + 8
+            most = -(-ctx.max_rows * self.group // 64) + ctx.max_seqs + 8
             cap = 2 * max(n, most)
             self._host = torch.empty(cap, dtype=torch.int32).pin_memory()
             self._dev = torch.empty(cap, dtype=torch.int32, device=device)
@@ -79,7 +81,7 @@ def step_tiles(ctx, plan: AttentionPlan):
     if cached is not None:
         return cached
     g = plan.group
-    rows_per_tile = 16 if ctx.max_q_len * g <= 16 else 64
+    rows_per_tile = 16 if ctx.max_q_len * g <= 16 else plan.prefill_rows
     counts = [-(-q * g // rows_per_tile) for q in ctx.host_q_len]
     pad = ctx.pad_seqs if rows_per_tile == 16 else 0     # padded decode steps keep a fixed grid
     n_tiles = sum(counts) + pad

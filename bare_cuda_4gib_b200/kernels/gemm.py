@@ -110,13 +110,13 @@ def token_tile(rows: int) -> int:
 
 def choose_splits(rows: int, n: int, k: int, bn: int) -> int:
     """How many thread blocks share the K range of one output tile: enough to put about two
-    blocks on every SM, at least four 64-wide K blocks each, and partial results (written and
-    read back in float32) of at most a quarter of the weight bytes."""
+    blocks on every SM, at least four 64-wide K blocks each, and partial results (float32, written
+    and read back through the L2 cache, not HBM) of at most about the weight's own bytes."""
     if rows > SPLIT_MAX_ROWS:
         return 1
     tiles = -(-n // BM) * -(-rows // bn)
     k_blocks = -(-k // BK)
-    splits = min(k_blocks // 4, TARGET_BLOCKS // tiles, max(1, k // (16 * rows)))
+    splits = min(k_blocks // 4, TARGET_BLOCKS // tiles, max(1, k // (4 * rows)))
     splits = max(1, splits)
     per = -(-k_blocks // splits)
     return -(-k_blocks // per)

@@ -56,10 +56,17 @@ class DeviceSampler:
         self._out = torch.empty(max_rows, dtype=torch.int32, device=device)
         self._out_host = torch.empty(max_rows, dtype=torch.int32).pin_memory()
 
-    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], rngs: Sequence) -> List[int]:
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], rngs: Sequence,
+               argmax: Optional[torch.Tensor] = None) -> List[int]:
+        """`argmax` (optional): the rows' argmax already computed on the device; a batch of greedy
+        requests then needs one small download and nothing else."""
         from ..kernels import lib as K
 
         rows = len(params)
+        if argmax is not None and all(p.greedy() for p in params):
+            self._out_host[:rows].copy_(argmax[:rows], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            return self._out_host[:rows].tolist()
         temps, uniforms = self._host[:rows].numpy(), self._host[self.max_rows: self.max_rows + rows].numpy()
         host_rows = []
         for r, (p, rng) in enumerate(zip(params, rngs)):
