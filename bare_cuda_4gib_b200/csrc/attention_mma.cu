@@ -68,6 +68,14 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// 2^x for softmax weights: the hardware approximation (relative error about 2^-22, far below the
+// bfloat16 rounding of the probabilities that follows); -inf gives 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -125,6 +133,11 @@ attention_mma_kernel(AttnArgs a) {
   const int last_token = min(q_len - 1, (row0 + BM - 1) / group);
   const int first_token = row0 / group;
   const int hi_key = pos0 + last_token;  // newest visible key of any row
+  // positions of the tile's valid rows: [tile_min_pos, tile_max_pos].  Rows past the request's
+  // last packed row are never stored, so it does not matter what they "see" in unmasked blocks
+  // (their queries are zero, their scores finite).
+  const int tile_min_pos = pos0 + first_token;
+  const int tile_max_pos = pos0 + last_token;
   int lo_key = 0;
   if (a.window > 0) lo_key = max(0, pos0 + first_token - a.window + 1);
   const int kb_lo = lo_key / BN, kb_hi = hi_key / BN;  // inclusive
@@ -147,31 +160,44 @@ attention_mma_kernel(AttnArgs a) {
 
   const __nv_bfloat16* kc = reinterpret_cast<const __nv_bfloat16*>(a.cache.k);
   const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(a.cache.v);
-  // Page lookups: a key block lies in one page (pages of 64 positions or more) or spans 64 / page
-  // pages.  With a power-of-two page size the position is split with a shift and a mask.
+  // Page lookups.  When a page holds a multiple of 64 positions, a key block lies inside one page:
+  // one table entry per block, and each thread's offsets inside the block never change.  Smaller
+  // pages are looked up per row.
   const int page_tokens = a.cache.page_tokens;
-  const int page_shift = (page_tokens & (page_tokens - 1)) == 0 ? __ffs(page_tokens) - 1 : -1;
+  const bool block_in_page = (page_tokens % BN) == 0;
   const int32_t* table_row = a.cache.block_table + (long long)seq * a.cache.table_stride;
   const long long head_offset = (long long)kvh * page_tokens * D;
+  constexpr int LOADS = (BN * CHUNKS + NT_THREADS - 1) / NT_THREADS;   // 16-byte chunks per thread and block
   // copies block kb into its stage (nothing if kb is past the end) and closes one cp.async group
   auto load_block = [&](int kb, int stage) {
-    __nv_bfloat16* ks = Ks + stage * BN * LDS;
-    __nv_bfloat16* vs = Vs + stage * BN * LDS;
-    for (int i = threadIdx.x; kb < kb_end && i < BN * CHUNKS; i += NT_THREADS) {
-      const int r = i / CHUNKS, c = i % CHUNKS;
-      const int key = kb * BN + r;
-      long long src = 0;
-      bool valid = key < kv_len;
-      if (valid) {
-        const int block = page_shift >= 0 ? key >> page_shift : key / page_tokens;
-        const int in_page = page_shift >= 0 ? key & (page_tokens - 1) : key % page_tokens;
-        const int page = __ldg(table_row + block);
-        valid = page >= 0;
-        src = (long long)page * a.cache.page_stride + head_offset + (long long)in_page * D + c * 8;
+    if (kb < kb_end) {
+      __nv_bfloat16* ks = Ks + stage * BN * LDS;
+      __nv_bfloat16* vs = Vs + stage * BN * LDS;
+      const int key0 = kb * BN;
+      long long block_base = -1;
+      if (block_in_page) {
+        const int page = __ldg(table_row + key0 / page_tokens);
+        if (page >= 0) block_base = (long long)page * a.cache.page_stride + head_offset + (long long)(key0 % page_tokens) * D;
       }
-      if (!valid) src = 0;
-      cp_async16(ks + r * LDS + c * 8, kc + src, valid);
-      cp_async16(vs + r * LDS + c * 8, vc + src, valid);
+#pragma unroll
+      for (int j = 0; j < LOADS; ++j) {
+        const int i = threadIdx.x + j * NT_THREADS;
+        if (BN * CHUNKS % NT_THREADS != 0 && i >= BN * CHUNKS) break;
+        const int r = i / CHUNKS, c = i % CHUNKS;
+        long long src = 0;
+        bool valid = key0 + r < kv_len;
+        if (block_in_page) {
+          valid = valid && block_base >= 0;
+          if (valid) src = block_base + r * D + c * 8;
+        } else if (valid) {
+          const int key = key0 + r;
+          const int page = __ldg(table_row + key / page_tokens);
+          valid = page >= 0;
+          if (valid) src = (long long)page * a.cache.page_stride + head_offset + (long long)(key % page_tokens) * D + c * 8;
+        }
+        cp_async16(ks + r * LDS + c * 8, kc + src, valid);
+        cp_async16(vs + r * LDS + c * 8, vc + src, valid);
+      }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -234,21 +260,35 @@ attention_mma_kernel(AttnArgs a) {
       }
     }
 
+    // a block wholly below every row's position and inside every row's window needs no mask
+    const bool all_visible = kb * BN + BN - 1 <= tile_min_pos && (a.window <= 0 || kb * BN > tile_max_pos - a.window);
     uint32_t pf[MT][NT / 2][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
       // scale, mask, running maximum
       float mx[2] = {-INFINITY, -INFINITY};
+      if (all_visible) {
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
+        for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int h = e >> 1;
-          const int key = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-          const bool visible = key <= row_pos[mt][h] && (a.window <= 0 || key > row_pos[mt][h] - a.window);
-          const float v = visible ? s[mt][nt][e] * a.scale_log2 : -INFINITY;
-          s[mt][nt][e] = v;
-          mx[h] = fmaxf(mx[h], v);
+          for (int e = 0; e < 4; ++e) {
+            const float v = s[mt][nt][e] * a.scale_log2;
+            s[mt][nt][e] = v;
+            mx[e >> 1] = fmaxf(mx[e >> 1], v);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int h = e >> 1;
+            const int key = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+            const bool visible = key <= row_pos[mt][h] && (a.window <= 0 || key > row_pos[mt][h] - a.window);
+            const float v = visible ? s[mt][nt][e] * a.scale_log2 : -INFINITY;
+            s[mt][nt][e] = v;
+            mx[h] = fmaxf(mx[h], v);
+          }
         }
       }
       float corr[2], m_use[2];
@@ -258,22 +298,25 @@ attention_mma_kernel(AttnArgs a) {
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
         const float m_new = fmaxf(m[mt][h], mx[h]);
         m_use[h] = m_new == -INFINITY ? 0.0f : m_new;
-        corr[h] = exp2f(m[mt][h] - m_use[h]);  // m = -inf gives 0
+        corr[h] = fast_exp2(m[mt][h] - m_use[h]);  // m = -inf gives 0; an unchanged maximum gives exactly 1
         m[mt][h] = m_new;
         l[mt][h] *= corr[h];
       }
+      // most blocks leave every row's maximum where it was: nothing to rescale then
+      if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {
 #pragma unroll
-      for (int i = 0; i < D / 8; ++i) {
-        o[mt][i][0] *= corr[0];
-        o[mt][i][1] *= corr[0];
-        o[mt][i][2] *= corr[1];
-        o[mt][i][3] *= corr[1];
+        for (int i = 0; i < D / 8; ++i) {
+          o[mt][i][0] *= corr[0];
+          o[mt][i][1] *= corr[0];
+          o[mt][i][2] *= corr[1];
+          o[mt][i][3] *= corr[1];
+        }
       }
       // probabilities, as A fragments for P V
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        const float p0 = exp2f(s[mt][nt][0] - m_use[0]), p1 = exp2f(s[mt][nt][1] - m_use[0]);
-        const float p2 = exp2f(s[mt][nt][2] - m_use[1]), p3 = exp2f(s[mt][nt][3] - m_use[1]);
+        const float p0 = fast_exp2(s[mt][nt][0] - m_use[0]), p1 = fast_exp2(s[mt][nt][1] - m_use[0]);
+        const float p2 = fast_exp2(s[mt][nt][2] - m_use[1]), p3 = fast_exp2(s[mt][nt][3] - m_use[1]);
         l[mt][0] += p0 + p1;
         l[mt][1] += p2 + p3;
         pf[mt][nt / 2][(nt & 1) * 2 + 0] = pack_bf16(p0, p1);

@@ -20,9 +20,10 @@
 // the result does not depend on timing.
 //
 // MODE 1 (SwiGLU): w is [gate rows; up rows] and the block stores silu(gate) * up.  ORIENT 0
-// accumulates gate and up for the same 128 features in two accumulators; ORIENT 1 loads BN/2 gate
-// rows and the matching BN/2 up rows as one N operand, so a thread finds gate in column c and up
-// in column BN/2 + c.
+// makes its 128 MMA rows of 64 gate rows and the matching 64 up rows, so the accumulator holds
+// gate in lanes 0..63 and up in lanes 64..127; the two epilogue warps that own the up lanes hand
+// their values over through shared memory.  ORIENT 1 loads BN/2 gate rows and the matching BN/2
+// up rows as one N operand, so a thread finds gate in column c and up in column BN/2 + c.
 //
 // Warps: 0 = TMA producer, 1 = tensor memory allocation + MMA issue, 2..5 = epilogue.
 // Every wait on an mbarrier is bounded: after about a second without progress the thread sets
@@ -143,7 +144,7 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
 // 256, so that the number of tiles can be matched to the number of SMs).
 struct Geometry {
   int bn;           // MMA N: tokens (ORIENT 0) or weight rows (ORIENT 1) per tile
-  int a_tiles;      // 128-row operand tiles per stage (2 for ORIENT 0 SwiGLU)
+  int a_tiles;      // 128-row operand tiles per stage
   int b_bytes;      // bytes of the N operand tile
   int stage_bytes;
   int stages;
@@ -157,7 +158,7 @@ constexpr int MAX_STAGES = 8;
 static Geometry make_geometry(int bn, int mode, int orient, int blocks_per_sm) {
   Geometry g;
   g.bn = bn;
-  g.a_tiles = (mode == 1 && orient == 0) ? 2 : 1;
+  g.a_tiles = 1;
   g.b_bytes = bn * BK * 2;
   g.stage_bytes = g.a_tiles * A_BYTES + g.b_bytes;
   const int budget = (blocks_per_sm == 2 ? 110 : 200) * 1024;
@@ -188,8 +189,9 @@ gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // ORIENT 0: 128 features x BN tokens.  ORIENT 1: 128 tokens x BN features (MODE 1: BN/2 outputs).
-  const int F_TILE = ORIENT == 0 ? BM : (MODE == 1 ? BN / 2 : BN);
+  // ORIENT 0: 128 features (MODE 1: 64 outputs) x BN tokens.  ORIENT 1: 128 tokens x BN features
+  // (MODE 1: BN/2 outputs).
+  const int F_TILE = ORIENT == 0 ? (MODE == 1 ? BM / 2 : BM) : (MODE == 1 ? BN / 2 : BN);
   const int f0 = blockIdx.x * F_TILE;
   const int t0 = blockIdx.y * (ORIENT == 0 ? BN : BM);
   const int kb_begin = blockIdx.z * k_blocks_per_split;
@@ -204,8 +206,8 @@ gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_
     mbar_expect_tx(&full_bar[s], geo.stage_bytes);
     const int k0 = (kb_begin + i) * BK;
     if (ORIENT == 0) {
-      tma_load_2d(stage, &map_w, &full_bar[s], k0, f0);
-      if (MODE == 1) tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], k0, up_row_offset + f0);
+      tma_load_2d(stage, &map_w, &full_bar[s], k0, f0);   // MODE 1: map_w's box has 64 rows
+      if (MODE == 1) tma_load_2d(stage + A_BYTES / 2, &map_w, &full_bar[s], k0, up_row_offset + f0);
     } else {
       uint8_t* b_tile = stage + A_BYTES;
       tma_load_2d(b_tile, &map_w, &full_bar[s], k0, f0);
@@ -302,10 +304,6 @@ gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_
           const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
           const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);
           umma_bf16(tmem_base, desc_a + koff, desc_b + koff, idesc, acc);
-          if (MODE == 1 && ORIENT == 0) {
-            const uint64_t desc_up = smem_desc_sw128(a_addr + A_BYTES);
-            umma_bf16(tmem_base + BN, desc_up + koff, desc_b + koff, idesc, acc);
-          }
         }
         umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
         if (++s == geo.stages) { s = 0; phase ^= 1; }
@@ -320,32 +318,78 @@ gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_
       *abort_flag = 1;
       atomicCAS(error_word, 0, ERR_TIMEOUT_EPILOGUE);
     }
-    ok = ok && !*abort_flag;
+    asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps agree on whether to go on
+    ok = !*abort_flag;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok) {
       const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
       float* out_f32 = reinterpret_cast<float*>(out) + (long long)blockIdx.z * partial_stride;
       __nv_bfloat16* out_bf16 = reinterpret_cast<__nv_bfloat16*>(out) + (long long)blockIdx.z * partial_stride;
-      if (ORIENT == 0) {
+      if (ORIENT == 0 && MODE == 1) {
+        // lanes 0..63 hold gate, lanes 64..127 up, for the block's 64 output features: the up warps
+        // park their values in shared memory (the pipeline stages are idle by now), [token][feature]
+        float* handover = reinterpret_cast<float*>(smem);
+        const int l64 = (quad & 1) * 32 + lane;
+        if (quad >= 2) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 16) {
+            if (t0 + c0 >= n_tokens) break;
+            uint32_t u[16];
+            if (n_kb > 0) {
+              tmem_load16(lane_base + c0, u);
+              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) u[j] = 0u;
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) handover[(c0 + j) * 64 + l64] = __uint_as_float(u[j]);
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
+        if (quad < 2) {
+          const int f = f0 + l64;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 16) {
+            if (t0 + c0 >= n_tokens) break;
+            uint32_t g[16];
+            if (n_kb > 0) {
+              tmem_load16(lane_base + c0, g);
+              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) g[j] = 0u;
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int t = t0 + c0 + j;
+              if (t < n_tokens && f < n_features) {
+                const float gate = __uint_as_float(g[j]);
+                const float v = gate / (1.0f + expf(-gate)) * handover[(c0 + j) * 64 + l64];
+                if (out_is_f32) out_f32[(long long)t * ld_out + f] = v;
+                else out_bf16[(long long)t * ld_out + f] = __float2bfloat16_rn(v);
+              }
+            }
+          }
+        }
+      } else if (ORIENT == 0) {
         const int f = f0 + quad * 32 + lane;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
           if (t0 + c0 >= n_tokens) break;  // uniform across the warp
-          uint32_t g[16], u[16];
+          uint32_t g[16];
           if (n_kb > 0) {
             tmem_load16(lane_base + c0, g);
-            if (MODE == 1) tmem_load16(lane_base + BN + c0, u);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) g[j] = u[j] = 0u;
+            for (int j = 0; j < 16; ++j) g[j] = 0u;
           }
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int t = t0 + c0 + j;
             if (t < n_tokens && f < n_features) {
-              float v = __uint_as_float(g[j]);
-              if (MODE == 1) v = v / (1.0f + expf(-v)) * __uint_as_float(u[j]);
+              const float v = __uint_as_float(g[j]);
               if (out_is_f32) out_f32[(long long)t * ld_out + f] = v;
               else out_bf16[(long long)t * ld_out + f] = __float2bfloat16_rn(v);
             }
@@ -447,7 +491,7 @@ int launch(int bn, const CUtensorMap* map_w, const CUtensorMap* map_a, void* out
   }
   const int k_blocks = (K + BK - 1) / BK;
   const int per_split = (k_blocks + splits - 1) / splits;
-  const int f_tile = ORIENT == 0 ? BM : (MODE == 1 ? bn / 2 : bn);
+  const int f_tile = ORIENT == 0 ? (MODE == 1 ? BM / 2 : BM) : (MODE == 1 ? bn / 2 : bn);
   const int t_tile = ORIENT == 0 ? bn : BM;
   dim3 grid((n_features + f_tile - 1) / f_tile, (n_tokens + t_tile - 1) / t_tile, splits);
   if (grid.y > 65535 || grid.z > 65535) return ERR_BAD_SIZE;
@@ -481,7 +525,7 @@ extern "C" int llm_gemm_tensor_map(void* map_out, const void* base, long long ro
 // out[z][t, f] (z < splits) = partial sums of act[t, :] . w[f, :]; mode 1: silu(gate) * up with
 // w = [gate; up], the up rows starting at `up_row_offset` (splits must be 1 then).
 // `bn` is the N tile, a multiple of 16 up to 256 (of 32 for orient 1 with mode 1).
-// orient 0: bn tokens per tile; map_a's box must have bn rows, map_w's 128.
+// orient 0: bn tokens per tile; map_a's box must have bn rows, map_w's 128 (64 in mode 1).
 // orient 1: bn weight rows per tile; map_a's box must have 128 rows, map_w's bn rows (bn / 2 in mode 1).
 extern "C" int llm_gemm_bf16(const void* map_w, const void* map_a, void* out, int out_dtype, int n_tokens,
                              int n_features, int K, long long ld_out, long long partial_stride, int splits,
@@ -502,7 +546,7 @@ extern "C" int llm_gemm_bf16(const void* map_w, const void* map_a, void* out, in
   // of half the pipeline depth each: worth it only when there are more tiles than SMs and at
   // least three stages still fit (two for the SwiGLU tiles, whose long epilogue gains most).
   const Geometry two = make_geometry(bn, mode, orient, 2);
-  const long long f_tile = orient == 0 ? BM : (mode == 1 ? bn / 2 : bn), t_tile = orient == 0 ? bn : BM;
+  const long long f_tile = orient == 0 ? (mode == 1 ? BM / 2 : BM) : (mode == 1 ? bn / 2 : bn), t_tile = orient == 0 ? bn : BM;
   const long long tiles = ((n_features + f_tile - 1) / f_tile) * ((n_tokens + t_tile - 1) / t_tile) * splits;
   const bool pair = tiles > 148 && two.tmem_cols <= 256 && two.stages >= ((orient == 1 && mode == 1) ? 2 : 3);
 #define GEMM_CASE(MODE_, ORIENT_)                                                                            \

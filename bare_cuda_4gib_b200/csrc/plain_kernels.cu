@@ -343,6 +343,66 @@ rope_cache_write_kernel(const TI* __restrict__ qkv, int n_partials, long long pa
   }
 }
 
+// The same for many tokens of a bfloat16 step: one thread rotates eight neighbouring pairs with
+// 16-byte loads and stores (head sizes that are multiples of 16, one finished input, no partials).
+__global__ void __launch_bounds__(256)
+rope_cache_write_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out, PagedCache cache,
+                            const int32_t* __restrict__ positions, const int32_t* __restrict__ row_seq,
+                            const float* __restrict__ inv_freq, int q_heads, int write_cache, int n_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int d = cache.head_dim, half = d / 2;
+  const int groups = half / 8;                         // 8-pair groups per rotated head
+  const int n_heads = q_heads + 2 * cache.kv_heads;
+  const int per_token = (q_heads + cache.kv_heads) * groups + cache.kv_heads * (d / 8);
+  const long long total = (long long)n_tokens * per_token;
+  for (long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x; item < total;
+       item += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(item / per_token);
+    int w = (int)(item % per_token);
+    const int pos = positions[t];
+    const __nv_bfloat16* row = qkv + (long long)t * n_heads * d;
+    const int rotated = (q_heads + cache.kv_heads) * groups;
+    if (w < rotated) {
+      const int h = w / groups, p0 = (w % groups) * 8;
+      __nv_bfloat16* dst;
+      if (h < q_heads) {
+        dst = q_out + ((long long)t * q_heads + h) * d;
+      } else {
+        if (!write_cache) continue;
+        const long long off = cache_offset(cache, row_seq[t], pos, h - q_heads);
+        if (off < 0) continue;
+        dst = (__nv_bfloat16*)cache.k + off;
+      }
+      const uint4 lo_raw = *reinterpret_cast<const uint4*>(row + (long long)h * d + p0);
+      const uint4 hi_raw = *reinterpret_cast<const uint4*>(row + (long long)h * d + half + p0);
+      const __nv_bfloat16* lo = reinterpret_cast<const __nv_bfloat16*>(&lo_raw);
+      const __nv_bfloat16* hi = reinterpret_cast<const __nv_bfloat16*>(&hi_raw);
+      uint4 lo_out, hi_out;
+      __nv_bfloat16* lo_o = reinterpret_cast<__nv_bfloat16*>(&lo_out);
+      __nv_bfloat16* hi_o = reinterpret_cast<__nv_bfloat16*>(&hi_out);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float c = 1.0f, s = 0.0f;
+        if (inv_freq) sincosf((float)pos * inv_freq[p0 + j], &s, &c);
+        const float a = __bfloat162float(lo[j]), b = __bfloat162float(hi[j]);
+        lo_o[j] = __float2bfloat16_rn(a * c - b * s);
+        hi_o[j] = __float2bfloat16_rn(b * c + a * s);
+      }
+      *reinterpret_cast<uint4*>(dst + p0) = lo_out;
+      *reinterpret_cast<uint4*>(dst + half + p0) = hi_out;
+    } else {
+      if (!write_cache) continue;
+      w -= rotated;
+      const int kvh = w / (d / 8), c0 = (w % (d / 8)) * 8;
+      const long long off = cache_offset(cache, row_seq[t], pos, kvh);
+      if (off < 0) continue;
+      *reinterpret_cast<uint4*>((__nv_bfloat16*)cache.v + off + c0) =
+          *reinterpret_cast<const uint4*>(row + (long long)(q_heads + cache.kv_heads + kvh) * d + c0);
+    }
+  }
+}
+
 extern "C" int llm_rope_cache_write(const void* qkv, int in_dtype, int n_partials,
                                     long long partial_stride, void* q_out, int out_dtype, void* k_base,
                                     void* v_base, const int32_t* block_table, long long page_stride,
@@ -354,6 +414,15 @@ extern "C" int llm_rope_cache_write(const void* qkv, int in_dtype, int n_partial
   if (head_dim % 2) return ERR_BAD_SIZE;
   PagedCache c{k_base, v_base, block_table, page_stride, table_stride, page_tokens, kv_heads, head_dim};
   const int n_heads = q_heads + 2 * kv_heads;
+  const auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (in_dtype == DT_BF16 && out_dtype == DT_BF16 && n_partials == 1 && head_dim % 16 == 0 && n_tokens >= 64 &&
+      aligned16(qkv) && aligned16(q_out) && aligned16(k_base) && aligned16(v_base)) {
+    const long long items = (long long)n_tokens * ((q_heads + kv_heads) * (head_dim / 16) + kv_heads * (head_dim / 8));
+    const int blocks = (int)((items + 255) / 256 < 148 * 8 ? (items + 255) / 256 : 148 * 8);
+    launch_kernel(rope_cache_write_vec_kernel, blocks, 256, 0, stream, (const __nv_bfloat16*)qkv,
+                  (__nv_bfloat16*)q_out, c, positions, row_seq, inv_freq, q_heads, write_cache, n_tokens);
+    return launch_status();
+  }
   dim3 grid(n_tokens, (n_heads + ROPE_HEADS_PER_BLOCK - 1) / ROPE_HEADS_PER_BLOCK);
   if (grid.y > 65535) return ERR_BAD_SIZE;
 #define LAUNCH_ROPE(TI, TO)                                                                   \
@@ -522,9 +591,20 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, int32_t* __
   const float* row = logits + (long long)blockIdx.x * vocab;
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float v = row[i];
-    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+  if ((vocab & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    for (int i = threadIdx.x; i < vocab / 4; i += blockDim.x) {
+      const float4 q = row4[i];
+      const float v[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (v[j] > bv || (v[j] == bv && 4 * i + j < bi)) { bv = v[j]; bi = 4 * i + j; }
+    }
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      const float v = row[i];
+      if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
   }
   auto better = [](float v, int i, float w, int j) { return v > w || (v == w && i < j); };
 #pragma unroll
@@ -553,7 +633,7 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, int32_t* __
 extern "C" int llm_argmax_rows(const float* logits, int32_t* out, int rows, int vocab,
                                cudaStream_t stream) {
   if (rows <= 0) return 0;
-  launch_kernel(argmax_rows_kernel, rows, 256, 0, stream, logits, out, vocab);
+  launch_kernel(argmax_rows_kernel, rows, 1024, 0, stream, logits, out, vocab);
   return launch_status();
 }
 
@@ -623,7 +703,7 @@ __global__ void sample_rows_kernel(const float* __restrict__ logits,
 extern "C" int llm_sample_rows(const float* logits, const float* temperature, const float* uniform,
                                int32_t* out, int rows, int vocab, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  launch_kernel(argmax_rows_kernel, rows, 256, 0, stream, logits, out, vocab);
+  launch_kernel(argmax_rows_kernel, rows, 1024, 0, stream, logits, out, vocab);
   launch_kernel(sample_rows_kernel, rows, 256, 0, stream, logits, temperature, uniform, out, vocab);
   return launch_status();
 }

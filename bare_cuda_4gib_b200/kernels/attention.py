@@ -3,6 +3,7 @@ size, the per-step list of row tiles, and the choice of how many thread blocks s
 
 from __future__ import annotations
 
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Dict, Optional
 
@@ -99,6 +100,8 @@ def step_tiles(ctx, plan: AttentionPlan):
     if rows_per_tile == 16:
         key_blocks = -(-ctx.max_kv_len // KEY_BLOCK)
         n_splits = max(1, min(key_blocks, -(-TARGET_BLOCKS // (n_tiles * plan.kv_heads))))
+        if os.environ.get("BARE_CUDA_B200_ATTN_SPLITS"):     # experiments only
+            n_splits = min(key_blocks, int(os.environ["BARE_CUDA_B200_ATTN_SPLITS"]))
         if n_tiles * plan.kv_heads > COUNTER_WORDS:
             n_splits = 1
     out = (dev[:n_tiles], dev[n_tiles: 2 * n_tiles], n_tiles, rows_per_tile, n_splits)

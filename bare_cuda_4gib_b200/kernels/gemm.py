@@ -169,18 +169,18 @@ def run(ctx, plan: GemmPlan, a: torch.Tensor, rows: int, out_dtype: torch.dtype,
     bn = token_tile(rows)
     if swiglu:
         inter = plan.n // 2
-        tiles = -(-inter // BM) * -(-rows // bn)
-        if tiles * 2 >= 148 or rows > SPLIT_MAX_ROWS:
-            out = ctx.ws.get(buffer, (rows, inter), out_dtype)
-            _check(l.llm_gemm_bf16(ctypes.addressof(plan.map_w), ctypes.addressof(plan.act_map(a, bn)),
-                                   out.data_ptr(), DT_BF16 if out_dtype == torch.bfloat16 else DT_F32, rows,
-                                   inter, plan.k, out.stride(0), 0, 1, bn, 1, 0, inter, err.data_ptr(), ctx.stream),
-                   "gemm_tcgen05 (swiglu)")
+        out = ctx.ws.get(buffer, (rows, inter), out_dtype)
+        if -(-inter // (BM // 2)) * -(-rows // bn) >= N_SMS:
+            # 64 gate rows and the matching 64 up rows share a block's 128 MMA rows: SwiGLU in the
+            # epilogue and no partial results, when that alone gives every SM a block
+            _check(l.llm_gemm_bf16(ctypes.addressof(plan.weight_map(BM // 2)), ctypes.addressof(plan.act_map(a, bn)),
+                                   out.data_ptr(), code, rows, inter, plan.k, out.stride(0), 0, 1, bn, 1, 0, inter,
+                                   err.data_ptr(), ctx.stream), "gemm_tcgen05 (swiglu)")
             return Partials(out)
-        # few tiles: stream [gate; up] as one product split over K, then reduce inside SwiGLU
+        # a narrow feed-forward: stream [gate; up] as one product split over K so that every SM takes
+        # part, and add the partial results inside the SwiGLU kernel
         from . import lib as K
         full = run(ctx, plan, a, rows, torch.float32, buffer + ".gate_up", True, False)
-        out = ctx.ws.get(buffer, (rows, inter), out_dtype)
         K.swiglu(full, out, rows, ctx.stream)
         return Partials(out)
     splits = choose_splits(rows, plan.n, plan.k, bn) if (allow_partials and out_dtype == torch.float32) else 1

@@ -92,26 +92,29 @@ def _rope_ref(x, pos, inv_freq):
     return torch.cat([lo * c - hi * s, hi * c + lo * s], -1)
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_rope_cache_write_and_attention_plain(dtype):
-    """Rotation + cache write, then attention over scrambled pages with a window, against dense math."""
+@pytest.mark.parametrize("dtype,lens", [(torch.float32, [21, 5]), (torch.bfloat16, [21, 5]), (torch.bfloat16, [75, 8])])
+def test_rope_cache_write_and_attention_plain(dtype, lens):
+    """Rotation + cache write, then attention over scrambled pages with a window, against dense math
+    (75 + 8 tokens of one finished bfloat16 input take the vector kernel)."""
     from bare_cuda_4gib_b200.kernels import lib as K
     heads, kv_heads, d, page, window = 6, 2, 48, 8, 13
-    lens = [21, 5]      # two sequences, fed whole
-    storage, table, view = _paged_cache(kv_heads, d, page, 12, dtype)
-    pages = list(range(12))
+    storage, table, view = _paged_cache(kv_heads, d, page, 14, dtype)
+    pages = list(range(14))
     random.Random(3).shuffle(pages)
-    table[0, :3] = torch.tensor(pages[:3], dtype=torch.int32)
-    table[1, :1] = torch.tensor(pages[3:4], dtype=torch.int32)
+    n0 = -(-lens[0] // page)
+    table[0, :n0] = torch.tensor(pages[:n0], dtype=torch.int32)
+    table[1, :1] = torch.tensor(pages[n0: n0 + 1], dtype=torch.int32)
     n = sum(lens)
     positions = torch.tensor(list(range(lens[0])) + list(range(lens[1])), dtype=torch.int32, device=DEV)
     row_seq = torch.tensor([0] * lens[0] + [1] * lens[1], dtype=torch.int32, device=DEV)
     width = (heads + 2 * kv_heads) * d
-    qkv = torch.randn(2, n, width, device=DEV).to(dtype)          # two partial results
+    parts = 1 if n >= 64 else 2                                    # partial results (one: the vector kernel)
+    qkv = torch.randn(parts, n, width, device=DEV).to(dtype)
     inv_freq = (1.0 / (10000.0 ** (torch.arange(d // 2, dtype=torch.float32) * 2.0 / d))).to(DEV)
     q = torch.empty(n, heads * d, device=DEV, dtype=dtype)
-    K.rope_cache_write(K.Partials(qkv, 2), q, view, positions, row_seq, inv_freq, heads, True, n)
-    full = qkv.float().sum(0) if dtype == torch.float32 else (qkv[0].float() + qkv[1].float())
+    K.rope_cache_write(K.Partials(qkv, parts) if parts > 1 else K.Partials(qkv[0]), q, view, positions, row_seq,
+                       inv_freq, heads, True, n)
+    full = qkv.float().sum(0)
     qr = _rope_ref(full[:, : heads * d].view(n, heads, d), positions, inv_freq)
     kr = _rope_ref(full[:, heads * d: (heads + kv_heads) * d].view(n, kv_heads, d), positions, inv_freq)
     vr = full[:, (heads + kv_heads) * d:].view(n, kv_heads, d).double()
