@@ -237,7 +237,7 @@ class CacheManager:
         k_ptr = g.storage.data_ptr() + j * g.cache_elems * esize
         v_ptr = k_ptr + (g.cache_elems // 2) * esize
         return CacheView(k_ptr, v_ptr, block_table, g.page_stride, block_table.stride(0), g.page_tokens,
-                         g.request.kv_heads, g.request.head_dim, g.dtype)
+                         g.request.kv_heads, g.request.head_dim, g.dtype, g.storage.data_ptr(), g.storage.numel())
 
     # ------------------------------------------------------------------ accounting
     def pages_in_use(self) -> List[int]:

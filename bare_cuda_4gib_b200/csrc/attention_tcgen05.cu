@@ -1,0 +1,606 @@
+// Paged flash attention for prefill portions on the Blackwell tensor cores: both matrix products
+// of attention are tcgen05.mma with their accumulators in tensor memory.  It covers the prefill
+// shape of csrc/attention_mma.cu (same arguments, same packing of the query heads that share a
+// key/value head into the rows of a tile) for head sizes 64 and 128; the decode shape stays with
+// the mma.sync kernel.  As there, nothing of cuongvng/bare-cuda-4gib's [heads, T, keys] score
+// buffer exists (engine/kernels/attention_qk.cu:49-68, softmax.cu:28-42, attention_av.cu:24-44).
+//
+// One thread block = 128 packed rows of one request and one key/value head.  Keys are visited in
+// blocks of 128 positions:
+//   loader warp    one thread copies the block's keys and values from the request's pages into
+//                  128-byte-swizzled shared memory with TMA (one tensor map over the cache group's
+//                  whole pool, a box per page piece; four stages, two for head size 128); Q is staged
+//                  once with cp.async;
+//   MMA thread     S = Q K^T (M 128, N 128, K head size) into tensor memory columns [0, 128);
+//   softmax warps  two threads per row, 64 keys each: read their half of the row of S from tensor
+//                  memory, scale, mask, running maximum (shared with the partner through shared
+//                  memory) and sum in float32 (base 2), write P as bfloat16 into swizzled shared
+//                  memory (the A operand of the second product);
+//   MMA thread     O_block = P V (M 128, N 64 per 64 value columns, K 128) into tensor memory;
+//                  V stays as it lies in the cache ([key][channel]) and is described to the MMA as
+//                  an MN-major operand;
+//   softmax warps  O = O * correction + O_block, with O (half the channels per thread) in registers.
+// S and P are double-buffered: the MMA thread issues S of block j+1 while the softmax warps work on
+// block j, and O_block of block j is added one iteration late, so nobody waits for the tensor core.
+// Every mbarrier wait is bounded: on a timeout the thread sets the error word, all roles leave
+// their loops, tensor memory is released and the block returns.
+
+#include "common.cuh"
+
+#include <cuda.h>
+#include <string.h>
+
+#ifndef HEAD_DIM
+#define HEAD_DIM 64
+#endif
+
+namespace {
+
+constexpr int D = HEAD_DIM;
+static_assert(D == 64 || D == 128, "the tcgen05 attention kernel is built for head sizes 64 and 128");
+constexpr int KA = D / 64;       // 64-wide sub-tiles ("atoms") along the head dimension
+constexpr int BM = 128;          // packed rows per block
+constexpr int BN = 128;          // keys per block
+constexpr int STAGES = D == 64 ? 4 : 2;   // key/value blocks in flight (what shared memory allows)
+constexpr int SUB = 128 * 128;   // bytes of a [128 rows x 64 bf16] swizzled sub-tile
+constexpr int Q_BYTES = KA * SUB;
+constexpr int KV_BYTES = 2 * KA * SUB;   // keys then values of one stage
+constexpr int P_BYTES = 2 * SUB;         // [128 rows x 128 keys] as two sub-tiles; two such buffers
+constexpr int SOFTMAX_THREADS = 256, LOADER_THREADS = 32;
+constexpr int MMA_WARP = SOFTMAX_THREADS / 32;
+constexpr int NUM_THREADS = SOFTMAX_THREADS + 32 + LOADER_THREADS;   // warps 0-7 softmax, 8 MMA, 9 loader
+constexpr int TMEM_COLS = 512;
+constexpr int O_COL = 256;       // first tensor-memory column of the P V result (S buffers at 0 and 128)
+constexpr int DH = D / 2;        // output channels per softmax thread
+constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;
+constexpr int EXCHANGE_BYTES = 2 * 2 * 128 * 4;   // row maxima per column half, two buffers (row sums reuse one)
+constexpr size_t SMEM_BYTES = Q_BYTES + STAGES * KV_BYTES + 2 * P_BYTES + EXCHANGE_BYTES + 160;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ unsigned long long global_timer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long start = global_timer();
+  for (unsigned spins = 0;; ++spins) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spins & 63u) == 63u) {
+      if (*abort_flag) return false;
+      if (global_timer() - start > WAIT_LIMIT_NS) return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+
+// Byte offset of the 16-byte chunk `chunk` (0..7) of row `row` inside a [rows x 64 bf16] sub-tile
+// with the 128-byte swizzle: rows are 128 bytes, groups of 8 rows are 1024 bytes, and the chunk
+// index is XORed with the row's index inside its group.
+__device__ __forceinline__ uint32_t swizzled(int row, int chunk) {
+  return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4));
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, 1024 bytes between 8-row groups.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// float32 accumulator, bfloat16 operands, A K-major; B K-major or (b_mn = 1) MN-major.
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n, int b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_load32_nowait(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait_loads() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// -DATTN_TRACE: thread block (0, 0) records SM clock stamps per role and key block into
+// `trace` ([role][block], 64 blocks per role); a development aid, absent from normal builds.
+#ifdef ATTN_TRACE
+#define TRACE(role, j) do { if (blockIdx.x == 0 && blockIdx.y == 0 && a.trace && (j) < 64) a.trace[(role) * 64 + (j)] = clock64(); } while (0)
+#else
+#define TRACE(role, j) do { } while (0)
+#endif
+
+struct AttnArgs {
+  long long* trace;
+  // the cache group's pool seen as rows of D elements: row = page * page_rows + k_row0 (or v_row0)
+  // + kv head * page_tokens + position in page; the tensor map's box is 64 columns x box_rows rows
+  long long page_rows, k_row0, v_row0;
+  int box_rows;
+  const __nv_bfloat16* q;      // [tokens, q_heads, D]
+  __nv_bfloat16* out;          // [tokens, q_heads * D]
+  PagedCache cache;
+  const int32_t* seq_q_start;
+  const int32_t* seq_q_len;
+  const int32_t* seq_kv_len;
+  const int32_t* tile_seq;     // per tile: batch sequence (-1: nothing to do)
+  const int32_t* tile_index;   // per tile: which 128-row tile of the sequence's packed rows
+  int q_heads;
+  float scale_log2;
+  int window;
+  int* error_word;
+};
+
+constexpr int ERR_LOADER = 11, ERR_MMA = 12, ERR_SOFTMAX = 13, ERR_LAYOUT = 14;
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem[];   // swizzled tiles need 1024-byte alignment (checked below)
+  uint8_t* q_smem = smem;
+  uint8_t* kv_smem = q_smem + Q_BYTES;              // [STAGES][keys: KA sub-tiles | values: KA sub-tiles]
+  uint8_t* p_smem = kv_smem + STAGES * KV_BYTES;    // [2][two sub-tiles of 64 keys]
+  float* row_max = reinterpret_cast<float*>(p_smem + 2 * P_BYTES);   // [2 buffers][2 halves][128 rows]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(row_max + 2 * 2 * 128);
+  uint64_t* q_full = bars;                // loaders -> MMA: Q staged
+  uint64_t* kv_full = bars + 1;           // [STAGES] loaders -> MMA
+  uint64_t* kv_empty = kv_full + STAGES;  // [STAGES] MMA (commit) -> loaders
+  uint64_t* s_full = kv_empty + STAGES;   // [2] MMA (commit) -> softmax, per S buffer
+  uint64_t* p_full = s_full + 2;          // [2] softmax -> MMA: P written and S consumed, per buffer
+  uint64_t* o_full = p_full + 2;          // MMA (commit) -> softmax
+  uint64_t* o_empty = o_full + 1;         // softmax -> MMA: O_block consumed
+  uint64_t* x_bar = o_empty + 1;          // [2] softmax <-> softmax: row maxima written, per buffer
+  uint64_t* sum_bar = x_bar + 2;          // softmax <-> softmax: row sums written
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sum_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (smem_u32(smem) & 1023) {   // never seen; refuse rather than compute with a broken layout
+    if (threadIdx.x == 0) atomicCAS(a.error_word, 0, ERR_LAYOUT);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, LOADER_THREADS);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&s_full[b], 1);
+      mbar_init(&p_full[b], SOFTMAX_THREADS);
+      mbar_init(&x_bar[b], SOFTMAX_THREADS);
+    }
+    mbar_init(sum_bar, SOFTMAX_THREADS);
+    mbar_init(o_full, 1);
+    mbar_init(o_empty, SOFTMAX_THREADS);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == MMA_WARP) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  pdl_wait();
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  // ---- what this block works on (uniform across the block)
+  const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;   // later tiles see more keys: first
+  const int seq = a.tile_seq[tile];
+  int n_kb = 0, kb_lo = 0;
+  int q_start = 0, q_len = 0, kv_len = 0, row0 = 0, n_rows = 0, pos0 = 0, group = 1;
+  int tile_min_pos = 0, tile_max_pos = 0;
+  if (seq >= 0) {
+    group = a.q_heads / a.cache.kv_heads;
+    q_start = a.seq_q_start[seq];
+    q_len = a.seq_q_len[seq];
+    kv_len = a.seq_kv_len[seq];
+    row0 = a.tile_index[tile] * BM;
+    n_rows = q_len * group;
+    pos0 = kv_len - q_len;
+    const int last_token = min(q_len - 1, (row0 + BM - 1) / group), first_token = row0 / group;
+    tile_min_pos = pos0 + first_token;
+    tile_max_pos = pos0 + last_token;
+    const int lo_key = a.window > 0 ? max(0, tile_min_pos - a.window + 1) : 0;
+    kb_lo = lo_key / BN;
+    n_kb = tile_max_pos / BN - kb_lo + 1;
+  }
+
+  if (warp > MMA_WARP) {
+    // ------------------------------------------------------------------ loader warp
+    const int lt = threadIdx.x - (SOFTMAX_THREADS + 32);
+    // Q: 128 rows x D, 16-byte chunks; rows past the request's packed rows are zero
+    for (int i = lt; i < BM * (D / 8); i += LOADER_THREADS) {
+      const int r = i / (D / 8), c = i % (D / 8);
+      const int R = row0 + r;
+      const bool valid = seq >= 0 && R < n_rows;
+      const int token = valid ? R / group : 0, head = valid ? kvh * group + R % group : 0;
+      const __nv_bfloat16* src = a.q + ((long long)(q_start + token) * a.q_heads + head) * D + c * 8;
+      cp_async16(smem_u32(q_smem) + (c >> 3) * SUB + swizzled(r, c & 7), src, valid);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    mbar_arrive(q_full);
+    // Keys and values: one TMA box per piece of a page (a page holds box_rows or more positions
+    // of a key block).  A piece whose page is not held (given back by a window) is filled with
+    // zeros by the warp instead; its keys are masked, but stale shared memory must not reach P V.
+    const int page_tokens = a.cache.page_tokens;
+    const int32_t* table_row = a.cache.block_table + (long long)max(seq, 0) * a.cache.table_stride;
+    const int pieces = BN / a.box_rows;
+    auto issue_block = [&](int j) {
+      const int s = j % STAGES;
+      const uint32_t k_base = smem_u32(kv_smem) + s * KV_BYTES, v_base = k_base + KA * SUB;
+      const int key0 = (kb_lo + j) * BN;
+      uint32_t bytes = 0;
+      for (int piece = 0; piece < pieces; ++piece) {   // first the pieces without a page (all lanes)
+        const int key = key0 + piece * a.box_rows;
+        const int page = key < kv_len ? __ldg(table_row + key / page_tokens) : -1;
+        if (page >= 0) {
+          bytes += 2 * KA * a.box_rows * 128;
+        } else {
+          for (int at = 0; at < KA; ++at)
+            for (int i = lane; i < a.box_rows * 8; i += 32) {
+              const uint32_t off = at * SUB + piece * a.box_rows * 128 + i * 16;
+              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(k_base + off), "r"(0) : "memory");
+              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(v_base + off), "r"(0) : "memory");
+            }
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        mbar_expect_tx(&kv_full[s], bytes);   // also the barrier's one arrival
+        for (int piece = 0; piece < pieces; ++piece) {
+          const int key = key0 + piece * a.box_rows;
+          const int page = key < kv_len ? __ldg(table_row + key / page_tokens) : -1;
+          if (page < 0) continue;
+          const long long row = (long long)page * a.page_rows + (long long)kvh * page_tokens + key % page_tokens;
+          for (int at = 0; at < KA; ++at) {
+            const uint32_t off = at * SUB + piece * a.box_rows * 128;
+            tma_load_2d(k_base + off, &pool_map, &kv_full[s], at * 64, (int)(row + a.k_row0));
+            tma_load_2d(v_base + off, &pool_map, &kv_full[s], at * 64, (int)(row + a.v_row0));
+          }
+        }
+      }
+    };
+    // Block j + 1 is requested as soon as its stage is free (the MMA thread frees it with P V of
+    // block j - 1, which it issues after S of block j).
+    bool ok = true;
+    if (n_kb > 0) issue_block(0);
+    for (int j = 0; j + 1 < n_kb && ok; ++j) {
+      const int s1 = (j + 1) % STAGES;
+      const uint32_t use = (uint32_t)((j + 1) / STAGES);   // how often the stage was filled before
+      if (use > 0 && !mbar_wait(&kv_empty[s1], (use - 1) & 1, abort_flag)) {
+        if (lane == 0) {
+          *abort_flag = 1;
+          atomicCAS(a.error_word, 0, ERR_LOADER);
+        }
+        ok = false;
+        break;
+      }
+      if (lane == 0) TRACE(1, j + 1);
+      issue_block(j + 1);
+    }
+  } else if (warp == MMA_WARP) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_kb > 0) {
+      constexpr uint32_t idesc_s = instr_desc(BM, BN, 0);
+      constexpr uint32_t idesc_o = instr_desc(BM, 64, 1);
+      const uint32_t q_addr = smem_u32(q_smem);
+      // O_block(j) = P(j) V(j): after the softmax warps wrote P(j) and read O_block(j - 1)
+      auto issue_pv = [&](int j) -> bool {
+        const int s = j % STAGES, b = j & 1;
+        if (!mbar_wait(&p_full[b], (j >> 1) & 1, abort_flag)) return false;
+        if (j > 0 && !mbar_wait(o_empty, (j - 1) & 1, abort_flag)) return false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t v_addr = smem_u32(kv_smem) + s * KV_BYTES + KA * SUB, p_addr = smem_u32(p_smem) + b * P_BYTES;
+#pragma unroll
+        for (int vt = 0; vt < KA; ++vt)
+#pragma unroll
+          for (int kk = 0; kk < BN / 16; ++kk)
+            umma_bf16(tmem_base + O_COL + vt * 64, smem_desc_sw128(p_addr + (kk >> 2) * SUB) + 2 * (kk & 3),
+                      smem_desc_sw128(v_addr + vt * SUB) + (uint64_t)(kk * 2048 >> 4), idesc_o, kk > 0 ? 1u : 0u);
+        umma_commit(o_full);
+        umma_commit(&kv_empty[s]);
+        TRACE(3, j);
+        return true;
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      for (int j = 0; j < n_kb && ok; ++j) {
+        const int s = j % STAGES, b = j & 1;
+        // S(j) = Q K(j)^T into S buffer b: its previous reader, the softmax of block j - 2, is known
+        // to be done (this thread waited for P(j - 2) before it issued O_block(j - 2))
+        ok = mbar_wait(&kv_full[s], (j / STAGES) & 1, abort_flag);
+        if (!ok) break;
+        TRACE(0, j);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t k_addr = smem_u32(kv_smem) + s * KV_BYTES;
+#pragma unroll
+        for (int at = 0; at < KA; ++at)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_bf16(tmem_base + b * BN, smem_desc_sw128(q_addr + at * SUB) + 2 * k,
+                      smem_desc_sw128(k_addr + at * SUB) + 2 * k, idesc_s, (at > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&s_full[b]);
+        TRACE(2, j);
+        if (j > 0) ok = issue_pv(j - 1);   // while the softmax warps work on block j
+      }
+      if (ok) ok = issue_pv(n_kb - 1);
+      if (!ok) {
+        *abort_flag = 1;
+        atomicCAS(a.error_word, 0, ERR_MMA);
+        umma_commit(&s_full[0]);   // release whoever waits
+        umma_commit(&s_full[1]);
+        umma_commit(o_full);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax: two threads per row
+    const int quad = warp & 3, half = warp >> 2;     // tensor-memory lanes 32 * quad ..; keys 64 * half ..
+    const int r = quad * 32 + lane;                  // row of the tile = tensor-memory lane
+    const int R = row0 + r;
+    const bool row_valid = seq >= 0 && R < n_rows;
+    const int row_pos = row_valid ? pos0 + R / group : -1;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    float m = -INFINITY, l = 0.0f, corr_prev = 1.0f;
+    float o[DH];
+#pragma unroll
+    for (int i = 0; i < DH; ++i) o[i] = 0.0f;
+    // O(j) = O(j - 1) * corr(j) + O_block(j), added once the MMA thread reports O_block(j)
+    auto add_block = [&](int j, float corr) -> bool {
+      if (!mbar_wait(o_full, j & 1, abort_flag) || *abort_flag) return false;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      uint32_t v[DH];
+#pragma unroll
+      for (int c0 = 0; c0 < DH; c0 += 32) tmem_load32_nowait(lane_addr + O_COL + half * DH + c0, v + c0);
+      tmem_wait_loads();
+#pragma unroll
+      for (int i = 0; i < DH; ++i) o[i] = o[i] * corr + __uint_as_float(v[i]);
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(o_empty);
+      return true;
+    };
+    bool ok = true;
+    for (int j = 0; j < n_kb && ok; ++j) {
+      const int b = j & 1;
+      const int key0 = (kb_lo + j) * BN + half * 64;   // first key of this thread's half
+      ok = mbar_wait(&s_full[b], (j >> 1) & 1, abort_flag) && !*abort_flag;
+      if (!ok) break;
+      if (threadIdx.x == 0) TRACE(4, j);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const bool all_visible = (kb_lo + j) * BN + BN - 1 <= tile_min_pos &&
+                               (a.window <= 0 || (kb_lo + j) * BN > tile_max_pos - a.window);
+      uint32_t v[64];
+      tmem_load32_nowait(lane_addr + b * BN + half * 64, v);
+      tmem_load32_nowait(lane_addr + b * BN + half * 64 + 32, v + 32);
+      tmem_wait_loads();
+      float mx = -INFINITY;
+      if (all_visible) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const int key = key0 + i;
+          const bool visible = key <= row_pos && (a.window <= 0 || key > row_pos - a.window);
+          if (!visible) v[i] = 0xff800000u;   // -inf: gives probability 0 below
+          mx = fmaxf(mx, __uint_as_float(v[i]));
+        }
+      }
+      // the row's maximum over both halves
+      row_max[(b * 2 + half) * 128 + r] = mx;
+      mbar_arrive(&x_bar[b]);                          // (a bounded wait, unlike a hardware barrier)
+      ok = mbar_wait(&x_bar[b], (j >> 1) & 1, abort_flag);
+      if (!ok) break;
+      if (threadIdx.x == 0) TRACE(5, j);
+      mx = fmaxf(mx, row_max[(b * 2 + (half ^ 1)) * 128 + r]);
+      const float m_new = fmaxf(m, mx * a.scale_log2);       // scale > 0: the maximum commutes with it
+      const float m_use = m_new == -INFINITY ? 0.0f : m_new;
+      const float corr = fast_exp2(m - m_use);                 // m = -inf gives 0
+      m = m_new;
+      l *= corr;
+      // probabilities into shared memory as the A operand of P V: this thread's 64 keys are one sub-tile
+      uint8_t* p_tile = p_smem + b * P_BYTES + half * SUB;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        uint32_t packed[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(v[ch * 8 + 2 * e]), a.scale_log2, -m_use));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(v[ch * 8 + 2 * e + 1]), a.scale_log2, -m_use));
+          l += p0 + p1;
+          packed[e] = pack_bf16(p0, p1);
+        }
+        *reinterpret_cast<uint4*>(p_tile + swizzled(r, ch)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive(&p_full[b]);
+      if (threadIdx.x == 0) TRACE(6, j);
+      if (j > 0) ok = add_block(j - 1, corr_prev);   // the block before, whose P V ran meanwhile
+      if (threadIdx.x == 0) TRACE(7, j);
+      corr_prev = corr;
+    }
+    if (ok && n_kb > 0) ok = add_block(n_kb - 1, corr_prev);
+    if (!ok) {
+      *abort_flag = 1;
+      atomicCAS(a.error_word, 0, ERR_SOFTMAX);
+    }
+    // the row's sum over both halves, through the maxima buffer that the last block did not use
+    // (every thread is past that buffer's last read once it has passed the last block's exchange)
+    float* row_sum = row_max + (n_kb & 1) * 2 * 128;   // [2 halves][128 rows]
+    row_sum[half * 128 + r] = l;
+    mbar_arrive(sum_bar);
+    if (ok) ok = mbar_wait(sum_bar, 0, abort_flag);
+    l += row_sum[(half ^ 1) * 128 + r];
+    if (ok && row_valid) {
+      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+      const int token = R / group, head = kvh * group + R % group;
+      uint4* dst = reinterpret_cast<uint4*>(a.out + ((long long)(q_start + token) * a.q_heads + head) * D + half * DH);
+#pragma unroll
+      for (int c = 0; c < DH / 8; ++c)
+        dst[c] = make_uint4(pack_bf16(o[8 * c] * inv, o[8 * c + 1] * inv), pack_bf16(o[8 * c + 2] * inv, o[8 * c + 3] * inv),
+                            pack_bf16(o[8 * c + 4] * inv, o[8 * c + 5] * inv), pack_bf16(o[8 * c + 6] * inv, o[8 * c + 7] * inv));
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == MMA_WARP) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+}  // namespace
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// Writes the 128-byte tensor map of a cache group's pool: `rows` rows of D bfloat16 starting at
+// `base` (16-byte aligned), boxes of 64 columns x `box_rows` rows, 128-byte swizzle.
+extern "C" int llm_attention_tc_pool_map(void* map_out, const void* base, long long rows, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return 1000 + (int)cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || rows <= 0 || box_rows <= 0 || box_rows > 128) return ERR_BAD_SIZE;
+  cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(reinterpret_cast<CUtensorMap*>(map_out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
+                  dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 2000 + (int)r;
+}
+
+static long long* g_trace = nullptr;
+extern "C" void llm_attention_tc_set_trace(long long* buffer) { g_trace = buffer; }   // development aid
+
+extern "C" int llm_attention_tc_head_dim() { return D; }
+extern "C" int llm_attention_tc_rows() { return BM; }
+
+// Same arguments as llm_attention_mma without splits and scratch, plus the pool's tensor map
+// (llm_attention_tc_pool_map over `pool_base`, which k_base and v_base lie in, with boxes of
+// `box_rows` rows: a multiple of 8 that divides both 128 and the page size).  Every tile has 128
+// packed rows.
+extern "C" int llm_attention_tcgen05(const void* pool_map, const void* pool_base, int box_rows, const void* q, void* out,
+                                     void* k_base, void* v_base, const int32_t* block_table,
+                                     long long page_stride, int table_stride, int page_tokens, int kv_heads,
+                                     int head_dim, const int32_t* seq_q_start, const int32_t* seq_q_len,
+                                     const int32_t* seq_kv_len, const int32_t* tile_seq, const int32_t* tile_index,
+                                     int n_tiles, int q_heads, float scale, int window, int* error_word,
+                                     cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (head_dim != D || q_heads % kv_heads || kv_heads > 65535) return ERR_BAD_SIZE;
+  if (box_rows < 8 || box_rows % 8 || BN % box_rows || page_tokens % box_rows) return ERR_BAD_SIZE;
+  const long long k_off = reinterpret_cast<const char*>(k_base) - reinterpret_cast<const char*>(pool_base);
+  const long long v_off = reinterpret_cast<const char*>(v_base) - reinterpret_cast<const char*>(pool_base);
+  if (k_off < 0 || v_off < 0 || k_off % (D * 2) || v_off % (D * 2) || page_stride % D) return ERR_BAD_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(k_base) |
+       reinterpret_cast<uintptr_t>(v_base)) & 15)
+    return ERR_BAD_ALIGN;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) !=
+        cudaSuccess)
+      return launch_status();
+    configured = true;
+  }
+  CUtensorMap map;   // the caller's buffer need not be 64-byte aligned
+  memcpy(&map, pool_map, sizeof(CUtensorMap));
+  AttnArgs a;
+  a.trace = g_trace;
+  a.page_rows = page_stride / D;
+  a.k_row0 = k_off / (D * 2);
+  a.v_row0 = v_off / (D * 2);
+  a.box_rows = box_rows;
+  a.q = reinterpret_cast<const __nv_bfloat16*>(q);
+  a.out = reinterpret_cast<__nv_bfloat16*>(out);
+  a.cache = PagedCache{k_base, v_base, block_table, page_stride, table_stride, page_tokens, kv_heads, head_dim};
+  a.seq_q_start = seq_q_start;
+  a.seq_q_len = seq_q_len;
+  a.seq_kv_len = seq_kv_len;
+  a.tile_seq = tile_seq;
+  a.tile_index = tile_index;
+  a.q_heads = q_heads;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.window = window;
+  a.error_word = error_word;
+  dim3 grid(n_tiles, kv_heads);
+  launch_kernel(attention_tcgen05_kernel, grid, NUM_THREADS, SMEM_BYTES, stream, map, a);
+  return launch_status();
+}

@@ -3,6 +3,8 @@ size, the per-step list of row tiles, and the choice of how many thread blocks s
 
 from __future__ import annotations
 
+import ctypes
+import math
 import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Dict, Optional
@@ -11,12 +13,15 @@ import numpy as np
 import torch
 
 from . import build
+from ..errors import KernelLaunchError
 from .lib import CacheView, _check
 
 KEY_BLOCK = 64
 TARGET_BLOCKS = 148 * 2
 COUNTER_WORDS = 4096          # per-tile split counters at the start of the scratch (see the kernel)
 _libs: Dict[int, object] = {}
+_tc_libs: Dict[int, object] = {}
+TC_HEAD_DIMS = (64, 128)      # head sizes the tcgen05 prefill kernel is built for
 
 
 def supports(head_dim: int) -> bool:
@@ -41,15 +46,50 @@ def lib(head_dim: int):
     return l
 
 
+def tc_lib(head_dim: int):
+    """The tcgen05 prefill kernel's library for this head size."""
+    l = _tc_libs.get(head_dim)
+    if l is None:
+        l = build.load_library("attention_tcgen05.cu", defines(head_dim))
+        P, I, L, F = c_void_p, c_int, c_longlong, c_float
+        l.llm_attention_tcgen05.argtypes = [P, P, I, P, P, P, P, P, L, I, I, I, I, P, P, P, P, P, I, I, F, I, P, P]
+        l.llm_attention_tcgen05.restype = c_int
+        l.llm_attention_tc_pool_map.argtypes = [P, P, L, I]
+        l.llm_attention_tc_pool_map.restype = c_int
+        l.llm_attention_tc_rows.restype = c_int
+        _tc_libs[head_dim] = l
+    return l
+
+
 class AttentionPlan:
     def __init__(self, head_dim: int, heads: int, kv_heads: int):
         self.head_dim, self.heads, self.kv_heads = head_dim, heads, kv_heads
         self.group = heads // kv_heads
         self.lib = lib(head_dim)
         self.prefill_rows = int(self.lib.llm_attention_prefill_rows())
+        self.tc = None
+        if head_dim in TC_HEAD_DIMS and not os.environ.get("BARE_CUDA_B200_NO_TC_ATTENTION"):
+            self.tc = tc_lib(head_dim)
+            self.prefill_rows = int(self.tc.llm_attention_tc_rows())
         self._host = None
         self._dev = None
         self._scratch = None
+        self._pool_maps = {}
+
+    def pool_map(self, cache: CacheView):
+        """The TMA tensor map over a cache group's whole pool (one per pool) and its box height."""
+        box_rows = math.gcd(128, cache.page_tokens)
+        key = (cache.pool_ptr, cache.pool_elems, box_rows)
+        m = self._pool_maps.get(key)
+        if m is None:
+            m = (ctypes.c_ubyte * 128)()
+            _check(self.tc.llm_attention_tc_pool_map(ctypes.addressof(m), cache.pool_ptr,
+                                                     cache.pool_elems // self.head_dim, box_rows), "attention pool map")
+            self._pool_maps[key] = m
+        return m, box_rows
+
+    def tc_usable(self, cache: CacheView) -> bool:
+        return self.tc is not None and cache.pool_ptr != 0 and math.gcd(128, cache.page_tokens) >= 8
 
     def buffers(self, ctx, n: int, device):
         """Pinned and device int32 buffers for the tile list, sized once for the largest step so
@@ -112,6 +152,18 @@ def step_tiles(ctx, plan: AttentionPlan):
 def run(ctx, plan: AttentionPlan, q: torch.Tensor, out: torch.Tensor, cache: CacheView, scale: float,
         window: int) -> None:
     tile_seq, tile_index, n_tiles, rows_per_tile, n_splits = step_tiles(ctx, plan)
+    if plan.tc is not None and rows_per_tile != 16:
+        if not plan.tc_usable(cache):
+            raise KernelLaunchError(f"attention_tcgen05: cache pages of {cache.page_tokens} positions are not supported "
+                                    "(the page size must share a factor of at least 8 with 128)")
+        from . import gemm
+        pool_map, box_rows = plan.pool_map(cache)
+        _check(plan.tc.llm_attention_tcgen05(
+            ctypes.addressof(pool_map), cache.pool_ptr, box_rows, q.data_ptr(), out.data_ptr(), cache.k_ptr, cache.v_ptr, cache.block_table.data_ptr(), cache.page_stride,
+            cache.table_stride, cache.page_tokens, cache.kv_heads, cache.head_dim, ctx.seq_q_start.data_ptr(),
+            ctx.seq_q_len.data_ptr(), ctx.seq_kv_len.data_ptr(), tile_seq.data_ptr(), tile_index.data_ptr(), n_tiles,
+            plan.heads, scale, window, gemm.error_word(q.device).data_ptr(), ctx.stream), "attention_tcgen05")
+        return
     scratch_ptr = 0
     if n_splits > 1:
         floats = plan.lib.llm_attention_scratch_floats(n_tiles, plan.kv_heads, n_splits, rows_per_tile)

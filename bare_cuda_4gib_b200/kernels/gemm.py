@@ -47,8 +47,10 @@ def check_errors() -> None:
         code = int(_error_word.item())
         if code:
             _error_word.zero_()
-            role = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue"}.get(code, f"code {code}")
-            raise KernelLaunchError(f"gemm_tcgen05: a bounded wait ran out in the {role}; the result is invalid")
+            role = {1: "gemm TMA producer", 2: "gemm MMA issuer", 3: "gemm epilogue", 11: "attention loader",
+                    12: "attention MMA issuer", 13: "attention softmax",
+                    14: "attention (shared memory not 1024-byte aligned)"}.get(code, f"code {code}")
+            raise KernelLaunchError(f"a tcgen05 kernel gave up ({role}): a bounded wait ran out; the result is invalid")
 
 
 def supports(weight: torch.Tensor) -> bool:

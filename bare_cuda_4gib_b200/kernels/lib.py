@@ -63,10 +63,11 @@ class CacheView:
     """What a kernel needs to address one cache (one run of a layer) inside its group's pool."""
 
     __slots__ = ("k_ptr", "v_ptr", "block_table", "page_stride", "table_stride", "page_tokens",
-                 "kv_heads", "head_dim", "dtype")
+                 "kv_heads", "head_dim", "dtype", "pool_ptr", "pool_elems")
 
     def __init__(self, k_ptr, v_ptr, block_table, page_stride, table_stride, page_tokens, kv_heads,
-                 head_dim, dtype):
+                 head_dim, dtype, pool_ptr=0, pool_elems=0):
+        self.pool_ptr, self.pool_elems = pool_ptr, pool_elems     # the group's whole storage (for TMA)
         self.k_ptr, self.v_ptr = k_ptr, v_ptr
         self.block_table = block_table
         self.page_stride, self.table_stride = page_stride, table_stride

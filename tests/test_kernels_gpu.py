@@ -299,7 +299,7 @@ def _attention_case(seqs, heads, kv_heads, d, page, window, seed, far_key=False)
         vs.append(v)
     esize = 2
     view = CacheView(storage.data_ptr(), storage.data_ptr() + (elems // 2) * esize, table, elems, table.shape[1],
-                     page, kv_heads, d, torch.bfloat16)
+                     page, kv_heads, d, torch.bfloat16, storage.data_ptr(), storage.numel())
     n = sum(q for q, _ in seqs)
     q = torch.randn(n, heads, d, device=DEV).to(torch.bfloat16)
     if far_key:
@@ -317,6 +317,8 @@ def _attention_case(seqs, heads, kv_heads, d, page, window, seed, far_key=False)
     plan = fast.plan_for(d, heads, kv_heads)
     scale = 1.0 / math.sqrt(d)
     fast.run(ctx, plan, q.view(n, heads * d), out, view, scale, window)
+    from bare_cuda_4gib_b200.kernels import gemm
+    gemm.check_errors()
     want = torch.zeros(n, heads, d, dtype=torch.float64, device=DEV)
     for s, (q_len, kv_len) in enumerate(seqs):
         for i in range(q_len):
