@@ -12,16 +12,18 @@
 //                  whole pool, a box per page piece; four stages, two for head size 128); Q is staged
 //                  once with cp.async;
 //   MMA thread     S = Q K^T (M 128, N 128, K head size) into tensor memory columns [0, 128);
-//   softmax warps  two threads per row, 64 keys each: read their half of the row of S from tensor
-//                  memory, scale, mask, running maximum (shared with the partner through shared
-//                  memory) and sum in float32 (base 2), write P as bfloat16 into swizzled shared
-//                  memory (the A operand of the second product);
+//   softmax warps  two groups of four warps; group g takes the key blocks j with j % 2 == g and
+//                  keeps a running softmax of its own.  One thread per row: read the row of S from
+//                  tensor memory, scale, mask, running maximum and sum in float32 (base 2), write
+//                  P as bfloat16 into swizzled shared memory (the A operand of the second product);
 //   MMA thread     O_block = P V (M 128, N 64 per 64 value columns, K 128) into tensor memory;
 //                  V stays as it lies in the cache ([key][channel]) and is described to the MMA as
 //                  an MN-major operand;
-//   softmax warps  O = O * correction + O_block, with O (half the channels per thread) in registers.
-// S and P are double-buffered: the MMA thread issues S of block j+1 while the softmax warps work on
-// block j, and O_block of block j is added one iteration late, so nobody waits for the tensor core.
+//   softmax warps  O = O * correction + O_block, with O in registers, one block of the group late,
+//                  so nobody waits for the tensor core; at the end the two groups' (maximum, sum,
+//                  O) are merged through shared memory.
+// S, P and O_block exist once per group: while one group exponentiates (the special-function
+// units bound this kernel), the other reads its maxima or adds its O_block.
 // Every mbarrier wait is bounded: on a timeout the thread sets the error word, all roles leave
 // their loops, tensor memory is released and the block returns.
 
@@ -50,11 +52,12 @@ constexpr int SOFTMAX_THREADS = 256, LOADER_THREADS = 32;
 constexpr int MMA_WARP = SOFTMAX_THREADS / 32;
 constexpr int NUM_THREADS = SOFTMAX_THREADS + 32 + LOADER_THREADS;   // warps 0-7 softmax, 8 MMA, 9 loader
 constexpr int TMEM_COLS = 512;
-constexpr int O_COL = 256;       // first tensor-memory column of the P V result (S buffers at 0 and 128)
-constexpr int DH = D / 2;        // output channels per softmax thread
+constexpr int O_COL = 256;       // first tensor-memory column of the P V results (S buffers at 0 and 128)
+constexpr int GROUP_THREADS = 128;
+constexpr int DH = D / 2;        // output channels per thread in the final merge
 constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;
-constexpr int EXCHANGE_BYTES = 2 * 2 * 128 * 4;   // row maxima per column half, two buffers (row sums reuse one)
-constexpr size_t SMEM_BYTES = Q_BYTES + STAGES * KV_BYTES + 2 * P_BYTES + EXCHANGE_BYTES + 160;
+constexpr size_t SMEM_BYTES = Q_BYTES + STAGES * KV_BYTES + 2 * P_BYTES + 192;   // 17 barriers + 2 words
+static_assert((size_t)STAGES * KV_BYTES + 2 * P_BYTES >= (size_t)2 * 128 * (D + 2) * 4, "the merge area reuses the stages");
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -196,18 +199,18 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
   uint8_t* q_smem = smem;
   uint8_t* kv_smem = q_smem + Q_BYTES;              // [STAGES][keys: KA sub-tiles | values: KA sub-tiles]
   uint8_t* p_smem = kv_smem + STAGES * KV_BYTES;    // [2][two sub-tiles of 64 keys]
-  float* row_max = reinterpret_cast<float*>(p_smem + 2 * P_BYTES);   // [2 buffers][2 halves][128 rows]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(row_max + 2 * 2 * 128);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + 2 * P_BYTES);
   uint64_t* q_full = bars;                // loaders -> MMA: Q staged
   uint64_t* kv_full = bars + 1;           // [STAGES] loaders -> MMA
   uint64_t* kv_empty = kv_full + STAGES;  // [STAGES] MMA (commit) -> loaders
   uint64_t* s_full = kv_empty + STAGES;   // [2] MMA (commit) -> softmax, per S buffer
   uint64_t* p_full = s_full + 2;          // [2] softmax -> MMA: P written and S consumed, per buffer
-  uint64_t* o_full = p_full + 2;          // MMA (commit) -> softmax
-  uint64_t* o_empty = o_full + 1;         // softmax -> MMA: O_block consumed
-  uint64_t* x_bar = o_empty + 1;          // [2] softmax <-> softmax: row maxima written, per buffer
-  uint64_t* sum_bar = x_bar + 2;          // softmax <-> softmax: row sums written
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sum_bar + 1);
+  uint64_t* o_full = p_full + 2;          // [2] MMA (commit) -> softmax, per group
+  uint64_t* o_empty = o_full + 2;         // [2] softmax -> MMA: O_block consumed, per group
+  uint64_t* s_free = o_empty + 2;         // [2] softmax -> MMA: the group holds its S values in registers
+  uint64_t* done_bar = s_free + 2;        // softmax <-> softmax: both groups finished their blocks
+  uint64_t* merge_bar = done_bar + 1;     // softmax <-> softmax: both groups wrote their state
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(merge_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   pdl_launch_dependents();
@@ -217,6 +220,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
     return;
   }
   if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&pool_map)) : "memory");
     mbar_init(q_full, LOADER_THREADS);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&kv_full[s], 1);
@@ -224,12 +228,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&s_full[b], 1);
-      mbar_init(&p_full[b], SOFTMAX_THREADS);
-      mbar_init(&x_bar[b], SOFTMAX_THREADS);
+      mbar_init(&p_full[b], GROUP_THREADS);
+      mbar_init(&o_full[b], 1);
+      mbar_init(&o_empty[b], GROUP_THREADS);
+      mbar_init(&s_free[b], GROUP_THREADS);
     }
-    mbar_init(sum_bar, SOFTMAX_THREADS);
-    mbar_init(o_full, 1);
-    mbar_init(o_empty, SOFTMAX_THREADS);
+    mbar_init(done_bar, SOFTMAX_THREADS);
+    mbar_init(merge_bar, SOFTMAX_THREADS);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -287,18 +292,29 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
     // zeros by the warp instead; its keys are masked, but stale shared memory must not reach P V.
     const int page_tokens = a.cache.page_tokens;
     const int32_t* table_row = a.cache.block_table + (long long)max(seq, 0) * a.cache.table_stride;
-    const int pieces = BN / a.box_rows;
+    const int pieces = BN / a.box_rows;   // at most 16: lane p looks piece p up, lane 0 issues the copies
+    const int page_shift = (page_tokens & (page_tokens - 1)) == 0 ? __ffs(page_tokens) - 1 : -1;
     auto issue_block = [&](int j) {
       const int s = j % STAGES;
       const uint32_t k_base = smem_u32(kv_smem) + s * KV_BYTES, v_base = k_base + KA * SUB;
       const int key0 = (kb_lo + j) * BN;
-      uint32_t bytes = 0;
-      for (int piece = 0; piece < pieces; ++piece) {   // first the pieces without a page (all lanes)
-        const int key = key0 + piece * a.box_rows;
-        const int page = key < kv_len ? __ldg(table_row + key / page_tokens) : -1;
-        if (page >= 0) {
-          bytes += 2 * KA * a.box_rows * 128;
-        } else {
+      // lane p: the pool row of piece p's first position, or -1 if its page is not held
+      long long my_row = -1;
+      if (lane < pieces) {
+        const int key = key0 + lane * a.box_rows;
+        if (key < kv_len) {
+          const int block = page_shift >= 0 ? key >> page_shift : key / page_tokens;
+          const int in_page = page_shift >= 0 ? key & (page_tokens - 1) : key % page_tokens;
+          const int page = __ldg(table_row + block);
+          if (page >= 0) my_row = (long long)page * a.page_rows + (long long)kvh * page_tokens + in_page;
+        }
+      }
+      const uint32_t held = __ballot_sync(0xffffffffu, my_row >= 0) & ((pieces < 32) ? ((1u << pieces) - 1u) : 0xffffffffu);
+      const uint32_t missing = ~held & ((pieces < 32) ? ((1u << pieces) - 1u) : 0xffffffffu);
+      if (lane == 0) TRACE(8, j);
+      if (missing) {   // rare: zero the pieces without a page, and make the stores visible to the MMA
+        for (int piece = 0; piece < pieces; ++piece) {
+          if (!((missing >> piece) & 1u)) continue;
           for (int at = 0; at < KA; ++at)
             for (int i = lane; i < a.box_rows * 8; i += 32) {
               const uint32_t off = at * SUB + piece * a.box_rows * 128 + i * 16;
@@ -306,23 +322,22 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
               asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(v_base + off), "r"(0) : "memory");
             }
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      if (lane == 0) mbar_expect_tx(&kv_full[s], (uint32_t)__popc(held) * 2u * KA * a.box_rows * 128u);   // also the one arrival
+      if (lane == 0) TRACE(9, j);
       __syncwarp();
-      if (lane == 0) {
-        mbar_expect_tx(&kv_full[s], bytes);   // also the barrier's one arrival
-        for (int piece = 0; piece < pieces; ++piece) {
-          const int key = key0 + piece * a.box_rows;
-          const int page = key < kv_len ? __ldg(table_row + key / page_tokens) : -1;
-          if (page < 0) continue;
-          const long long row = (long long)page * a.page_rows + (long long)kvh * page_tokens + key % page_tokens;
-          for (int at = 0; at < KA; ++at) {
-            const uint32_t off = at * SUB + piece * a.box_rows * 128;
-            tma_load_2d(k_base + off, &pool_map, &kv_full[s], at * 64, (int)(row + a.k_row0));
-            tma_load_2d(v_base + off, &pool_map, &kv_full[s], at * 64, (int)(row + a.v_row0));
-          }
-        }
+      // lane 0 issues the key copies, lane 1 the value copies: issuing is what takes the time
+      for (int piece = 0; piece < pieces; ++piece) {
+        const long long row = __shfl_sync(0xffffffffu, my_row, piece);
+        if (lane > 1 || row < 0) continue;
+        const uint32_t base = lane == 0 ? k_base : v_base;
+        const long long row0_of_cache = lane == 0 ? a.k_row0 : a.v_row0;
+        for (int at = 0; at < KA; ++at)
+          tma_load_2d(base + at * SUB + piece * a.box_rows * 128, &pool_map, &kv_full[s], at * 64, (int)(row + row0_of_cache));
       }
+      if (lane == 0) TRACE(10, j);
     };
     // Block j + 1 is requested as soon as its stage is free (the MMA thread frees it with P V of
     // block j - 1, which it issues after S of block j).
@@ -348,31 +363,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
       constexpr uint32_t idesc_s = instr_desc(BM, BN, 0);
       constexpr uint32_t idesc_o = instr_desc(BM, 64, 1);
       const uint32_t q_addr = smem_u32(q_smem);
-      // O_block(j) = P(j) V(j): after the softmax warps wrote P(j) and read O_block(j - 1)
-      auto issue_pv = [&](int j) -> bool {
+      // S(j) = Q K(j)^T into the S buffer of block j's group
+      auto issue_s = [&](int j) -> bool {
         const int s = j % STAGES, b = j & 1;
-        if (!mbar_wait(&p_full[b], (j >> 1) & 1, abort_flag)) return false;
-        if (j > 0 && !mbar_wait(o_empty, (j - 1) & 1, abort_flag)) return false;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t v_addr = smem_u32(kv_smem) + s * KV_BYTES + KA * SUB, p_addr = smem_u32(p_smem) + b * P_BYTES;
-#pragma unroll
-        for (int vt = 0; vt < KA; ++vt)
-#pragma unroll
-          for (int kk = 0; kk < BN / 16; ++kk)
-            umma_bf16(tmem_base + O_COL + vt * 64, smem_desc_sw128(p_addr + (kk >> 2) * SUB) + 2 * (kk & 3),
-                      smem_desc_sw128(v_addr + vt * SUB) + (uint64_t)(kk * 2048 >> 4), idesc_o, kk > 0 ? 1u : 0u);
-        umma_commit(o_full);
-        umma_commit(&kv_empty[s]);
-        TRACE(3, j);
-        return true;
-      };
-      bool ok = mbar_wait(q_full, 0, abort_flag);
-      for (int j = 0; j < n_kb && ok; ++j) {
-        const int s = j % STAGES, b = j & 1;
-        // S(j) = Q K(j)^T into S buffer b: its previous reader, the softmax of block j - 2, is known
-        // to be done (this thread waited for P(j - 2) before it issued O_block(j - 2))
-        ok = mbar_wait(&kv_full[s], (j / STAGES) & 1, abort_flag);
-        if (!ok) break;
+        if (!mbar_wait(&kv_full[s], (j / STAGES) & 1, abort_flag)) return false;
         TRACE(0, j);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t k_addr = smem_u32(kv_smem) + s * KV_BYTES;
@@ -384,124 +378,196 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
                       smem_desc_sw128(k_addr + at * SUB) + 2 * k, idesc_s, (at > 0 || k > 0) ? 1u : 0u);
         umma_commit(&s_full[b]);
         TRACE(2, j);
-        if (j > 0) ok = issue_pv(j - 1);   // while the softmax warps work on block j
+        return true;
+      };
+      // O_block(j) = P(j) V(j) into the group's O_block, once the group has read its O_block(j - 2)
+      auto issue_pv = [&](int j) -> bool {
+        const int s = j % STAGES, b = j & 1;
+        if (j > 1 && !mbar_wait(&o_empty[b], ((j >> 1) - 1) & 1, abort_flag)) return false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t v_addr = smem_u32(kv_smem) + s * KV_BYTES + KA * SUB, p_addr = smem_u32(p_smem) + b * P_BYTES;
+#pragma unroll
+        for (int vt = 0; vt < KA; ++vt)
+#pragma unroll
+          for (int kk = 0; kk < BN / 16; ++kk)
+            umma_bf16(tmem_base + O_COL + b * D + vt * 64, smem_desc_sw128(p_addr + (kk >> 2) * SUB) + 2 * (kk & 3),
+                      smem_desc_sw128(v_addr + vt * SUB) + (uint64_t)(kk * 2048 >> 4), idesc_o, kk > 0 ? 1u : 0u);
+        umma_commit(&o_full[b]);
+        umma_commit(&kv_empty[s]);
+        TRACE(3, j);
+        return true;
+      };
+      // Both groups get their first S at once.  A group reports when it holds S(j) in registers:
+      // its next S is issued then, while it still exponentiates; P V follows when it reports P(j).
+      // With two stages only, S(j + 2) needs the stage that P V of block j frees, so it comes after.
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      if (ok) ok = issue_s(0);
+      if (ok && n_kb > 1) ok = issue_s(1);
+      for (int j = 0; j < n_kb && ok; ++j) {
+        if (STAGES >= 3) {
+          ok = mbar_wait(&s_free[j & 1], (j >> 1) & 1, abort_flag);
+          if (ok && j + 2 < n_kb) ok = issue_s(j + 2);
+          if (ok) ok = mbar_wait(&p_full[j & 1], (j >> 1) & 1, abort_flag);
+          if (ok) ok = issue_pv(j);
+        } else {
+          ok = mbar_wait(&p_full[j & 1], (j >> 1) & 1, abort_flag);
+          if (ok) ok = issue_pv(j);
+          if (ok && j + 2 < n_kb) ok = issue_s(j + 2);
+        }
       }
-      if (ok) ok = issue_pv(n_kb - 1);
       if (!ok) {
         *abort_flag = 1;
         atomicCAS(a.error_word, 0, ERR_MMA);
         umma_commit(&s_full[0]);   // release whoever waits
         umma_commit(&s_full[1]);
-        umma_commit(o_full);
+        umma_commit(&o_full[0]);
+        umma_commit(&o_full[1]);
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax: two threads per row
-    const int quad = warp & 3, half = warp >> 2;     // tensor-memory lanes 32 * quad ..; keys 64 * half ..
+    // ------------------------------------------------------------------ softmax: two groups, one thread per row
+    const int quad = warp & 3, g = warp >> 2;        // tensor-memory lanes 32 * quad ..; group g takes blocks j % 2 == g
     const int r = quad * 32 + lane;                  // row of the tile = tensor-memory lane
     const int R = row0 + r;
     const bool row_valid = seq >= 0 && R < n_rows;
     const int row_pos = row_valid ? pos0 + R / group : -1;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const uint32_t s_addr = lane_addr + g * BN, o_addr = lane_addr + O_COL + g * D;
     float m = -INFINITY, l = 0.0f, corr_prev = 1.0f;
-    float o[DH];
+    float o[D];
 #pragma unroll
-    for (int i = 0; i < DH; ++i) o[i] = 0.0f;
-    // O(j) = O(j - 1) * corr(j) + O_block(j), added once the MMA thread reports O_block(j)
+    for (int i = 0; i < D; ++i) o[i] = 0.0f;
+    // O = O * corr + O_block(j), once the MMA thread reports the group's O_block(j)
     auto add_block = [&](int j, float corr) -> bool {
-      if (!mbar_wait(o_full, j & 1, abort_flag) || *abort_flag) return false;
+      if (!mbar_wait(&o_full[g], (j >> 1) & 1, abort_flag) || *abort_flag) return false;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      uint32_t v[DH];
 #pragma unroll
-      for (int c0 = 0; c0 < DH; c0 += 32) tmem_load32_nowait(lane_addr + O_COL + half * DH + c0, v + c0);
-      tmem_wait_loads();
+      for (int c0 = 0; c0 < D; c0 += 64) {
+        uint32_t v[64];
+        tmem_load32_nowait(o_addr + c0, v);
+        tmem_load32_nowait(o_addr + c0 + 32, v + 32);
+        tmem_wait_loads();
 #pragma unroll
-      for (int i = 0; i < DH; ++i) o[i] = o[i] * corr + __uint_as_float(v[i]);
+        for (int i = 0; i < 64; ++i) o[c0 + i] = o[c0 + i] * corr + __uint_as_float(v[i]);
+      }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(o_empty);
+      mbar_arrive(&o_empty[g]);
       return true;
     };
     bool ok = true;
-    for (int j = 0; j < n_kb && ok; ++j) {
-      const int b = j & 1;
-      const int key0 = (kb_lo + j) * BN + half * 64;   // first key of this thread's half
-      ok = mbar_wait(&s_full[b], (j >> 1) & 1, abort_flag) && !*abort_flag;
+    int last = -1;
+    for (int j = g; j < n_kb && ok; j += 2) {
+      const int key0 = (kb_lo + j) * BN;
+      ok = mbar_wait(&s_full[g], (j >> 1) & 1, abort_flag) && !*abort_flag;
       if (!ok) break;
       if (threadIdx.x == 0) TRACE(4, j);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const bool all_visible = (kb_lo + j) * BN + BN - 1 <= tile_min_pos &&
-                               (a.window <= 0 || (kb_lo + j) * BN > tile_max_pos - a.window);
-      uint32_t v[64];
-      tmem_load32_nowait(lane_addr + b * BN + half * 64, v);
-      tmem_load32_nowait(lane_addr + b * BN + half * 64 + 32, v + 32);
-      tmem_wait_loads();
+      const bool all_visible = key0 + BN - 1 <= tile_min_pos && (a.window <= 0 || key0 > tile_max_pos - a.window);
+      // pass 1: the row's maximum
       float mx = -INFINITY;
-      if (all_visible) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-      } else {
+      for (int h = 0; h < 2; ++h) {
+        uint32_t v[64];
+        tmem_load32_nowait(s_addr + h * 64, v);
+        tmem_load32_nowait(s_addr + h * 64 + 32, v + 32);
+        tmem_wait_loads();
+        if (all_visible) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
-          const int key = key0 + i;
-          const bool visible = key <= row_pos && (a.window <= 0 || key > row_pos - a.window);
-          if (!visible) v[i] = 0xff800000u;   // -inf: gives probability 0 below
-          mx = fmaxf(mx, __uint_as_float(v[i]));
+          for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const int key = key0 + h * 64 + i;
+            const bool visible = key <= row_pos && (a.window <= 0 || key > row_pos - a.window);
+            if (visible) mx = fmaxf(mx, __uint_as_float(v[i]));
+          }
         }
       }
-      // the row's maximum over both halves
-      row_max[(b * 2 + half) * 128 + r] = mx;
-      mbar_arrive(&x_bar[b]);                          // (a bounded wait, unlike a hardware barrier)
-      ok = mbar_wait(&x_bar[b], (j >> 1) & 1, abort_flag);
-      if (!ok) break;
       if (threadIdx.x == 0) TRACE(5, j);
-      mx = fmaxf(mx, row_max[(b * 2 + (half ^ 1)) * 128 + r]);
       const float m_new = fmaxf(m, mx * a.scale_log2);       // scale > 0: the maximum commutes with it
       const float m_use = m_new == -INFINITY ? 0.0f : m_new;
       const float corr = fast_exp2(m - m_use);                 // m = -inf gives 0
       m = m_new;
       l *= corr;
-      // probabilities into shared memory as the A operand of P V: this thread's 64 keys are one sub-tile
-      uint8_t* p_tile = p_smem + b * P_BYTES + half * SUB;
+      // pass 2: probabilities into shared memory as the A operand of P V (two sub-tiles of 64 keys)
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        uint32_t packed[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(v[ch * 8 + 2 * e]), a.scale_log2, -m_use));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(v[ch * 8 + 2 * e + 1]), a.scale_log2, -m_use));
-          l += p0 + p1;
-          packed[e] = pack_bf16(p0, p1);
+      for (int h = 0; h < 2; ++h) {
+        uint32_t v[64];
+        tmem_load32_nowait(s_addr + h * 64, v);
+        tmem_load32_nowait(s_addr + h * 64 + 32, v + 32);
+        tmem_wait_loads();
+        if (h == 1) {   // the last read of S(j): the MMA thread may overwrite the buffer with S(j + 2)
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          mbar_arrive(&s_free[g]);
         }
-        *reinterpret_cast<uint4*>(p_tile + swizzled(r, ch)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        if (!all_visible) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const int key = key0 + h * 64 + i;
+            const bool visible = key <= row_pos && (a.window <= 0 || key > row_pos - a.window);
+            if (!visible) v[i] = 0xff800000u;   // -inf: probability 0
+          }
+        }
+        uint8_t* p_tile = p_smem + g * P_BYTES + h * SUB;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          uint32_t packed[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(v[ch * 8 + 2 * e]), a.scale_log2, -m_use));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(v[ch * 8 + 2 * e + 1]), a.scale_log2, -m_use));
+            l += p0 + p1;
+            packed[e] = pack_bf16(p0, p1);
+          }
+          *reinterpret_cast<uint4*>(p_tile + swizzled(r, ch)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      mbar_arrive(&p_full[b]);
+      mbar_arrive(&p_full[g]);
       if (threadIdx.x == 0) TRACE(6, j);
-      if (j > 0) ok = add_block(j - 1, corr_prev);   // the block before, whose P V ran meanwhile
+      if (last >= 0) ok = add_block(last, corr_prev);   // the group's block before, whose P V ran meanwhile
       if (threadIdx.x == 0) TRACE(7, j);
       corr_prev = corr;
+      last = j;
     }
-    if (ok && n_kb > 0) ok = add_block(n_kb - 1, corr_prev);
+    if (ok && last >= 0) ok = add_block(last, corr_prev);
     if (!ok) {
       *abort_flag = 1;
       atomicCAS(a.error_word, 0, ERR_SOFTMAX);
     }
-    // the row's sum over both halves, through the maxima buffer that the last block did not use
-    // (every thread is past that buffer's last read once it has passed the last block's exchange)
-    float* row_sum = row_max + (n_kb & 1) * 2 * 128;   // [2 halves][128 rows]
-    row_sum[half * 128 + r] = l;
-    mbar_arrive(sum_bar);
-    if (ok) ok = mbar_wait(sum_bar, 0, abort_flag);
-    l += row_sum[(half ^ 1) * 128 + r];
-    if (ok && row_valid) {
-      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-      const int token = R / group, head = kvh * group + R % group;
-      uint4* dst = reinterpret_cast<uint4*>(a.out + ((long long)(q_start + token) * a.q_heads + head) * D + half * DH);
+    // ---- merge the two groups.  First everybody must be done with the stages (the MMAs that read
+    // them have all completed once both groups have added their last O_block), then each thread
+    // parks (maximum, sum, O) of its row there, then each thread finishes half of its row.
+    float* park = reinterpret_cast<float*>(kv_smem);   // [2 groups][128 rows][D + 2]
+    mbar_arrive(done_bar);
+    if (ok) ok = mbar_wait(done_bar, 0, abort_flag);
+    float* mine = park + ((size_t)g * 128 + r) * (D + 2);
+    mine[0] = m;
+    mine[1] = l;
 #pragma unroll
-      for (int c = 0; c < DH / 8; ++c)
-        dst[c] = make_uint4(pack_bf16(o[8 * c] * inv, o[8 * c + 1] * inv), pack_bf16(o[8 * c + 2] * inv, o[8 * c + 3] * inv),
-                            pack_bf16(o[8 * c + 4] * inv, o[8 * c + 5] * inv), pack_bf16(o[8 * c + 6] * inv, o[8 * c + 7] * inv));
+    for (int i = 0; i < D; ++i) mine[2 + i] = o[i];
+    mbar_arrive(merge_bar);
+    if (ok) ok = mbar_wait(merge_bar, 0, abort_flag);
+    if (ok && row_valid) {
+      const float* a0 = park + ((size_t)0 * 128 + r) * (D + 2);
+      const float* a1 = park + ((size_t)1 * 128 + r) * (D + 2);
+      const float m0 = a0[0], m1 = a1[0];
+      const float mm = fmaxf(m0, m1);
+      const float f0 = m0 == -INFINITY ? 0.0f : fast_exp2(m0 - mm), f1 = m1 == -INFINITY ? 0.0f : fast_exp2(m1 - mm);
+      const float total = a0[1] * f0 + a1[1] * f1;
+      const float inv = total > 0.0f ? 1.0f / total : 0.0f;
+      const int token = R / group, head = kvh * group + R % group;
+      uint4* dst = reinterpret_cast<uint4*>(a.out + ((long long)(q_start + token) * a.q_heads + head) * D + g * DH);
+      const float* x0 = a0 + 2 + g * DH;
+      const float* x1 = a1 + 2 + g * DH;
+#pragma unroll
+      for (int c = 0; c < DH / 8; ++c) {
+        float y[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] = (x0[8 * c + e] * f0 + x1[8 * c + e] * f1) * inv;
+        dst[c] = make_uint4(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]), pack_bf16(y[4], y[5]), pack_bf16(y[6], y[7]));
+      }
     }
   }
 
