@@ -201,18 +201,18 @@ gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_
   // One stage's loads, in two halves: the weight tiles depend on no other kernel and may be
   // fetched before pdl_wait(); the activation tile is another kernel's output and may not.
   // The first half arms the stage's barrier with the bytes of both.
-  auto issue_weights = [&](int i, int s) {   // k block i of this split into stage s
+  auto issue_weights = [&](int i, int s, int which) {   // which: 0 = arm + first tile, 1 = second tile, 2 = both
     uint8_t* stage = smem + s * geo.stage_bytes;
-    mbar_expect_tx(&full_bar[s], geo.stage_bytes);
+    if (which != 1) mbar_expect_tx(&full_bar[s], geo.stage_bytes);
     const int k0 = (kb_begin + i) * BK;
     if (ORIENT == 0) {
-      tma_load_2d(stage, &map_w, &full_bar[s], k0, f0);   // MODE 1: map_w's box has 64 rows
-      if (MODE == 1) tma_load_2d(stage + A_BYTES / 2, &map_w, &full_bar[s], k0, up_row_offset + f0);
+      if (which != 1) tma_load_2d(stage, &map_w, &full_bar[s], k0, f0);   // MODE 1: map_w's box has 64 rows
+      if (MODE == 1 && which != 0) tma_load_2d(stage + A_BYTES / 2, &map_w, &full_bar[s], k0, up_row_offset + f0);
     } else {
       uint8_t* b_tile = stage + A_BYTES;
-      tma_load_2d(b_tile, &map_w, &full_bar[s], k0, f0);
+      if (which != 1) tma_load_2d(b_tile, &map_w, &full_bar[s], k0, f0);
       // MODE 1: map_w's box has BN/2 rows: gate rows above, the matching up rows below
-      if (MODE == 1) tma_load_2d(b_tile + geo.b_bytes / 2, &map_w, &full_bar[s], k0, up_row_offset + f0);
+      if (MODE == 1 && which != 0) tma_load_2d(b_tile + geo.b_bytes / 2, &map_w, &full_bar[s], k0, up_row_offset + f0);
     }
   };
   auto issue_activations = [&](int i, int s) {
@@ -235,7 +235,7 @@ gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    for (int i = 0; i < n_early; ++i) issue_weights(i, i);   // overlaps the tail of the kernel before
+    for (int i = 0; i < n_early; ++i) issue_weights(i, i, 2);   // overlaps the tail of the kernel before
     pdl_wait();
     for (int i = 0; i < n_early; ++i) issue_activations(i, i);
   }
@@ -253,7 +253,10 @@ gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
-    if (lane == 0) {
+    // Issuing a TMA copy costs the issuing thread a few hundred cycles, so a stage's copies are
+    // shared: lane 0 arms the barrier and fetches the weight tile(s), lane 1 the activations.
+    // (A third lane for the second weight tile of a SwiGLU product measured slower.)
+    if (lane < 2) {
       int armed = n_early;
       // stage and phase advance by counting: a division per k block would slow the issue down
       int s = n_early == geo.stages ? 0 : n_early;
@@ -264,12 +267,12 @@ gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_
           atomicCAS(error_word, 0, ERR_TIMEOUT_PRODUCER);
           break;
         }
-        issue_weights(i, s);
-        issue_activations(i, s);
+        if (lane == 1) issue_activations(i, s);
+        else issue_weights(i, s, 2);
         armed = i + 1;
         if (++s == geo.stages) { s = 0; phase ^= 1; }
       }
-      if (*abort_flag) {
+      if (lane == 0 && *abort_flag) {
         // copies already issued still land in shared memory: wait for them (bounded) before leaving
         for (int i = max(0, armed - geo.stages); i < armed; ++i) {
           const unsigned long long start = global_timer();
