@@ -1,6 +1,7 @@
 """`llm-kernel-bench`: one kernel of the engine alone, timed with CUDA events, beside its roofline.
 
     bin/llm-kernel-bench gemm --rows 8 --out 2560 --in 2048 [--swiglu] [--partials]
+    bin/llm-kernel-bench gemv --tokens 8 --out 5632 --in 2048 --form swiglu --norm
     bin/llm-kernel-bench attention --batch 8 --q-len 1 --context 2048 --heads 32 --kv-heads 4 --head-dim 64
     bin/llm-kernel-bench norm --rows 2048 --hidden 2048 --partials 1
     bin/llm-kernel-bench rope --rows 2048 --heads 32 --kv-heads 4 --head-dim 64
@@ -106,6 +107,56 @@ def bench_gemm(a):
             weight_bytes + a.rows * a.inner * 2 + out_bytes, 2.0 * a.rows * n * a.inner)
 
 
+def bench_gemv(a):
+    """The few-token fused product: --form plain | add | swiglu | rope (out = (heads + 2 kv heads) * head dim),
+    --norm takes the input from a float32 residual stream through RMSNorm."""
+    import torch
+    from ..kernels import gemv
+    from ..kernels import lib as K
+    ctx = _ctx(max(a.tokens, 16))
+    ctx.dtype = torch.bfloat16
+    n = 2 * a.out if a.form == "swiglu" else a.out
+    weight_bytes = n * a.inner * 2
+    copies = max(1, min(64, -(-a.l2_mb * (1 << 20) * 2 // weight_bytes)))
+    weights = [(torch.randn(n, a.inner, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(copies)]
+    residual = torch.randn(a.tokens, a.inner, device="cuda")
+    norm_w = torch.ones(a.inner, device="cuda", dtype=torch.bfloat16)
+    x_plain = torch.randn(a.tokens, a.inner, device="cuda").to(torch.bfloat16)
+    target = torch.zeros(a.tokens, a.out, device="cuda")
+    epilogue = None
+    if a.form == "add":
+        epilogue = K.AddTo(target)
+    elif a.form == "rope":
+        d, kvh = a.head_dim, a.kv_heads
+        heads = a.out // d - 2 * kvh
+        page, blocks = 64, 4
+        elems = 2 * kvh * page * d
+        storage = torch.zeros(a.tokens * blocks, elems, device="cuda", dtype=torch.bfloat16)
+        table = torch.arange(a.tokens * blocks, dtype=torch.int32, device="cuda").view(a.tokens, blocks)
+        view = K.CacheView(storage.data_ptr(), storage.data_ptr() + elems, table, elems, blocks, page, kvh, d, torch.bfloat16)
+        pos = torch.full((a.tokens,), 100, dtype=torch.int32, device="cuda")
+        seq = torch.arange(a.tokens, dtype=torch.int32, device="cuda")
+        inv = (1.0 / (10000.0 ** (torch.arange(d // 2, dtype=torch.float32) * 2.0 / d))).cuda()
+        q_out = torch.empty(a.tokens, heads * d, device="cuda", dtype=torch.bfloat16)
+        epilogue = K.RotateAndCache(q_out, view, pos, seq, inv, heads, True)
+    state = {"i": 0}
+
+    def run():
+        w = weights[state["i"] % copies]
+        state["i"] += 1
+        if getattr(a, "prefetch", False):       # as inside a step: each launch pulls the next launch's weights towards L2
+            nxt = weights[state["i"] % copies]
+            ctx.gemv_prev = [(w.data_ptr(), weight_bytes), (nxt.data_ptr(), weight_bytes)]
+            ctx.gemv_now = []
+        x = K.LazyNorm(ctx, residual, norm_w, 1e-5, a.tokens, None, "normed") if a.norm else x_plain
+        gemv.run(ctx, w, x, a.tokens, torch.bfloat16 if a.form == "swiglu" else torch.float32, "out",
+                 a.form == "swiglu", epilogue)
+
+    us = _time(run, a.iters, a.warmup)
+    _report(f"gemv tokens={a.tokens} out={a.out} in={a.inner} form={a.form} norm={a.norm} copies={copies}", us,
+            weight_bytes + a.tokens * a.inner * (4 if a.norm else 2) + a.tokens * a.out * 4, 2.0 * a.tokens * n * a.inner)
+
+
 def bench_attention(a):
     import torch
     from ..kernels import attention as fast
@@ -188,6 +239,16 @@ def main(argv=None) -> int:
     g.add_argument("--swiglu", action="store_true")
     g.add_argument("--partials", action="store_true", help="float32 output that may be split over K")
     g.add_argument("--l2-mb", type=int, default=126)
+    v = sub.add_parser("gemv", parents=[common])
+    v.add_argument("--tokens", type=int, default=8)
+    v.add_argument("--out", type=int, required=True, help="output features (per half with --form swiglu)")
+    v.add_argument("--in", dest="inner", type=int, required=True)
+    v.add_argument("--form", default="plain", choices=["plain", "add", "swiglu", "rope"])
+    v.add_argument("--norm", action="store_true")
+    v.add_argument("--prefetch", action="store_true", help="each launch prefetches the next launch's weights into L2")
+    v.add_argument("--kv-heads", type=int, default=4)
+    v.add_argument("--head-dim", type=int, default=64)
+    v.add_argument("--l2-mb", type=int, default=126)
     t = sub.add_parser("attention", parents=[common])
     for name, default in (("batch", 8), ("q-len", 1), ("context", 2048), ("heads", 32), ("kv-heads", 4),
                           ("head-dim", 64), ("page", 64)):
@@ -201,7 +262,7 @@ def main(argv=None) -> int:
         r.add_argument(f"--{name}", type=int, default=default)
     args = ap.parse_args(argv)
     GRAPH[0] = not args.no_graph
-    {"gemm": bench_gemm, "attention": bench_attention, "norm": bench_norm, "rope": bench_rope}[args.kernel](args)
+    {"gemm": bench_gemm, "gemv": bench_gemv, "attention": bench_attention, "norm": bench_norm, "rope": bench_rope}[args.kernel](args)
     return 0
 
 

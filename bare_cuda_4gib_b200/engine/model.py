@@ -120,7 +120,8 @@ class Model:
             pending = self.blocks[call.layer].forward(ctx, ctx.calls[i], x, pending)
         if ctx.n_want == 0:
             return None
-        normed = self.final_norm.forward(ctx, x, pending, ctx.n_want, ctx.want_rows, buffer="final_normed")
+        normed = self.final_norm.forward(ctx, x, pending, ctx.n_want, ctx.want_rows, buffer="final_normed",
+                                         lazy=getattr(self.head, "takes_lazy_input", False))
         return self.head.forward(ctx, normed, ctx.n_want)
 
 

@@ -87,6 +87,9 @@ class StepContext:
         self.max_q_len = 0
         self.max_kv_len = 0
         self.extras: Dict[object, object] = {}
+        self.residual = None       # the float32 residual stream while a layer runs
+        self.gemv_prev: list = []  # the few-token products of the previous step, in call order
+        self.gemv_now: list = []
 
 
 def padded_batch(n: int) -> int:
@@ -279,6 +282,7 @@ class StepRunner:
         c.host_slots = slots
         c.stream = torch.cuda.current_stream().cuda_stream
         c.extras.clear()
+        c.gemv_prev, c.gemv_now = c.gemv_now, []
         self.model.plan_step(c)
         return decode, n_want
 

@@ -128,6 +128,46 @@ class Partials:
         return self.tensor.shape[-1]
 
 
+class AddTo:
+    """Asks a product to add its result into the float32 residual stream itself."""
+
+    __slots__ = ("residual",)
+
+    def __init__(self, residual: torch.Tensor):
+        self.residual = residual
+
+
+class RotateAndCache:
+    """Asks the [q; k; v] product to rotate q and k by position, write q to `q_out` and put k and
+    v into the cache (what `rope_cache_write` does as a kernel of its own)."""
+
+    __slots__ = ("q_out", "cache", "positions", "row_seq", "inv_freq", "q_heads", "write_cache")
+
+    def __init__(self, q_out, cache, positions, row_seq, inv_freq, q_heads, write_cache):
+        self.q_out, self.cache, self.positions, self.row_seq = q_out, cache, positions, row_seq
+        self.inv_freq, self.q_heads, self.write_cache = inv_freq, q_heads, write_cache
+
+
+class LazyNorm:
+    """rms_norm(residual rows) * weight that has not been computed: a product that can norm its
+    own input takes it as it is, everything else calls `materialize()`."""
+
+    __slots__ = ("ctx", "residual", "weight", "eps", "rows", "row_index", "buffer")
+
+    def __init__(self, ctx, residual, weight, eps, rows, row_index, buffer):
+        self.ctx, self.residual, self.weight, self.eps = ctx, residual, weight, eps
+        self.rows, self.row_index, self.buffer = rows, row_index, buffer
+
+    def materialize(self) -> torch.Tensor:
+        out = self.ctx.ws.get(self.buffer, (self.rows, self.residual.shape[-1]), self.ctx.dtype)
+        add_rmsnorm(self.residual, None, self.weight, out, self.eps, self.rows, self.row_index, self.ctx.stream)
+        return out
+
+
+def materialize(h):
+    return h.materialize() if isinstance(h, LazyNorm) else h
+
+
 def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, n_tokens: int, stream=None) -> None:
     _dev(table, ids, out)
     _check(plain().lib.llm_embed_gather(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(),

@@ -71,16 +71,20 @@ class Attention(Part):
             from ..kernels import attention as fast
             fast.step_tiles(ctx, self.fast)
 
-    def forward(self, ctx, call, h: torch.Tensor) -> K.Partials:
+    takes_lazy_input = True
+
+    def forward(self, ctx, call, h):
         n = ctx.n_tokens
         qd = self.heads * self.head_dim
         # few rows: float32 partial results let the product split its inner dimension over more SMs
         qkv_dtype = torch.float32 if n <= 256 else ctx.dtype
-        qkv = self.qkv.forward(ctx, h, n, qkv_dtype, "qkv", allow_partials=True)
         q = ctx.ws.get("q", (n, qd), ctx.dtype)
         inv_freq = self.position.fused_rotation()
-        K.rope_cache_write(qkv, q, call.cache, ctx.positions, ctx.row_seq, inv_freq, self.heads,
-                           call.writes_cache, n, ctx.stream)
+        rotate = K.RotateAndCache(q, call.cache, ctx.positions, ctx.row_seq, inv_freq, self.heads, call.writes_cache)
+        qkv = self.qkv.forward(ctx, h, n, qkv_dtype, "qkv", allow_partials=True, epilogue=rotate)
+        if qkv is not None:
+            K.rope_cache_write(qkv, q, call.cache, ctx.positions, ctx.row_seq, inv_freq, self.heads,
+                               call.writes_cache, n, ctx.stream)
         out = ctx.ws.get("attn_out", (n, qd), ctx.dtype)
         window = int(self.window) if self.window else 0
         if self.fast is not None and ctx.use_fast_attention:
@@ -89,4 +93,6 @@ class Attention(Part):
         else:
             K.attention_plain(q, out, call.cache, ctx.positions, ctx.row_seq, self.heads, n,
                               self.scale, window, ctx.stream)
-        return self.o.forward(ctx, out, n, torch.float32, "attn_proj", allow_partials=True)
+        residual = getattr(ctx, "residual", None)
+        return self.o.forward(ctx, out, n, torch.float32, "attn_proj", allow_partials=True,
+                              epilogue=K.AddTo(residual) if residual is not None else None)

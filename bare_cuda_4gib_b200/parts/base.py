@@ -2,15 +2,19 @@
 
 Families and the one method each must have besides `weight_specs` / `bind`:
 
-* norm          `forward(ctx, residual, delta, rows, row_index=None) -> activations`
+* norm          `forward(ctx, residual, delta, rows, row_index=None, buffer=..., lazy=False) -> activations`
                 adds `delta` (a `Partials`, or None) into the float32 residual stream, then
-                normalises; returns [rows, hidden] in the step's activation type.
+                normalises; returns [rows, hidden] in the step's activation type.  With `lazy`
+                it may return a `LazyNorm` (see kernels.lib) instead, which the consumer either
+                hands to a `Linear` or turns into a matrix with `materialize()`; the block asks
+                for that only of consumers that declare `takes_lazy_input = True`.
 * position      either `fused_rotation()` -> float32 inverse frequencies [head_dim / 2] that the
                 attention kernels apply themselves, or `apply(ctx, q, k)` on separate tensors.
-* mixer         `forward(ctx, call, h) -> Partials` (the mixer's contribution to the residual);
+* mixer         `forward(ctx, call, h) -> Partials` (the mixer's contribution to the residual), or
+                None if it has added the contribution into `ctx.residual` itself;
                 `cache_request()` -> `KVCacheRequest` or None; `state_request()` ->
                 `StateRequest` or None.  The cache manager serves both.
-* feed_forward  `forward(ctx, h) -> Partials`
+* feed_forward  `forward(ctx, h) -> Partials`, or None as for a mixer
 * block         `forward(ctx, call, residual, pending) -> Partials`: runs one layer; `pending` is
                 the previous layer's contribution that has not been added to the residual yet.
 * embedding     `forward(ctx) -> residual [tokens, hidden] float32`

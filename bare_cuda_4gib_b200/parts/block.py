@@ -2,7 +2,9 @@
 
 "prenorm": x += mixer(norm(x)); x += feed_forward(norm(x))
 (cuongvng/bare-cuda-4gib engine/src/model.cpp:526-604).  Each add is carried out by the norm
-that follows it, so a layer hands its last contribution on, not yet added, as `pending`.
+that follows it, so a layer hands its last contribution on, not yet added, as `pending` - unless
+the part's last kernel added it into the residual stream itself (`ctx.residual`), in which case the
+part returns None.
 """
 
 from __future__ import annotations
@@ -24,7 +26,8 @@ class PreNormBlock:
 
     def forward(self, ctx, call, residual, pending):
         n = ctx.n_tokens
-        h = self.mixer_norm.forward(ctx, residual, pending, n)
+        ctx.residual = residual      # a part may add its contribution here itself and return None
+        h = self.mixer_norm.forward(ctx, residual, pending, n, lazy=getattr(self.mixer, "takes_lazy_input", False))
         mixed = self.mixer.forward(ctx, call, h)
-        h = self.ffn_norm.forward(ctx, residual, mixed, n)
+        h = self.ffn_norm.forward(ctx, residual, mixed, n, lazy=getattr(self.ffn, "takes_lazy_input", False))
         return self.ffn.forward(ctx, h)

@@ -40,5 +40,7 @@ class OutputHead(Part):
         self.linear = Linear(self.tensors["weight"], "lm_head")
         self.linear.prepare(dtype)
 
-    def forward(self, ctx, normed: torch.Tensor, rows: int) -> torch.Tensor:
+    takes_lazy_input = True
+
+    def forward(self, ctx, normed, rows: int) -> torch.Tensor:
         return self.linear.forward(ctx, normed, rows, torch.float32, "logits").tensor

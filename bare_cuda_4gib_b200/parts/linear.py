@@ -22,17 +22,28 @@ class Linear:
         self.name = name
         self.out_features, self.in_features = weight.shape
         self.fast = None  # set by prepare() when the tensor-core kernel takes this matrix
+        self.few = False  # whether the few-token fused kernel takes this matrix
 
     def prepare(self, act_dtype: torch.dtype) -> None:
         if act_dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16 and self.weight.is_cuda:
             from ..kernels import gemm
             self.fast = gemm.plan_for(self.weight)
+            from ..kernels import gemv
+            self.few = gemv.supports(self.weight)
 
-    def forward(self, ctx, a: torch.Tensor, rows: int, out_dtype: torch.dtype, buffer: str,
-                allow_partials: bool = False, swiglu: bool = False) -> K.Partials:
+    def forward(self, ctx, a, rows: int, out_dtype: torch.dtype, buffer: str,
+                allow_partials: bool = False, swiglu: bool = False, epilogue=None) -> Optional[K.Partials]:
         """a[:rows] @ W^T into the workspace buffer `buffer`.  With `swiglu`, W is [gate; up] and
-        the result is silu(gate) * up of half the width (fused where the kernel can)."""
+        the result is silu(gate) * up of half the width (fused where the kernel can).  `a` is a
+        matrix or a `LazyNorm`.  `epilogue` (`AddTo`, `RotateAndCache`) names what the caller will
+        do with the result next: a kernel that can do it itself does, and None comes back; from
+        every other kernel the plain result comes back and the epilogue stays the caller's."""
         width = self.out_features // 2 if swiglu else self.out_features
+        if self.few and ctx.use_fast_gemm:
+            from ..kernels import gemv
+            if gemv.takes(rows, self.in_features):
+                return gemv.run(ctx, self.weight, a, rows, out_dtype, buffer, swiglu, epilogue)
+        a = K.materialize(a)
         if self.fast is not None and ctx.use_fast_gemm:
             from ..kernels import gemm
             return gemm.run(ctx, self.fast, a, rows, out_dtype, buffer, allow_partials, swiglu)

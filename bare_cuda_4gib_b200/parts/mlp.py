@@ -31,7 +31,11 @@ class SwiGLUFeedForward(Part):
         self.gate_up.prepare(dtype)
         self.down.prepare(dtype)
 
-    def forward(self, ctx, h: torch.Tensor) -> K.Partials:
+    takes_lazy_input = True
+
+    def forward(self, ctx, h):
         n = ctx.n_tokens
         act = self.gate_up.forward(ctx, h, n, ctx.dtype, "ffn_act", swiglu=True)
-        return self.down.forward(ctx, act.tensor, n, torch.float32, "ffn_out", allow_partials=True)
+        residual = getattr(ctx, "residual", None)
+        return self.down.forward(ctx, act.tensor, n, torch.float32, "ffn_out", allow_partials=True,
+                                 epilogue=K.AddTo(residual) if residual is not None else None)

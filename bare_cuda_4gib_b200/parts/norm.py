@@ -25,7 +25,14 @@ class RMSNorm(Part):
         return {"weight": ((self.params["size"],), "norm")}
 
     def forward(self, ctx, residual: torch.Tensor, delta: Optional[K.Partials], rows: int,
-                row_index: Optional[torch.Tensor] = None, buffer: str = "normed") -> torch.Tensor:
+                row_index: Optional[torch.Tensor] = None, buffer: str = "normed", lazy: bool = False):
+        """With `lazy` (the consumer takes a `LazyNorm`) and nothing to add, a few-token bfloat16
+        step gets the norm as a description that the consuming product computes in its own kernel."""
+        if lazy and delta is None and ctx.dtype == torch.bfloat16 and ctx.use_fast_gemm:
+            from ..kernels import gemv
+            if gemv.takes(rows, int(self.params["size"])) and self.tensors["weight"].is_cuda:
+                return K.LazyNorm(ctx, residual, self.tensors["weight"], float(self.params["eps"]), rows,
+                                  row_index, buffer)
         out = ctx.ws.get(buffer, (rows, self.params["size"]), ctx.dtype)
         K.add_rmsnorm(residual, delta, self.tensors["weight"], out, float(self.params["eps"]), rows,
                       row_index, ctx.stream)
