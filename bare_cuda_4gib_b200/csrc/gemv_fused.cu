@@ -65,6 +65,7 @@ struct GemvArgs {
   int x_ld;                 // shared-memory row stride of x in elements
   int kc, stages;           // k values per stage of the ring, number of stages
   int norm_rows;            // PRO_NORM: residual rows staged in shared memory at a time
+  int first_aliased;        // PRO_NORM: stages from this one on double as that staging area (else = stages)
   int* error_word;
   // input
   const void* x;            // PRO_BF16: bfloat16 [tokens, k]; PRO_NORM: float32 residual rows
@@ -187,12 +188,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_fused_kernel(const GemvArgs a
   uint8_t* ring = smem;                                                              // [stages][16][row_stride]
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(ring + (size_t)a.stages * stage_bytes);   // [8 * NT][x_ld]
   float* red = reinterpret_cast<float*>(xs + (size_t)8 * NT * a.x_ld);               // [2][WARPS][NT * 4][32]
-  float* staging = red + 2 * WARPS * NT * 4 * 32;                                    // PRO_NORM: [norm_rows][k]
-  float* norm_ws = staging + (PRO == PRO_NORM ? (size_t)a.norm_rows * a.k : 0);      // PRO_NORM: [k]
+  float* norm_ws = red + 2 * WARPS * NT * 4 * 32;                                    // PRO_NORM: [k]
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(norm_ws + (PRO == PRO_NORM ? a.k : 0));
   uint64_t* empty_bar = full_bar + MAX_STAGES;
   uint64_t* x_bar = empty_bar + MAX_STAGES;
-  volatile int* gave_up = reinterpret_cast<volatile int*>(x_bar + 1);
+  uint64_t* norm_done = x_bar + 1;
+  volatile int* gave_up = reinterpret_cast<volatile int*>(norm_done + 1);
+  // PRO_NORM: residual rows are staged as float32 [norm_rows][k] in the ring's last stages, which
+  // the producer leaves alone until the norm is done
+  float* staging = reinterpret_cast<float*>(ring + (size_t)a.first_aliased * stage_bytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 
   TRACE(0);
@@ -202,6 +206,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_fused_kernel(const GemvArgs a
       mbar_init(&empty_bar[s], WARPS);
     }
     mbar_init(x_bar, 1);
+    mbar_init(norm_done, 1);
     *gave_up = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -213,6 +218,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_fused_kernel(const GemvArgs a
     int stage = 0;
     uint32_t phase = 0;
     uint32_t in_flight = 0, in_flight_parity = 0;   // per stage: a load was issued / with which parity
+    bool staging_free = false;
     for (int item = blockIdx.x; item < a.n_items; item += gridDim.x) {
       int lo, hi;
       item_rows<EPI>(a, item, lane & 7, lo, hi);
@@ -220,6 +226,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_fused_kernel(const GemvArgs a
       for (int k0 = 0; k0 < a.k; k0 += a.kc) {
         const int len = min(a.kc, a.k - k0);
         bool ok = true;
+        if (PRO == PRO_NORM && stage >= a.first_aliased && !staging_free) {
+          if (lane == 0) ok = mbar_wait(norm_done, 0, gave_up, a.error_word, ERR_GEMV_PRODUCER);
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) goto producer_done;
+          staging_free = true;
+        }
         if (lane == 0) ok = mbar_wait(&empty_bar[stage], phase ^ 1u, gave_up, a.error_word, ERR_GEMV_PRODUCER);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) goto producer_done;
@@ -284,6 +296,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_fused_kernel(const GemvArgs a
           }
         }
         mbar_wait(x_bar, x_phase, gave_up, a.error_word, ERR_GEMV_CONSUMER);
+        TRACE(6);
         x_phase ^= 1u;
       }
       for (int j = warp; j < a.norm_rows && r0 + j < 8 * NT; j += WARPS) {
@@ -332,6 +345,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_fused_kernel(const GemvArgs a
   }
   TRACE(3);
   consumer_barrier();
+  if (PRO == PRO_NORM && threadIdx.x == 0) mbar_arrive(norm_done);
   TRACE(4);
 
   int buf = 0, stage = 0;
@@ -498,7 +512,7 @@ int launch_pro(int pro, int epi, const GemvArgs& a, size_t smem, int grid, cudaS
 // How a launch lays out shared memory: the stage size kc (k values), the number of stages, the
 // residual rows staged at a time, and the total.  Returns false if x and two stages do not fit.
 struct SmemPlan {
-  int x_ld, kc, stages, norm_rows;
+  int x_ld, kc, stages, norm_rows, first_aliased;
   size_t bytes;
 };
 
@@ -512,25 +526,30 @@ static bool plan_smem(int tokens, int k, int pro, SmemPlan& p) {
     kc_wish = v ? atoi(v) : 2048;
     if (kc_wish < 32 || kc_wish % 32) kc_wish = 2048;
   }
-  // staging of residual rows: as many as leave the ring at least 96 KB, else fewer
-  for (int want_ring = 96 * 1024; want_ring >= 0; want_ring -= 96 * 1024)
-    for (int rows = 8; rows >= 1; rows /= 2) {
-      p.norm_rows = pro == PRO_NORM ? rows : 0;
-      const size_t fixed = (size_t)8 * nt * p.x_ld * 2 + (size_t)2 * WARPS * nt * 4 * 32 * 4 +
-                           (size_t)p.norm_rows * k * 4 + (pro == PRO_NORM ? (size_t)k * 4 : 0) +
-                           (2 * MAX_STAGES + 1) * 8 + 16;
-      for (int kc = kc_wish; kc >= 128; kc /= 2) {
-        const int use = kc < k ? kc : k;
-        const size_t stage = (size_t)16 * (use * 2 + ROW_PAD);
-        if (fixed + 2 * stage > (size_t)SMEM_BUDGET) continue;
-        size_t stages = ((size_t)SMEM_BUDGET - fixed) / stage;
-        if (stages > MAX_STAGES) stages = MAX_STAGES;
-        if (stages * stage < (size_t)want_ring) continue;
-        p.kc = use, p.stages = (int)stages, p.bytes = fixed + stages * stage;
-        return true;
+  const size_t fixed = (size_t)8 * nt * p.x_ld * 2 + (size_t)2 * WARPS * nt * 4 * 32 * 4 +
+                       (pro == PRO_NORM ? (size_t)k * 4 : 0) + (2 * MAX_STAGES + 2) * 8 + 16;
+  for (int kc = kc_wish; kc >= 128; kc /= 2) {
+    const int use = kc < k ? kc : k;
+    const size_t stage = (size_t)16 * (use * 2 + ROW_PAD);
+    if (fixed + 2 * stage > (size_t)SMEM_BUDGET) continue;
+    size_t stages = ((size_t)SMEM_BUDGET - fixed) / stage;
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    p.kc = use, p.stages = (int)stages, p.bytes = fixed + stages * stage;
+    p.norm_rows = 0, p.first_aliased = (int)stages;
+    if (pro == PRO_NORM) {
+      // the staging area takes the ring's last stages; all eight rows of a token group at once if
+      // that leaves a stage for the weights meanwhile, else fewer rows at a time
+      for (int rows = 8; rows >= 1; rows /= 2) {
+        const size_t aliased = ((size_t)rows * k * 4 + stage - 1) / stage;
+        if (aliased < stages || (rows == 1 && aliased <= stages)) {
+          p.norm_rows = rows, p.first_aliased = (int)(stages - aliased);
+          break;
+        }
       }
-      if (pro != PRO_NORM) break;
+      if (p.norm_rows == 0) continue;
     }
+    return true;
+  }
   return false;
 }
 
@@ -568,7 +587,7 @@ extern "C" int llm_gemv_fused(const void* w, int w_rows, int k, int tokens, int 
   GemvArgs a = {};
   a.w = static_cast<const __nv_bfloat16*>(w);
   a.w_rows = w_rows, a.k = k, a.tokens = tokens;
-  a.x_ld = plan.x_ld, a.kc = plan.kc, a.stages = plan.stages, a.norm_rows = plan.norm_rows, a.error_word = error_word;
+  a.x_ld = plan.x_ld, a.kc = plan.kc, a.stages = plan.stages, a.norm_rows = plan.norm_rows, a.first_aliased = plan.first_aliased, a.error_word = error_word;
   a.x = x, a.x_stride = x_stride, a.norm_w = norm_w, a.norm_w_dtype = norm_w_dtype, a.eps = eps, a.row_index = row_index;
   a.out = out, a.out_dtype = out_dtype, a.out_stride = out_stride, a.n_out = n_out, a.up_offset = up_offset;
   a.cache = PagedCache{k_base, v_base, block_table, page_stride, table_stride, page_tokens, kv_heads, head_dim};

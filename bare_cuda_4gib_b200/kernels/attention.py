@@ -1,5 +1,8 @@
-"""Launcher of the tensor-core paged attention (csrc/attention_mma.cu): one library per head
-size, the per-step list of row tiles, and the choice of how many thread blocks split a tile's keys."""
+"""Launcher of the paged attention kernels: csrc/attention_mma.cu (every head size and batch
+shape), csrc/attention_tcgen05.cu (prompt portions, head sizes 64 and 128) and
+csrc/attention_decode.cu (steps of very few tokens per request, head sizes 64 and 128); one
+library per head size, the per-step list of row tiles, and the choice of how many thread blocks
+split a tile's keys."""
 
 from __future__ import annotations
 
@@ -21,7 +24,9 @@ TARGET_BLOCKS = 148 * 2
 COUNTER_WORDS = 4096          # per-tile split counters at the start of the scratch (see the kernel)
 _libs: Dict[int, object] = {}
 _tc_libs: Dict[int, object] = {}
-TC_HEAD_DIMS = (64, 128)      # head sizes the tcgen05 prefill kernel is built for
+_decode_libs: Dict[int, object] = {}
+TC_HEAD_DIMS = (64, 128)      # head sizes the tcgen05 prefill kernel and the decode kernel are built for
+DECODE_MAX_TILES = 148        # (tiles x kv heads) up to which the cluster decode kernel runs
 
 
 def supports(head_dim: int) -> bool:
@@ -61,6 +66,20 @@ def tc_lib(head_dim: int):
     return l
 
 
+def decode_lib(head_dim: int):
+    """The cluster decode kernel's library for this head size."""
+    l = _decode_libs.get(head_dim)
+    if l is None:
+        l = build.load_library("attention_decode.cu", defines(head_dim))
+        P, I, L, F = c_void_p, c_int, c_longlong, c_float
+        l.llm_attention_decode.argtypes = [P, P, L, I, P, P, P, P, P, L, I, I, I, I, P, P, P, P, P, I, I, I, I, F, I, P, P]
+        l.llm_attention_decode.restype = c_int
+        l.llm_attention_decode_pool_map.argtypes = [P, P, L, I]
+        l.llm_attention_decode_pool_map.restype = c_int
+        _decode_libs[head_dim] = l
+    return l
+
+
 class AttentionPlan:
     def __init__(self, head_dim: int, heads: int, kv_heads: int):
         self.head_dim, self.heads, self.kv_heads = head_dim, heads, kv_heads
@@ -71,10 +90,30 @@ class AttentionPlan:
         if head_dim in TC_HEAD_DIMS and not os.environ.get("BARE_CUDA_B200_NO_TC_ATTENTION"):
             self.tc = tc_lib(head_dim)
             self.prefill_rows = int(self.tc.llm_attention_tc_rows())
+        self.decode = None
+        if head_dim in TC_HEAD_DIMS and not os.environ.get("BARE_CUDA_B200_NO_DECODE_ATTENTION"):
+            self.decode = decode_lib(head_dim)
         self._host = None
         self._dev = None
         self._scratch = None
         self._pool_maps = {}
+        self._decode_maps = {}
+
+    def decode_map(self, cache: CacheView):
+        """The decode kernel's tensor map over a cache group's pool (boxes of at most 64 rows)."""
+        box_rows = math.gcd(KEY_BLOCK, cache.page_tokens)
+        key = (cache.pool_ptr, cache.pool_elems, box_rows)
+        m = self._decode_maps.get(key)
+        if m is None:
+            m = (ctypes.c_ubyte * 128)()
+            _check(self.decode.llm_attention_decode_pool_map(ctypes.addressof(m), cache.pool_ptr,
+                                                             cache.pool_elems // self.head_dim, box_rows),
+                   "attention decode pool map")
+            self._decode_maps[key] = m
+        return m, box_rows
+
+    def decode_usable(self, cache: CacheView) -> bool:
+        return self.decode is not None and cache.pool_ptr != 0 and math.gcd(KEY_BLOCK, cache.page_tokens) >= 8
 
     def pool_map(self, cache: CacheView):
         """The TMA tensor map over a cache group's whole pool (one per pool) and its box height."""
@@ -144,14 +183,34 @@ def step_tiles(ctx, plan: AttentionPlan):
             n_splits = min(key_blocks, int(os.environ["BARE_CUDA_B200_ATTN_SPLITS"]))
         if n_tiles * plan.kv_heads > COUNTER_WORDS:
             n_splits = 1
-    out = (dev[:n_tiles], dev[n_tiles: 2 * n_tiles], n_tiles, rows_per_tile, n_splits)
+    dec_splits = dec_slots = 0
+    if rows_per_tile == 16 and plan.decode is not None and n_tiles * plan.kv_heads <= DECODE_MAX_TILES:
+        # the cluster decode kernel: up to 8 blocks of 4 warps share a tile; a warp keeps `slots` key blocks in flight
+        key_blocks = -(-ctx.max_kv_len // KEY_BLOCK)
+        dec_splits = max(1, min(8, -(-TARGET_BLOCKS // (n_tiles * plan.kv_heads)), -(-key_blocks // 4)))
+        if os.environ.get("BARE_CUDA_B200_ATTN_SPLITS"):     # experiments only
+            dec_splits = max(1, min(8, int(os.environ["BARE_CUDA_B200_ATTN_SPLITS"])))
+        per_warp = -(-key_blocks // (4 * dec_splits))
+        dec_slots = 1 if (per_warp <= 2 or plan.head_dim > 64) else 2
+    out = (dev[:n_tiles], dev[n_tiles: 2 * n_tiles], n_tiles, rows_per_tile, n_splits, dec_splits, dec_slots)
     ctx.extras[key] = out
     return out
 
 
 def run(ctx, plan: AttentionPlan, q: torch.Tensor, out: torch.Tensor, cache: CacheView, scale: float,
         window: int) -> None:
-    tile_seq, tile_index, n_tiles, rows_per_tile, n_splits = step_tiles(ctx, plan)
+    tile_seq, tile_index, n_tiles, rows_per_tile, n_splits, dec_splits, dec_slots = step_tiles(ctx, plan)
+    if dec_splits and plan.decode_usable(cache):
+        from . import gemm
+        pool_map, box_rows = plan.decode_map(cache)
+        _check(plan.decode.llm_attention_decode(
+            ctypes.addressof(pool_map), cache.pool_ptr, cache.pool_elems // plan.head_dim, box_rows, q.data_ptr(),
+            out.data_ptr(), cache.k_ptr, cache.v_ptr, cache.block_table.data_ptr(), cache.page_stride,
+            cache.table_stride, cache.page_tokens, cache.kv_heads, cache.head_dim, ctx.seq_q_start.data_ptr(),
+            ctx.seq_q_len.data_ptr(), ctx.seq_kv_len.data_ptr(), tile_seq.data_ptr(), tile_index.data_ptr(), n_tiles,
+            dec_splits, dec_slots, plan.heads, scale, window, gemm.error_word(q.device).data_ptr(), ctx.stream),
+            "attention_decode")
+        return
     if plan.tc is not None and rows_per_tile != 16:
         if not plan.tc_usable(cache):
             raise KernelLaunchError(f"attention_tcgen05: cache pages of {cache.page_tokens} positions are not supported "

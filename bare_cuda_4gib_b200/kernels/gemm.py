@@ -50,7 +50,7 @@ def check_errors() -> None:
             role = {1: "gemm TMA producer", 2: "gemm MMA issuer", 3: "gemm epilogue", 11: "attention loader",
                     12: "attention MMA issuer", 13: "attention softmax",
                     14: "attention (shared memory not 1024-byte aligned)", 21: "few-token product, producer",
-                    22: "few-token product, consumer"}.get(code, f"code {code}")
+                    22: "few-token product, consumer", 31: "decode attention"}.get(code, f"code {code}")
             raise KernelLaunchError(f"a kernel gave up ({role}): a bounded wait ran out; the result is invalid")
 
 

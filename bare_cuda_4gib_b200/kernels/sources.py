@@ -8,4 +8,5 @@ def all_libraries():
     jobs = [("plain_kernels.cu", ()), ("gemm_tcgen05.cu", ()), ("gemv_fused.cu", ())]
     jobs += [("attention_mma.cu", (f"-DHEAD_DIM={d}",)) for d in ATTENTION_HEAD_DIMS]
     jobs += [("attention_tcgen05.cu", (f"-DHEAD_DIM={d}",)) for d in (64, 128)]
+    jobs += [("attention_decode.cu", (f"-DHEAD_DIM={d}",)) for d in (64, 128)]
     return jobs
