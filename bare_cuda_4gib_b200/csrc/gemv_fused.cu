@@ -54,7 +54,7 @@ enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_ROPE = 3 };
 // into a buffer set with llm_gemv_set_trace; a development aid, absent from normal builds.
 #ifdef GEMV_TRACE
 __device__ long long* g_trace = nullptr;
-#define TRACE(i) do { if (blockIdx.x == 0 && threadIdx.x == 0 && g_trace) g_trace[i] = clock64(); } while (0)
+#define TRACE(i) do { if (blockIdx.x == 0 && threadIdx.x == 0 && trace_to) trace_to[i] = clock64(); } while (0)
 #else
 #define TRACE(i) do { } while (0)
 #endif
@@ -198,7 +198,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_fused_kernel(const GemvArgs a
   // the producer leaves alone until the norm is done
   float* staging = reinterpret_cast<float*>(ring + (size_t)a.first_aliased * stage_bytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-
+#ifdef GEMV_TRACE
+  long long* const trace_to = g_trace;
+#endif
   TRACE(0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < a.stages; ++s) {
@@ -528,8 +530,12 @@ static bool plan_smem(int tokens, int k, int pro, SmemPlan& p) {
   }
   const size_t fixed = (size_t)8 * nt * p.x_ld * 2 + (size_t)2 * WARPS * nt * 4 * 32 * 4 +
                        (pro == PRO_NORM ? (size_t)k * 4 : 0) + (2 * MAX_STAGES + 2) * 8 + 16;
-  for (int kc = kc_wish; kc >= 128; kc /= 2) {
-    const int use = kc < k ? kc : k;
+  // the stage size: the longest piece of a row (k / n values, a multiple of 32, at most kc_wish)
+  // of which two stages fit; longer pieces mean fewer copies per byte
+  for (int n = 1; n <= k / 32; ++n) {
+    if (k % (32 * n) || k / n > kc_wish) continue;
+    const int use = k / n;
+    if (use < 128 && n > 1) break;
     const size_t stage = (size_t)16 * (use * 2 + ROW_PAD);
     if (fixed + 2 * stage > (size_t)SMEM_BUDGET) continue;
     size_t stages = ((size_t)SMEM_BUDGET - fixed) / stage;
