@@ -354,3 +354,141 @@ def test_attention_mma_window_and_far_key():
     # one early key dominates every query: the output must be that key's value row
     got, want, _ = _attention_case([(1, 900), (33, 500)], 8, 2, 64, 64, 0, seed=2, far_key=True)
     _close(got, want, 2 ** -7, 4e-3)
+
+
+# ------------------------------------------------------------------------------ few-token fused product
+
+def _gemv_input(tokens, k, norm, ctx):
+    """x as the kernel takes it (a LazyNorm over a residual stream, or a bfloat16 matrix) and as float64."""
+    from bare_cuda_4gib_b200.kernels import lib as K
+    if norm:
+        residual = torch.randn(tokens + 3, k, device=DEV) * 1.5
+        weight = (1.0 + 0.1 * torch.randn(k, device=DEV)).to(torch.bfloat16)
+        rows = torch.tensor([(i * 2) % (tokens + 3) for i in range(tokens)], dtype=torch.int32, device=DEV)
+        eps = 1e-5
+        r = residual[rows.long()].double()
+        want = r / torch.sqrt((r * r).mean(-1, keepdim=True) + eps) * weight.double()
+        # the kernel rounds the normed input to bfloat16 once, as the unfused kernel does
+        return K.LazyNorm(ctx, residual, weight, eps, tokens, rows, "normed"), want.to(torch.bfloat16).double()
+    x = torch.randn(tokens, k, device=DEV).to(torch.bfloat16)
+    return x, x.double()
+
+
+@pytest.mark.parametrize("tokens,n,k", [(1, 70, 64), (8, 258, 96), (5, 2048, 352), (13, 100, 2048), (16, 33, 2816), (8, 40, 5632),
+                                        (3, 1000, 1408)])
+@pytest.mark.parametrize("norm", [False, True])
+def test_gemv_fused_plain_and_add(tokens, n, k, norm):
+    from bare_cuda_4gib_b200.kernels import gemm, gemv
+    from bare_cuda_4gib_b200.kernels import lib as K
+    torch.manual_seed(tokens * 31 + n)
+    ctx = _ctx()
+    ctx.dtype = torch.bfloat16
+    w = (torch.randn(n, k, device=DEV) * 0.1).to(torch.bfloat16)
+    assert gemv.supports(w) and gemv.takes(tokens, k)
+    assert not gemv.takes(16, 5632) and not gemv.takes(8, 40)     # x does not fit beside the ring; k no multiple of 32
+    x, xd = _gemv_input(tokens, k, norm, ctx)
+    want = xd @ w.double().t()
+    for out_dtype in (torch.float32, torch.bfloat16):
+        got = gemv.run(ctx, w, x, tokens, out_dtype, "out", False, None).tensor
+        _close(got, want, 1e-5 if out_dtype == torch.float32 else 2 ** -8, 2e-4 * math.sqrt(k))
+    target = torch.randn(tokens, n, device=DEV)
+    before = target.double().clone()
+    assert gemv.run(ctx, w, x, tokens, torch.float32, "out", False, K.AddTo(target)) is None
+    gemm.check_errors()
+    _close(target, before + want, 1e-5, 2e-4 * math.sqrt(k))
+
+
+@pytest.mark.parametrize("tokens,inter,k", [(2, 176, 64), (8, 100, 96), (16, 5632, 2048), (7, 13, 160)])
+@pytest.mark.parametrize("norm", [False, True])
+def test_gemv_fused_swiglu(tokens, inter, k, norm):
+    from bare_cuda_4gib_b200.kernels import gemm, gemv
+    torch.manual_seed(inter)
+    ctx = _ctx()
+    ctx.dtype = torch.bfloat16
+    w = (torch.randn(2 * inter, k, device=DEV) * 0.2).to(torch.bfloat16)
+    x, xd = _gemv_input(tokens, k, norm, ctx)
+    got = gemv.run(ctx, w, x, tokens, torch.bfloat16, "act", True, None).tensor
+    gemm.check_errors()
+    gu = xd @ w.double().t()
+    g, u = gu[:, :inter], gu[:, inter:]
+    _close(got, g / (1 + torch.exp(-g)) * u, 2 ** -7, 2e-3)
+
+
+@pytest.mark.parametrize("heads,kv_heads,d,page", [(6, 2, 48, 8), (32, 4, 64, 64), (3, 1, 128, 32), (4, 4, 16, 16)])
+@pytest.mark.parametrize("rotate", [True, False])
+def test_gemv_fused_rotation_and_cache_write(heads, kv_heads, d, page, rotate):
+    """[q; k; v] product, rotation by position and the write into scrambled pages in one kernel,
+    for tokens of two requests at different positions."""
+    from bare_cuda_4gib_b200.kernels import gemm, gemv
+    from bare_cuda_4gib_b200.kernels import lib as K
+    torch.manual_seed(d)
+    k_in, tokens = 96, 9
+    ctx = _ctx()
+    ctx.dtype = torch.bfloat16
+    storage, table, view = _paged_cache(kv_heads, d, page, 16, torch.bfloat16)
+    pages = list(range(16))
+    random.Random(5).shuffle(pages)
+    table[0, :8] = torch.tensor(pages[:8], dtype=torch.int32)
+    table[1, :8] = torch.tensor(pages[8:], dtype=torch.int32)
+    # request 0 brings 6 tokens from position 3 * page - 2 on (crossing a page edge), request 1 three from 0
+    p0 = 3 * page - 2
+    positions = torch.tensor(list(range(p0, p0 + 6)) + [0, 1, 2], dtype=torch.int32, device=DEV)
+    row_seq = torch.tensor([0] * 6 + [1] * 3, dtype=torch.int32, device=DEV)
+    width = (heads + 2 * kv_heads) * d
+    w = (torch.randn(width, k_in, device=DEV) * 0.2).to(torch.bfloat16)
+    x, xd = _gemv_input(tokens, k_in, True, ctx)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(d // 2, dtype=torch.float32) * 2.0 / d))).to(DEV) if rotate else None
+    q = torch.full((tokens, heads * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+    epilogue = K.RotateAndCache(q, view, positions, row_seq, inv_freq, heads, True)
+    assert gemv.run(ctx, w, x, tokens, torch.float32, "qkv", False, epilogue) is None
+    gemm.check_errors()
+    full = xd @ w.double().t()
+    qw = full[:, : heads * d].view(tokens, heads, d)
+    kw = full[:, heads * d: (heads + kv_heads) * d].view(tokens, kv_heads, d)
+    vw = full[:, (heads + kv_heads) * d:].view(tokens, kv_heads, d)
+    if rotate:
+        qw, kw = _rope_ref(qw, positions, inv_freq), _rope_ref(kw, positions, inv_freq)
+    _close(q.view(tokens, heads, d), qw, 2 ** -7, 2e-3)
+    sv = storage.view(16, 2, kv_heads, page, d)
+    for t in range(tokens):
+        pos, seq = int(positions[t]), int(row_seq[t])
+        pg = int(table[seq, pos // page])
+        _close(sv[pg, 0, :, pos % page], kw[t], 2 ** -7, 2e-3)
+        _close(sv[pg, 1, :, pos % page], vw[t], 2 ** -7, 2e-3)
+    # nothing else was written: every other cache position is still zero
+    written = torch.zeros(16, page, dtype=torch.bool, device=DEV)
+    for t in range(tokens):
+        pos, seq = int(positions[t]), int(row_seq[t])
+        written[int(table[seq, pos // page]), pos % page] = True
+    assert float(sv.float().abs().amax(dim=(1, 2, 4))[~written].max()) == 0.0
+
+
+# ------------------------------------------------------------------------------ cluster decode attention
+
+@pytest.mark.parametrize("heads,kv_heads,d,page", [(32, 4, 64, 64), (8, 8, 64, 16), (16, 2, 128, 32), (6, 3, 64, 8),
+                                                   (16, 1, 128, 64)])
+@pytest.mark.parametrize("splits", [0, 1, 3, 8])
+def test_attention_decode_cluster(heads, kv_heads, d, page, splits, monkeypatch):
+    """Single decode rows of requests of very different lengths (one key, a page's edge, thousands),
+    with the number of blocks per cluster forced to 1, 3 and 8 and left to the launcher (0)."""
+    if splits:
+        monkeypatch.setenv("BARE_CUDA_B200_ATTN_SPLITS", str(splits))
+    seqs = [(1, 2049), (1, 1), (1, page), (1, page + 1), (1, 700)]
+    got, want, ctx = _attention_case(seqs, heads, kv_heads, d, page, 0, seed=d + splits)
+    ran = [v for k, v in ctx.extras.items() if isinstance(k, tuple) and k[0] == "attention_tiles"]
+    assert ran and ran[0][5] >= 1, "the cluster decode kernel did not run"
+    _close(got, want, 2 ** -7, 4e-3)
+
+
+def test_attention_decode_two_tokens_window_and_far_key(monkeypatch):
+    # two tokens per request still fit the 16 packed rows of a tile when the group has at most 8 heads
+    got, want, ctx = _attention_case([(2, 300), (2, 2), (1, 77), (2, 1030)], 16, 2, 64, 16, 0, seed=11)
+    assert [v for k, v in ctx.extras.items() if isinstance(k, tuple)][0][5] >= 1
+    _close(got, want, 2 ** -7, 4e-3)
+    # a window: keys older than 50 positions do not count, whole key blocks below it are never read
+    got, want, _ = _attention_case([(1, 200), (2, 150), (1, 40)], 4, 2, 64, 16, 50, seed=12)
+    _close(got, want, 2 ** -7, 4e-3)
+    # one early key among a thousand dominates: the output must be that key's value row
+    monkeypatch.setenv("BARE_CUDA_B200_ATTN_SPLITS", "8")
+    got, want, _ = _attention_case([(1, 1900), (1, 500)], 8, 2, 64, 64, 0, seed=13, far_key=True)
+    _close(got, want, 2 ** -7, 4e-3)
