@@ -39,12 +39,38 @@ class ModelExecutor:
     def __init__(self, runner: StepRunner):
         self.runner = runner
         self.sampler = DeviceSampler(runner.device, runner.max_step_tokens)
+        # two buffers: a step's ids may still be unread when the next step's copy is queued
+        self._pinned = [torch.empty(runner.max_step_tokens, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._turn = 0
 
     def run(self, entries: Sequence[StepEntry], params: Sequence[SamplingParams], rngs: Sequence) -> List[int]:
-        logits = self.runner.step(entries)
+        return self.collect(self.launch(entries, params, rngs))
+
+    def launch(self, entries: Sequence[StepEntry], params: Sequence[SamplingParams], rngs: Sequence,
+               device_fed: bool = False):
+        """Starts a step and returns a handle for `collect`.  A step of greedy rows only is left
+        running: its argmax is copied to pinned memory behind it and an event marks the copy.
+        `device_fed`: the step's token ids are the argmax of the step before it (same requests in
+        the same order), taken on the device."""
+        logits = self.runner.step(entries, device_fed=device_fed)
         if logits is None:
-            return []
-        return self.sampler.sample(logits, params, rngs, self.runner.argmax)
+            return (None, 0, None, [])
+        rows = len(params)
+        if all(p.greedy() for p in params):
+            buffer = self._pinned[self._turn]
+            self._turn ^= 1
+            buffer[:rows].copy_(self.runner.argmax[:rows], non_blocking=True)
+            done = torch.cuda.Event()
+            done.record()
+            return (buffer, rows, done, None)
+        return (None, rows, None, self.sampler.sample(logits, params, rngs, self.runner.argmax))
+
+    def collect(self, handle) -> List[int]:
+        buffer, rows, done, tokens = handle
+        if tokens is not None:
+            return tokens
+        done.synchronize()
+        return buffer[:rows].tolist()
 
 
 class LLMEngine:

@@ -14,6 +14,16 @@ What differs: the reference prefills a whole prompt at admission, one request af
 before the decode pass of the same step; here prompts are cut into portions under the budget and
 share the batch with decode rows.
 
+Running ahead.  In steady decoding the host's share of a step (planning, metadata, reading the
+sampled ids back) would leave the GPU idle between steps.  With an executor that can launch a step
+and hand its tokens over later (`launch` / `collect`), a step of decode rows only, all greedy, is
+left in flight when `step()` returns; the next call first launches the following step for the same
+requests, whose token ids the device takes from the argmax of the step in flight, and only then
+collects that step's tokens and emits its events.  So events arrive one call late while this lasts,
+and a request that turns out to have ended (a stop id) has run one row too many, which is
+dropped.  Anything else - a request about to reach its length, someone waiting, a deadline,
+sampling on the host, pages that do not fit - ends the run and the scheduler goes on step by step.
+
 When pages run out.  Two policies:
 * "reserve" (the reference's, default): a request is admitted only if the pages of its whole run
   (prompt + target - 1 positions) fit beside what is already promised, so an admitted request
@@ -105,6 +115,16 @@ class _Live:
         self.original_prompt_len = len(request.prompt)
 
 
+class _InFlight:
+    """A launched step whose tokens have not been collected."""
+
+    __slots__ = ("handle", "wanted", "chain")
+
+    def __init__(self, handle, wanted, chain):
+        self.handle, self.wanted = handle, wanted
+        self.chain = chain      # a step of greedy decode rows only: the next one may be launched from its argmax
+
+
 class Scheduler:
     """Not thread-safe; one thread calls everything.  `executor.run(entries, params, rngs)` must
     return one sampled token per wanted row (see `engine.ModelExecutor`)."""
@@ -120,6 +140,8 @@ class Scheduler:
         self.committed = [0] * len(cache.groups)
         self.totals = SchedulerStats()
         self._admissions = 0
+        self._inflight: Optional[_InFlight] = None
+        self._can_run_ahead = hasattr(executor, "launch") and hasattr(executor, "collect")
 
     # ------------------------------------------------------------------ validity
     def target_tokens(self, prompt_len: int, max_new_tokens: int) -> int:
@@ -167,7 +189,7 @@ class Scheduler:
 
     @property
     def idle(self) -> bool:
-        return not self.waiting and not self.running
+        return not self.waiting and not self.running and self._inflight is None
 
     def stats(self) -> SchedulerStats:
         s = SchedulerStats(**self.totals.__dict__)
@@ -260,6 +282,12 @@ class Scheduler:
 
     def _run_step(self) -> List[TokenEvent]:
         events: List[TokenEvent] = []
+        if self._inflight is not None:
+            ahead = self._launch_ahead()
+            self._collect(events)
+            if ahead is not None:
+                self._inflight = ahead
+                return events
         self._expire(events)
         self._admit()
         if not self.running:
@@ -293,12 +321,25 @@ class Scheduler:
             else:
                 self.totals.prefill_tokens += n
                 self.totals.prefill_chunks += 1
-        tokens = self.executor.run(entries, params, rngs)
         self.totals.steps += 1
         for live, n in plan:
             live.fed += n
+        if not self._can_run_ahead:
+            self._emit(wanted, self.executor.run(entries, params, rngs), events)
+            return events
+        chain = (bool(wanted) and len(wanted) == len(plan) and all(n == 1 for _, n in plan)
+                 and all(p.greedy() for p in params))
+        self._inflight = _InFlight(self.executor.launch(entries, params, rngs), wanted, chain)
+        if not chain:
+            self._collect(events)
+        return events
+
+    def _emit(self, wanted, tokens, events: List[TokenEvent]) -> None:
+        """Books one sampled token per wanted row; rows of requests that ended meanwhile are dropped."""
         finished = []
         for live, token in zip(wanted, tokens):
+            if live.slot < 0:
+                continue
             token = int(token)
             event = TokenEvent(live.request.id, token, live.generated)
             live.generated += 1
@@ -313,4 +354,28 @@ class Scheduler:
         for live in finished:
             self._retire(live)
             self.running.remove(live)
-        return events
+
+    def _collect(self, events: List[TokenEvent]) -> None:
+        flight, self._inflight = self._inflight, None
+        self._emit(flight.wanted, self.executor.collect(flight.handle), events)
+
+    def _launch_ahead(self) -> Optional[_InFlight]:
+        """The step after the one in flight, for the same requests, with token ids taken on the
+        device from that step's argmax; None if anything could change the batch."""
+        flight = self._inflight
+        if not flight.chain or self.waiting or len(flight.wanted) != len(self.running):
+            return None
+        for live in flight.wanted:
+            # still running, no deadline, and the token in flight is not its last
+            if live.slot < 0 or live.deadline != float("inf") or live.generated + 1 >= live.target:
+                return None
+        if not self.cache.can_reserve([(live.slot, 1) for live in flight.wanted]):
+            return None
+        entries = [StepEntry(live.slot, [0], [0]) for live in flight.wanted]   # ids come from the device
+        params = [live.request.sampling for live in flight.wanted]
+        handle = self.executor.launch(entries, params, [live.rng for live in flight.wanted], device_fed=True)
+        for live in flight.wanted:
+            live.fed += 1
+        self.totals.steps += 1
+        self.totals.decode_tokens += len(entries)
+        return _InFlight(handle, flight.wanted, True)

@@ -200,10 +200,13 @@ class StepRunner:
             raise EngineError(f"step: {total} tokens in one batch, the engine takes {self.max_step_tokens}")
         return total, n_want
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], device_fed: bool = False) -> Optional[torch.Tensor]:
         """Runs the batch; returns float32 logits [wanted, vocab] on the device, in the order of
-        the entries and of each entry's `want` (None if nothing is wanted)."""
-        decode, n_want = self.begin(entries)
+        the entries and of each entry's `want` (None if nothing is wanted).  With `device_fed`
+        (one token per entry) the token ids are not the entries' but the argmax of the previous
+        step's wanted rows, row i for entry i, copied on the device: the caller need not have read
+        them yet."""
+        decode, n_want = self.begin(entries, device_fed=device_fed)
         logits = self._run(self.ctx, decode, entries)
         self.finish(entries)
         return None if logits is None else logits[:n_want]
@@ -213,7 +216,7 @@ class StepRunner:
         for e in entries:
             self.cache.commit(e.slot, len(e.tokens))
 
-    def begin(self, entries: Sequence[StepEntry]) -> Tuple[bool, int]:
+    def begin(self, entries: Sequence[StepEntry], device_fed: bool = False) -> Tuple[bool, int]:
         """Validates the batch, takes its pages, builds and sends the step's metadata and lets the
         parts plan; after this `self.ctx` describes the step.  Returns (pure decode step, wanted rows)."""
         total, n_want = self.validate(entries)
@@ -277,6 +280,10 @@ class StepRunner:
             w += 1
         used = self._rows_offset + 4 * rows
         self._dev[:used].copy_(self._host[:used], non_blocking=True)
+        if device_fed:
+            if any(len(e.tokens) != 1 for e in entries):
+                raise EngineError("step: device-fed token ids need one token per request")
+            tok_d[:n_seqs].copy_(self.argmax[:n_seqs], non_blocking=True)
         c.n_tokens, c.n_seqs, c.n_want, c.pad_seqs = rows, seqs, wanted, pad
         c.max_q_len, c.max_kv_len = max(c.host_q_len), max(c.host_kv_len)
         c.host_slots = slots

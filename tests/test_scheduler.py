@@ -164,3 +164,99 @@ def test_reserve_policy_never_runs_out():
     events = drain(s, 2000)
     assert s.stats().preemptions == 0
     assert sorted({e.id for e in events if e.finish == "length"}) == list(range(8))
+
+
+# ----------------------------------------------------------------------------- running ahead
+
+class AsyncFakeExecutor(FakeExecutor):
+    """The stand-in with `launch` / `collect`: what a step 'samples' is fixed at launch, handed
+    over at collection; a device-fed step must follow a collected-or-pending step of the same slots."""
+
+    def __init__(self, cache, stop_token_at=None):
+        super().__init__(cache)
+        self.pending, self.launched, self.fed_from_device = 0, 0, 0
+        self.stop_token_at = stop_token_at or {}     # slot length -> token to 'sample' instead
+
+    def launch(self, entries, params, rngs, device_fed=False):
+        if device_fed:
+            assert self.pending == 1, "a device-fed step needs the step before it still in flight"
+            assert all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+            assert [e.slot for e in entries] == self.last_slots
+            self.fed_from_device += 1
+        tokens = self.run(entries, params, rngs)
+        tokens = [self.stop_token_at.get(t - 1000, t) for t in tokens]
+        self.last_slots = [e.slot for e in entries]
+        self.pending += 1
+        self.launched += 1
+        assert self.pending <= 2
+        return tokens
+
+    def collect(self, handle):
+        self.pending -= 1
+        return handle
+
+
+def make_async(stop_token_at=None, **kw):
+    s, _, cache = make(**kw)
+    ex = AsyncFakeExecutor(cache, stop_token_at)
+    s.executor, s._can_run_ahead = ex, True
+    return s, ex, cache
+
+
+def test_running_ahead_gives_the_same_events_one_call_late():
+    def run(asynchronous):
+        s, ex, _ = (make_async if asynchronous else make)(pages=32, max_seqs=3, budget=16)
+        s.submit(Request(1, list(range(10)), 6))
+        s.submit(Request(2, list(range(3)), 9))
+        per_call = []
+        while not s.idle:
+            per_call.append([(e.id, e.token, e.index, e.finish) for e in s.step()])
+        return per_call, ex, s
+
+    sync_calls, _, _ = run(False)
+    async_calls, ex, s = run(True)
+    flat = lambda calls: [e for c in calls for e in c]
+    assert sorted(flat(sync_calls)) == sorted(flat(async_calls))           # the same tokens, indices and endings
+    for rid in (1, 2):                                                     # each request's events in order
+        assert [e for e in flat(sync_calls) if e[0] == rid] == [e for e in flat(async_calls) if e[0] == rid]
+    assert ex.fed_from_device >= 3                                         # it did run ahead
+    assert any(not c for c in async_calls[1:-1])                           # and events came a call late
+    assert ex.pending == 0 and s.stats().decode_tokens == 5 + 8
+
+
+def test_running_ahead_drops_the_row_of_a_request_that_stopped():
+    # request 1 'samples' its stop id when its slot holds 12 tokens; the step launched ahead of that
+    # news has one row too many for it, which must not become an event
+    s, ex, cache = make_async(stop_token_at={12: 77}, pages=32, max_seqs=3, budget=16)
+    s.submit(Request(1, list(range(10)), 20, stop_ids=[77]))
+    s.submit(Request(2, list(range(4)), 8))
+    events = drain(s)
+    one = [e for e in events if e.id == 1]
+    assert [e.token for e in one] == [1010, 1011, 77] and one[-1].finish == "stop"
+    two = [e for e in events if e.id == 2]
+    assert len(two) == 8 and two[-1].finish == "length"
+    assert cache.free_slots == 3 and cache.groups[0].pool.pages_in_use == 0
+    cache.check_consistency()
+
+
+def test_running_ahead_stops_for_waiting_requests_deadlines_and_sampling():
+    s, ex, _ = make_async(pages=32, max_seqs=1, budget=16)
+    s.submit(Request(1, list(range(4)), 5))
+    s.submit(Request(2, list(range(4)), 3))          # waits for the only slot: nothing runs ahead meanwhile
+    while not any(e.id == 1 and e.finish for e in s.step()):
+        assert ex.fed_from_device == 0
+    drain(s)
+    s, ex, _ = make_async(pages=32, max_seqs=2, budget=16)
+    s.submit(Request(1, list(range(4)), 6, timeout_ms=60000))
+    drain(s)
+    assert ex.fed_from_device == 0
+    s, ex, _ = make_async(pages=32, max_seqs=2, budget=16)
+    s.submit(Request(1, list(range(4)), 6, sampling=SamplingParams(temperature=0.7, seed=1)))
+    drain(s)
+    assert ex.fed_from_device == 0
+    s, ex, _ = make_async(pages=32, max_seqs=2, budget=16)
+    s.submit(Request(1, list(range(4)), 6))
+    s.step(); s.step(); s.step()
+    assert ex.fed_from_device >= 1
+    assert s.cancel(1) and not s.idle                # a step is still in flight
+    assert s.step() == [] and s.idle                 # its row is dropped
