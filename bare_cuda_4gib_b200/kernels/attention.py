@@ -26,7 +26,8 @@ _libs: Dict[int, object] = {}
 _tc_libs: Dict[int, object] = {}
 _decode_libs: Dict[int, object] = {}
 TC_HEAD_DIMS = (64, 128)      # head sizes the tcgen05 prefill kernel and the decode kernel are built for
-DECODE_MAX_TILES = 148        # (tiles x kv heads) up to which the cluster decode kernel runs
+DECODE_MAX_TILES = 65535 // 4 # (tiles x kv heads) up to which the cluster decode kernel runs
+N_SMS = 148
 
 
 def supports(head_dim: int) -> bool:
@@ -185,13 +186,19 @@ def step_tiles(ctx, plan: AttentionPlan):
             n_splits = 1
     dec_splits = dec_slots = 0
     if rows_per_tile == 16 and plan.decode is not None and n_tiles * plan.kv_heads <= DECODE_MAX_TILES:
-        # the cluster decode kernel: up to 8 blocks of 4 warps share a tile; a warp keeps `slots` key blocks in flight
+        # The cluster decode kernel: up to 8 blocks of 4 warps share a tile, a warp keeps one key
+        # block in flight.  As many blocks per tile as still lets every block be resident at once
+        # (a block holds 4 key blocks in shared memory), and no more than there are key blocks.
         key_blocks = -(-ctx.max_kv_len // KEY_BLOCK)
-        dec_splits = max(1, min(8, -(-TARGET_BLOCKS // (n_tiles * plan.kv_heads)), -(-key_blocks // 4)))
+        d = plan.head_dim       # shared memory of a block: alignment slack, 4 key blocks (K and V), Q, merge states, barriers
+        block_smem = 1024 + 4 * 2 * KEY_BLOCK * d * 2 + 16 * (d + 8) * 2 + 24 * (d + 4) * 4 + 128
+        resident = N_SMS * max(1, (227 * 1024) // block_smem)
+        dec_splits = max(1, min(8, resident // (n_tiles * plan.kv_heads), -(-key_blocks // 4)))
+        dec_slots = 1
         if os.environ.get("BARE_CUDA_B200_ATTN_SPLITS"):     # experiments only
             dec_splits = max(1, min(8, int(os.environ["BARE_CUDA_B200_ATTN_SPLITS"])))
-        per_warp = -(-key_blocks // (4 * dec_splits))
-        dec_slots = 1 if (per_warp <= 2 or plan.head_dim > 64) else 2
+        if os.environ.get("BARE_CUDA_B200_ATTN_SLOTS"):
+            dec_slots = int(os.environ["BARE_CUDA_B200_ATTN_SLOTS"])
     out = (dev[:n_tiles], dev[n_tiles: 2 * n_tiles], n_tiles, rows_per_tile, n_splits, dec_splits, dec_slots)
     ctx.extras[key] = out
     return out
