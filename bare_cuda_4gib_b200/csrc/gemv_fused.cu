@@ -7,8 +7,14 @@
 //   input   PRO_BF16   x is a bfloat16 matrix in global memory
 //           PRO_NORM   x = rms_norm(residual row) * weight, computed here from the float32
 //                      residual stream (cuongvng/bare-cuda-4gib engine/kernels/rmsnorm.cu:26-40)
+//           PRO_PRENORMED  the same norm, prepared by the product that last added into the
+//                      residual stream: x arrives as bfloat16(residual * weight) with the rows'
+//                      sums of squares in parts, and since the norm's factor rsqrt(mean + eps) is
+//                      one number per token it is applied to the float32 sums on the way out
 //   output  EPI_STORE  plain store (float32 or bfloat16)
-//           EPI_ADD    residual[t, n] += result                (residual_add.cu:20)
+//           EPI_ADD    residual[t, n] += result                (residual_add.cu:20); on request
+//                      it also leaves what PRO_PRENORMED of the next product needs: bfloat16(new
+//                      residual * next norm's weight) and this item's part of the sums of squares
 //           EPI_SWIGLU W = [gate; up]: out[t, i] = silu(gate_i) * up_i        (swiglu.cu:22-23)
 //           EPI_ROPE   W = [Wq; Wk; Wv]: rotates q and k by position, writes q to `out` and k, v
 //                      into the paged cache                    (rope.cu:25-47, model.cpp:548-556)
@@ -42,12 +48,12 @@ constexpr int THREADS = CONSUMERS + 32;        // plus the producer warp
 constexpr int MAX_STAGES = 12;
 constexpr int ROW_PAD = 64;                    // bytes between row pieces of a stage beyond their data:
                                                // keeps the 16-byte reads of a quarter warp on distinct banks
-constexpr int PREFETCH_CHUNK = 4096;
-constexpr int SMEM_BUDGET = 220 * 1024;        // dynamic shared memory of the one block per SM
+constexpr int SMEM_BUDGET = 220 * 1024;        // dynamic shared memory of one block per SM
 constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;
 constexpr int ERR_GEMV_PRODUCER = 21, ERR_GEMV_CONSUMER = 22;
 
-enum { PRO_BF16 = 0, PRO_NORM = 1 };
+enum { PRO_BF16 = 0, PRO_NORM = 1, PRO_PRENORMED = 2 };
+constexpr int SQ_SLOTS = 32;                  // token slots per item in the sums-of-squares parts
 enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_ROPE = 3 };
 
 // -DGEMV_TRACE: lane 0 of warp 0 of thread block 0 records SM clock stamps of the kernel's phases
@@ -73,7 +79,15 @@ struct GemvArgs {
   const void* norm_w;       // PRO_NORM: [k]
   int norm_w_dtype;
   float eps;
-  const int32_t* row_index; // PRO_NORM: token i reads residual row row_index[i] (null: i)
+  const int32_t* row_index; // PRO_NORM, PRO_PRENORMED: token i reads row row_index[i] (null: i)
+  const float* sq_in;       // PRO_PRENORMED: [sq_items][SQ_SLOTS] parts of the rows' sums of squares
+  int sq_items;
+  // EPI_ADD, optional: what the next product's PRO_PRENORMED needs
+  __nv_bfloat16* pre_x;     // [tokens, n_out] = bfloat16(new residual * pre_w)
+  long long pre_x_stride;
+  const void* pre_w;        // the next norm's weight [n_out]
+  int pre_w_dtype;
+  float* pre_sq;            // [n_items][SQ_SLOTS]
   // output
   void* out;                // EPI_STORE/EPI_SWIGLU: [tokens, n]; EPI_ADD: float32 residual; EPI_ROPE: q [tokens, q_heads * d]
   int out_dtype;
@@ -89,6 +103,7 @@ struct GemvArgs {
   // weights of a later product to pull into L2
   const uint8_t* prefetch;
   long long prefetch_bytes;
+  int prefetch_chunk;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -188,7 +203,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_fused_kernel(const GemvArgs a
   uint8_t* ring = smem;                                                              // [stages][16][row_stride]
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(ring + (size_t)a.stages * stage_bytes);   // [8 * NT][x_ld]
   float* red = reinterpret_cast<float*>(xs + (size_t)8 * NT * a.x_ld);               // [2][WARPS][NT * 4][32]
-  float* norm_ws = red + 2 * WARPS * NT * 4 * 32;                                    // PRO_NORM: [k]
+  float* scale_s = red + 2 * WARPS * NT * 4 * 32;                                    // PRO_PRENORMED: [SQ_SLOTS]
+  float* norm_ws = scale_s + SQ_SLOTS;                                               // PRO_NORM: [k]
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(norm_ws + (PRO == PRO_NORM ? a.k : 0));
   uint64_t* empty_bar = full_bar + MAX_STAGES;
   uint64_t* x_bar = empty_bar + MAX_STAGES;
@@ -250,6 +266,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_fused_kernel(const GemvArgs a
       }
       if (item == blockIdx.x && a.prefetch_bytes > 0) {
         // after the block's first loads are on their way: a later product's weights towards L2
+        const int PREFETCH_CHUNK = a.prefetch_chunk;
         const long long chunks = a.prefetch_bytes / PREFETCH_CHUNK;
         for (long long c = (long long)blockIdx.x * 32 + lane; c < chunks; c += (long long)gridDim.x * 32)
           prefetch_l2(a.prefetch + c * PREFETCH_CHUNK, PREFETCH_CHUNK);
@@ -337,12 +354,24 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_fused_kernel(const GemvArgs a
       if (lane == 0) mbar_expect_tx(x_bar, (uint32_t)a.tokens * a.k * 2u);
       __syncwarp();
       for (int r = lane; r < a.tokens; r += 32)
-        bulk_load(xs + (size_t)r * a.x_ld, x + (long long)r * a.x_stride, (uint32_t)a.k * 2u, x_bar);
+        bulk_load(xs + (size_t)r * a.x_ld, x + (long long)(a.row_index ? a.row_index[r] : r) * a.x_stride,
+                  (uint32_t)a.k * 2u, x_bar);
     }
     const int per_row = a.k / 8;
     for (int r = a.tokens; r < 8 * NT; ++r)
       for (int c = threadIdx.x; c < per_row; c += CONSUMERS)
         *reinterpret_cast<uint4*>(xs + (size_t)r * a.x_ld + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+    if (PRO == PRO_PRENORMED) {
+      // the norm's factor per token from the parts of its row's sum of squares: lanes take items
+      // lane, lane + 32, ..., then the warp adds up (the same order whatever the batch)
+      for (int tok = warp; tok < a.tokens; tok += WARPS) {
+        const int src = a.row_index ? a.row_index[tok] : tok;
+        float sq = 0.0f;
+        for (int i = lane; i < a.sq_items; i += 32) sq += a.sq_in[(size_t)i * SQ_SLOTS + src];
+        sq = warp_sum(sq);
+        if (lane == 0) scale_s[tok] = 1.0f / sqrtf(sq / (float)a.k + a.eps);
+      }
+    }
     mbar_wait(x_bar, 0, gave_up, a.error_word, ERR_GEMV_CONSUMER);
   }
   TRACE(3);
@@ -429,11 +458,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_fused_kernel(const GemvArgs a
         for (int w = 0; w < WARPS; ++w) s += red[((size_t)(buf * WARPS + w) * NT * 4 + n * 4 + i) * 32 + lane];
         v[i] = s;
       }
+      float sq_mine[2] = {0.0f, 0.0f};   // EPI_ADD with pre outputs: this thread's share of its two tokens' sums of squares
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const int tok = n * 8 + 2 * t + j;
         if (tok >= a.tokens) continue;
-        const float lo_v = v[j], hi_v = v[2 + j];
+        float lo_v = v[j], hi_v = v[2 + j];
+        if (PRO == PRO_PRENORMED) {
+          lo_v *= scale_s[tok];
+          hi_v *= scale_s[tok];
+        }
         if (EPI == EPI_STORE || EPI == EPI_ADD) {
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
@@ -441,7 +475,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_fused_kernel(const GemvArgs a
             if (row >= a.n_out) continue;
             const float val = half ? hi_v : lo_v;
             const long long at = (long long)tok * a.out_stride + row;
-            if (EPI == EPI_ADD) static_cast<float*>(a.out)[at] = (half ? old_hi[j] : old_lo[j]) + val;
+            if (EPI == EPI_ADD) {
+              const float now = (half ? old_hi[j] : old_lo[j]) + val;
+              static_cast<float*>(a.out)[at] = now;
+              if (a.pre_x) {
+                const float w = a.pre_w_dtype == DT_BF16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.pre_w)[row])
+                                                         : static_cast<const float*>(a.pre_w)[row];
+                a.pre_x[(long long)tok * a.pre_x_stride + row] = __float2bfloat16_rn(now * w);
+                sq_mine[j] += now * now;
+              }
+            }
             else if (a.out_dtype == DT_F32) static_cast<float*>(a.out)[at] = val;
             else static_cast<__nv_bfloat16*>(a.out)[at] = __float2bfloat16_rn(val);
           }
@@ -472,6 +515,18 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_fused_kernel(const GemvArgs a
             dst[0] = __float2bfloat16_rn(first);
             dst[half] = __float2bfloat16_rn(second);
           }
+        }
+      }
+      if (EPI == EPI_ADD && a.pre_x) {
+        // the item's 16 rows are spread over the 8 lanes that share t: add them up, lane g = 0 writes
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          float part = sq_mine[j];
+          part += __shfl_xor_sync(0xffffffffu, part, 4);
+          part += __shfl_xor_sync(0xffffffffu, part, 8);
+          part += __shfl_xor_sync(0xffffffffu, part, 16);
+          const int tok = n * 8 + 2 * t + j;
+          if (g == 0 && tok < a.tokens) a.pre_sq[(size_t)item * SQ_SLOTS + tok] = part;
         }
       }
     }
@@ -508,6 +563,7 @@ template <int NT>
 int launch_pro(int pro, int epi, const GemvArgs& a, size_t smem, int grid, cudaStream_t stream) {
   if (pro == PRO_BF16) return launch_epi<NT, PRO_BF16>(epi, a, smem, grid, stream);
   if (pro == PRO_NORM) return launch_epi<NT, PRO_NORM>(epi, a, smem, grid, stream);
+  if (pro == PRO_PRENORMED) return launch_epi<NT, PRO_PRENORMED>(epi, a, smem, grid, stream);
   return ERR_BAD_SIZE;
 }
 
@@ -518,7 +574,7 @@ struct SmemPlan {
   size_t bytes;
 };
 
-static bool plan_smem(int tokens, int k, int pro, SmemPlan& p) {
+static bool plan_smem(int tokens, int k, int pro, size_t budget, int min_stages, SmemPlan& p) {
   if (tokens < 1 || tokens > 32 || k < 32 || k % 32) return false;
   const int nt = (tokens + 7) / 8;
   p.x_ld = k + ((k * 2) % 128 == 64 ? 0 : 32);
@@ -528,7 +584,7 @@ static bool plan_smem(int tokens, int k, int pro, SmemPlan& p) {
     kc_wish = v ? atoi(v) : 2048;
     if (kc_wish < 32 || kc_wish % 32) kc_wish = 2048;
   }
-  const size_t fixed = (size_t)8 * nt * p.x_ld * 2 + (size_t)2 * WARPS * nt * 4 * 32 * 4 +
+  const size_t fixed = (size_t)8 * nt * p.x_ld * 2 + (size_t)2 * WARPS * nt * 4 * 32 * 4 + SQ_SLOTS * 4 +
                        (pro == PRO_NORM ? (size_t)k * 4 : 0) + (2 * MAX_STAGES + 2) * 8 + 16;
   // the stage size: the longest piece of a row (k / n values, a multiple of 32, at most kc_wish)
   // of which two stages fit; longer pieces mean fewer copies per byte
@@ -537,8 +593,8 @@ static bool plan_smem(int tokens, int k, int pro, SmemPlan& p) {
     const int use = k / n;
     if (use < 128 && n > 1) break;
     const size_t stage = (size_t)16 * (use * 2 + ROW_PAD);
-    if (fixed + 2 * stage > (size_t)SMEM_BUDGET) continue;
-    size_t stages = ((size_t)SMEM_BUDGET - fixed) / stage;
+    if (fixed + min_stages * stage > budget) continue;
+    size_t stages = (budget - fixed) / stage;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     p.kc = use, p.stages = (int)stages, p.bytes = fixed + stages * stage;
     p.norm_rows = 0, p.first_aliased = (int)stages;
@@ -570,7 +626,7 @@ extern "C" int llm_gemv_set_trace(long long* p) {
 // Shared memory the kernel needs for `tokens` tokens and inner dimension k (0: not supported).
 extern "C" long long llm_gemv_fused_smem(int tokens, int k) {
   SmemPlan p;
-  return plan_smem(tokens, k, PRO_NORM, p) ? (long long)p.bytes : 0;
+  return plan_smem(tokens, k, PRO_NORM, SMEM_BUDGET, 2, p) ? (long long)p.bytes : 0;
 }
 
 extern "C" int llm_gemv_fused(const void* w, int w_rows, int k, int tokens, int pro, int epi,
@@ -579,15 +635,18 @@ extern "C" int llm_gemv_fused(const void* w, int w_rows, int k, int tokens, int 
                               int up_offset, void* k_base, void* v_base, const int32_t* block_table,
                               long long page_stride, int table_stride, int page_tokens, int kv_heads, int head_dim,
                               const int32_t* positions, const int32_t* row_seq, const float* inv_freq, int q_heads,
-                              int write_cache, const void* prefetch, long long prefetch_bytes, int max_blocks,
-                              int* error_word, cudaStream_t stream) {
+                              int write_cache, const float* sq_in, int sq_items, void* pre_x, long long pre_x_stride,
+                              const void* pre_w, int pre_w_dtype, float* pre_sq, const void* prefetch,
+                              long long prefetch_bytes, int max_blocks, int* error_word, cudaStream_t stream) {
   SmemPlan plan;
-  if (!plan_smem(tokens, k, pro, plan)) return ERR_BAD_SIZE;
+  if (!plan_smem(tokens, k, pro, SMEM_BUDGET, 2, plan)) return ERR_BAD_SIZE;
   const size_t smem = plan.bytes;
   if (out_dtype != DT_F32 && out_dtype != DT_BF16) return ERR_BAD_DTYPE;
   if (epi == EPI_ADD && out_dtype != DT_F32) return ERR_BAD_DTYPE;
+  if (tokens > SQ_SLOTS || (pro == PRO_PRENORMED && (!sq_in || sq_items < 1)) || (pre_x && (epi != EPI_ADD || !pre_w || !pre_sq)))
+    return ERR_BAD_SIZE;
   const auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
-  if (!aligned16(w) || !aligned16(x) || (pro == PRO_BF16 && x_stride % 8) || (pro == PRO_NORM && x_stride % 4) ||
+  if (!aligned16(w) || !aligned16(x) || (pro != PRO_NORM && x_stride % 8) || (pro == PRO_NORM && x_stride % 4) ||
       (pro == PRO_NORM && !aligned16(norm_w)) || (prefetch_bytes > 0 && !aligned16(prefetch)))
     return ERR_BAD_ALIGN;
   GemvArgs a = {};
@@ -599,6 +658,10 @@ extern "C" int llm_gemv_fused(const void* w, int w_rows, int k, int tokens, int 
   a.cache = PagedCache{k_base, v_base, block_table, page_stride, table_stride, page_tokens, kv_heads, head_dim};
   a.positions = positions, a.row_seq = row_seq, a.inv_freq = inv_freq, a.q_heads = q_heads, a.write_cache = write_cache;
   a.prefetch = static_cast<const uint8_t*>(prefetch), a.prefetch_bytes = prefetch_bytes;
+  a.prefetch_chunk = 4096;
+  a.sq_in = sq_in, a.sq_items = sq_items;
+  a.pre_x = static_cast<__nv_bfloat16*>(pre_x), a.pre_x_stride = pre_x_stride, a.pre_w = pre_w, a.pre_w_dtype = pre_w_dtype;
+  a.pre_sq = pre_sq;
   if (epi == EPI_SWIGLU) {
     if (n_out < 1 || up_offset < n_out || up_offset + n_out > w_rows) return ERR_BAD_SIZE;
     a.n_items = (n_out + 7) / 8;

@@ -117,7 +117,14 @@ class Model:
         x = self.embed.forward(ctx)
         pending = None
         for i, call in enumerate(self.order):
+            # the norm that reads the residual stream after this layer: the next layer's first, or the final one
+            if i + 1 < len(self.order):
+                entry = getattr(self.blocks[self.order[i + 1].layer], "entry_norm", None)
+                ctx.norm_after_layer = entry() if entry else None
+            else:
+                ctx.norm_after_layer = self.final_norm if ctx.n_want > 0 else None
             pending = self.blocks[call.layer].forward(ctx, ctx.calls[i], x, pending)
+        ctx.norm_after_layer = None
         if ctx.n_want == 0:
             return None
         normed = self.final_norm.forward(ctx, x, pending, ctx.n_want, ctx.want_rows, buffer="final_normed",

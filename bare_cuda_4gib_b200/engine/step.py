@@ -88,6 +88,9 @@ class StepContext:
         self.max_kv_len = 0
         self.extras: Dict[object, object] = {}
         self.residual = None       # the float32 residual stream while a layer runs
+        self.following_norm = None # the norm part that reads the stream after the part that runs now
+        self.norm_after_layer = None
+        self.prenormed = None      # what the last adding product left for that norm (kernels.lib.Prenormed)
         self.gemv_prev: list = []  # the few-token products of the previous step, in call order
         self.gemv_now: list = []
 

@@ -16,13 +16,15 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from . import build
-from .lib import DT_BF16, DT_F32, AddTo, LazyNorm, Partials, RotateAndCache, _check, _ptr
+from .lib import DT_BF16, DT_F32, AddTo, LazyNorm, Partials, Prenormed, RotateAndCache, _check, _ptr
 
-PRO_BF16, PRO_NORM = 0, 1
+PRO_BF16, PRO_NORM, PRO_PRENORMED = 0, 1, 2
+SQ_SLOTS = 32
 EPI_STORE, EPI_ADD, EPI_SWIGLU, EPI_ROPE = 0, 1, 2, 3
 MAX_TOKENS = int(os.environ.get("BARE_CUDA_B200_GEMV_MAX_TOKENS", "16"))
 PREFETCH = os.environ.get("BARE_CUDA_B200_GEMV_PREFETCH", "0") not in ("0", "")
 PREFETCH_MAX_BYTES = 64 << 20      # never more than about half of L2
+PRENORM = os.environ.get("BARE_CUDA_B200_GEMV_PRENORM", "1") not in ("0", "")
 N_SMS = 148
 _lib = None
 _smem: Dict[Tuple[int, int], int] = {}
@@ -36,7 +38,7 @@ def lib():
         l.llm_gemv_fused_smem.argtypes = [I, I]
         l.llm_gemv_fused_smem.restype = L
         l.llm_gemv_fused.argtypes = [P, I, I, I, I, I, P, L, P, I, F, P, P, I, L, I, I, P, P, P, L, I, I, I, I,
-                                     P, P, P, I, I, P, L, I, P, P]
+                                     P, P, P, I, I, P, I, P, L, P, I, P, P, L, I, P, P]
         l.llm_gemv_fused.restype = c_int
         _lib = l
     return _lib
@@ -81,7 +83,12 @@ def run(ctx, weight: torch.Tensor, x, rows: int, out_dtype: torch.dtype, buffer:
     matrix or a `LazyNorm`; `epilogue` None, `AddTo` or `RotateAndCache`.  Returns the result, or
     None when the epilogue consumed it."""
     n, k = weight.shape
-    if isinstance(x, LazyNorm):
+    sq_in, sq_items = None, 0
+    if isinstance(x, LazyNorm) and x.prenormed is not None:
+        pre = x.prenormed
+        pro, xt, x_stride, sq_in, sq_items = PRO_PRENORMED, pre.x, pre.x.stride(0), pre.sq, pre.items
+        norm_w, eps, row_index, norm_code = None, x.eps, x.row_index, DT_F32
+    elif isinstance(x, LazyNorm):
         pro, xt, x_stride = PRO_NORM, x.residual, x.residual.stride(0)
         norm_w, eps, row_index = x.weight, x.eps, x.row_index
         norm_code = DT_BF16 if norm_w.dtype == torch.bfloat16 else DT_F32
@@ -90,11 +97,16 @@ def run(ctx, weight: torch.Tensor, x, rows: int, out_dtype: torch.dtype, buffer:
     cache = None
     up_offset = q_heads = write_cache = 0
     positions = row_seq = inv_freq = None
+    pre_x = pre_w = pre_sq = None
     if swiglu:
         epi, n_out, up_offset = EPI_SWIGLU, n // 2, n // 2
         out = ctx.ws.get(buffer, (rows, n_out), out_dtype)
     elif isinstance(epilogue, AddTo):
         epi, n_out, out = EPI_ADD, n, epilogue.residual
+        if epilogue.then_norm is not None and PRENORM:
+            pre_w = epilogue.then_norm.tensors["weight"]
+            pre_x = ctx.ws.get("prenormed.x", (rows, n), torch.bfloat16, max_rows=MAX_TOKENS)
+            pre_sq = ctx.ws.get("prenormed.sq", (-(-n // 16), SQ_SLOTS), torch.float32, max_rows=-(-n // 16))
     elif (isinstance(epilogue, RotateAndCache) and epilogue.cache.head_dim % 16 == 0
           and epilogue.cache.dtype == torch.bfloat16 and epilogue.q_out.dtype == torch.bfloat16):
         epi, n_out, out, cache = EPI_ROPE, n, epilogue.q_out, epilogue.cache
@@ -112,5 +124,8 @@ def run(ctx, weight: torch.Tensor, x, rows: int, out_dtype: torch.dtype, buffer:
         cache.block_table.data_ptr() if cache else 0, cache.page_stride if cache else 0,
         cache.table_stride if cache else 0, cache.page_tokens if cache else 1, cache.kv_heads if cache else 0,
         cache.head_dim if cache else 0, _ptr(positions), _ptr(row_seq), _ptr(inv_freq), q_heads, write_cache,
+        _ptr(sq_in), sq_items, _ptr(pre_x), pre_x.stride(0) if pre_x is not None else 0, _ptr(pre_w),
+        (DT_BF16 if pre_w.dtype == torch.bfloat16 else DT_F32) if pre_w is not None else DT_F32, _ptr(pre_sq),
         pf_ptr, pf_bytes, N_SMS, gemm.error_word(weight.device).data_ptr(), ctx.stream), "gemv_fused")
+    ctx.prenormed = Prenormed(epilogue.then_norm, pre_x, pre_sq, -(-n // 16)) if pre_x is not None else None
     return None if epi in (EPI_ADD, EPI_ROPE) else Partials(out)

@@ -129,12 +129,27 @@ class Partials:
 
 
 class AddTo:
-    """Asks a product to add its result into the float32 residual stream itself."""
+    """Asks a product to add its result into the float32 residual stream itself.  `then_norm`
+    (optional) is the norm part that will read the stream next, if it is one whose factor is a
+    single number per row (`prenormable`, with `tensors["weight"]` and `params["eps"]`): a kernel
+    that can then also leaves bfloat16(new residual * weight) and the rows' sums of squares, from
+    which the next product norms its input without reading the stream again (`Prenormed`)."""
 
-    __slots__ = ("residual",)
+    __slots__ = ("residual", "then_norm")
 
-    def __init__(self, residual: torch.Tensor):
+    def __init__(self, residual: torch.Tensor, then_norm=None):
         self.residual = residual
+        self.then_norm = then_norm if getattr(then_norm, "prenormable", False) else None
+
+
+class Prenormed:
+    """What an adding product left for the norm `norm`: `x` [rows, width] bfloat16 = residual *
+    weight, `sq` [items, 32] float32 parts of every row's sum of squares."""
+
+    __slots__ = ("norm", "x", "sq", "items")
+
+    def __init__(self, norm, x, sq, items):
+        self.norm, self.x, self.sq, self.items = norm, x, sq, items
 
 
 class RotateAndCache:
@@ -152,11 +167,12 @@ class LazyNorm:
     """rms_norm(residual rows) * weight that has not been computed: a product that can norm its
     own input takes it as it is, everything else calls `materialize()`."""
 
-    __slots__ = ("ctx", "residual", "weight", "eps", "rows", "row_index", "buffer")
+    __slots__ = ("ctx", "residual", "weight", "eps", "rows", "row_index", "buffer", "prenormed")
 
-    def __init__(self, ctx, residual, weight, eps, rows, row_index, buffer):
+    def __init__(self, ctx, residual, weight, eps, rows, row_index, buffer, prenormed=None):
         self.ctx, self.residual, self.weight, self.eps = ctx, residual, weight, eps
         self.rows, self.row_index, self.buffer = rows, row_index, buffer
+        self.prenormed = prenormed      # a `Prenormed` for this norm, if the last adding product left one
 
     def materialize(self) -> torch.Tensor:
         out = self.ctx.ws.get(self.buffer, (self.rows, self.residual.shape[-1]), self.ctx.dtype)

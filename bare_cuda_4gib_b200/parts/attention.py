@@ -95,4 +95,4 @@ class Attention(Part):
                               self.scale, window, ctx.stream)
         residual = getattr(ctx, "residual", None)
         return self.o.forward(ctx, out, n, torch.float32, "attn_proj", allow_partials=True,
-                              epilogue=K.AddTo(residual) if residual is not None else None)
+                              epilogue=K.AddTo(residual, getattr(ctx, "following_norm", None)) if residual is not None else None)

@@ -27,7 +27,16 @@ class PreNormBlock:
     def forward(self, ctx, call, residual, pending):
         n = ctx.n_tokens
         ctx.residual = residual      # a part may add its contribution here itself and return None
+        after = getattr(ctx, "norm_after_layer", None)
         h = self.mixer_norm.forward(ctx, residual, pending, n, lazy=getattr(self.mixer, "takes_lazy_input", False))
+        ctx.following_norm = self.ffn_norm     # the norm that reads the stream after the part that runs now
         mixed = self.mixer.forward(ctx, call, h)
         h = self.ffn_norm.forward(ctx, residual, mixed, n, lazy=getattr(self.ffn, "takes_lazy_input", False))
-        return self.ffn.forward(ctx, h)
+        ctx.following_norm = after
+        out = self.ffn.forward(ctx, h)
+        ctx.following_norm = None
+        return out
+
+    def entry_norm(self):
+        """The norm that reads the residual stream first when this layer runs."""
+        return self.mixer_norm

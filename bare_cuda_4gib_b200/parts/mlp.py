@@ -38,4 +38,4 @@ class SwiGLUFeedForward(Part):
         act = self.gate_up.forward(ctx, h, n, ctx.dtype, "ffn_act", swiglu=True)
         residual = getattr(ctx, "residual", None)
         return self.down.forward(ctx, act.tensor, n, torch.float32, "ffn_out", allow_partials=True,
-                                 epilogue=K.AddTo(residual) if residual is not None else None)
+                                 epilogue=K.AddTo(residual, getattr(ctx, "following_norm", None)) if residual is not None else None)

@@ -21,6 +21,8 @@ from .registry import register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Part):
+    prenormable = True      # the norm's factor is one number per row (see kernels.lib.AddTo)
+
     def local_weights(self):
         return {"weight": ((self.params["size"],), "norm")}
 
@@ -28,11 +30,13 @@ class RMSNorm(Part):
                 row_index: Optional[torch.Tensor] = None, buffer: str = "normed", lazy: bool = False):
         """With `lazy` (the consumer takes a `LazyNorm`) and nothing to add, a few-token bfloat16
         step gets the norm as a description that the consuming product computes in its own kernel."""
+        left = getattr(ctx, "prenormed", None)       # what the last adding product may have left for this norm
+        ctx.prenormed = None
         if lazy and delta is None and ctx.dtype == torch.bfloat16 and ctx.use_fast_gemm:
             from ..kernels import gemv
             if gemv.takes(rows, int(self.params["size"])) and self.tensors["weight"].is_cuda:
                 return K.LazyNorm(ctx, residual, self.tensors["weight"], float(self.params["eps"]), rows,
-                                  row_index, buffer)
+                                  row_index, buffer, left if left is not None and left.norm is self else None)
         out = ctx.ws.get(buffer, (rows, self.params["size"]), ctx.dtype)
         K.add_rmsnorm(residual, delta, self.tensors["weight"], out, float(self.params["eps"]), rows,
                       row_index, ctx.stream)

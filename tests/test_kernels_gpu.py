@@ -492,3 +492,45 @@ def test_attention_decode_two_tokens_window_and_far_key(monkeypatch):
     monkeypatch.setenv("BARE_CUDA_B200_ATTN_SPLITS", "8")
     got, want, _ = _attention_case([(1, 1900), (1, 500)], 8, 2, 64, 64, 0, seed=13, far_key=True)
     _close(got, want, 2 ** -7, 4e-3)
+
+
+@pytest.mark.parametrize("tokens,hidden,inter", [(8, 96, 64), (3, 352, 1408), (16, 2048, 160)])
+def test_gemv_fused_add_then_prenormed_input(tokens, hidden, inter):
+    """A product that adds into the residual stream and, asked to, leaves bfloat16(residual * w) and
+    the rows' sums of squares; the next product norms its input from those.  Both against float64."""
+    import types as _types
+    from bare_cuda_4gib_b200.kernels import gemm, gemv
+    from bare_cuda_4gib_b200.kernels import lib as K
+    torch.manual_seed(hidden + tokens)
+    ctx = _ctx()
+    ctx.dtype = torch.bfloat16
+    eps = 1e-6
+    norm = _types.SimpleNamespace(prenormable=True, params={"eps": eps, "size": hidden},
+                                  tensors={"weight": (1.0 + 0.2 * torch.randn(hidden, device=DEV)).to(torch.bfloat16)})
+    residual = torch.randn(tokens + 2, hidden, device=DEV) * 2.0
+    before = residual.double().clone()
+    w_down = (torch.randn(hidden, inter, device=DEV) * 0.3).to(torch.bfloat16)
+    act = torch.randn(tokens, inter, device=DEV).to(torch.bfloat16)
+    assert gemv.run(ctx, w_down, act, tokens, torch.float32, "out", False, K.AddTo(residual, norm)) is None
+    left = ctx.prenormed
+    assert left is not None and left.norm is norm
+    now = before.clone()
+    now[:tokens] += act.double() @ w_down.double().t()
+    _close(residual, now, 1e-5, 1e-4 * math.sqrt(inter))
+    # the next product: wanted rows in another order, its input normed from what was left
+    rows = torch.tensor(list(reversed(range(tokens))), dtype=torch.int32, device=DEV)
+    w_next = (torch.randn(70, hidden, device=DEV) * 0.1).to(torch.bfloat16)
+    lazy = K.LazyNorm(ctx, residual, norm.tensors["weight"], eps, tokens, rows, "normed", left)
+    got = gemv.run(ctx, w_next, lazy, tokens, torch.float32, "out2", False, None).tensor
+    gemm.check_errors()
+    r = now[rows.long()]
+    x = r / torch.sqrt((r * r).mean(-1, keepdim=True) + eps) * norm.tensors["weight"].double()
+    # The input is rounded to bfloat16 once (before the norm's factor here, after it in the unfused
+    # kernel: the same relative error 2^-9 / sqrt(3) per element of size ~1), so an output, a sum of
+    # `hidden` products with weights of size 0.1, is off by sigma = 2^-9 / sqrt(3) * sqrt(hidden) * 0.1;
+    # the bound is 8 sigma.
+    sigma = 2.0 ** -9 / math.sqrt(3.0) * math.sqrt(hidden) * 0.1
+    _close(got, x @ w_next.double().t(), 0.0, 8 * sigma)
+    # without the request nothing is left
+    gemv.run(ctx, w_down, act, tokens, torch.float32, "out", False, K.AddTo(residual))
+    assert ctx.prenormed is None
