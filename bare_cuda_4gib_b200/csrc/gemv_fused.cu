@@ -31,8 +31,7 @@
 // One block per SM.  A producer warp streams the block's items through a ring of shared-memory
 // stages (16 row pieces of up to `kc` values each, one bulk copy per piece, landing on an
 // mbarrier); it starts before the kernel has waited for its predecessor in the stream, since
-// weights are never written, and it may ask for a later product's weights to be brought into
-// L2.  Eight consumer warps split each stage's k range, multiply out of shared memory, and at
+// weights are never written.  Eight consumer warps split each stage's k range, multiply out of shared memory, and at
 // the end of an item add their partial sums in warp order, so a result depends neither on the
 // batch nor on the grid.  x for all tokens sits in shared memory for the whole kernel.  Every
 // wait on an mbarrier is bounded: after about a second without progress the thread records an
@@ -103,7 +102,6 @@ struct GemvArgs {
   // weights of a later product to pull into L2
   const uint8_t* prefetch;
   long long prefetch_bytes;
-  int prefetch_chunk;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -172,10 +170,6 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ void prefetch_l2(const uint8_t* p, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
 
 // The two rows of W that thread group g reads for `item` (clamped into W; `valid` tells whether
@@ -264,15 +258,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_fused_kernel(const GemvArgs a
           phase ^= 1u;
         }
       }
-      if (item == blockIdx.x && a.prefetch_bytes > 0) {
-        // after the block's first loads are on their way: a later product's weights towards L2
-        const int PREFETCH_CHUNK = a.prefetch_chunk;
-        const long long chunks = a.prefetch_bytes / PREFETCH_CHUNK;
-        for (long long c = (long long)blockIdx.x * 32 + lane; c < chunks; c += (long long)gridDim.x * 32)
-          prefetch_l2(a.prefetch + c * PREFETCH_CHUNK, PREFETCH_CHUNK);
-        const uint32_t tail = (uint32_t)(a.prefetch_bytes - chunks * PREFETCH_CHUNK) & ~15u;
-        if (blockIdx.x == 0 && lane == 0 && tail) prefetch_l2(a.prefetch + chunks * PREFETCH_CHUNK, tail);
-      }
     }
   producer_done:
     // If the block gave up, copies may still be on their way into its shared memory: wait for
@@ -287,6 +272,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_fused_kernel(const GemvArgs a
   }
 
   // ---- consumers
+  if (a.prefetch_bytes > 0) {
+    // A later product's weights towards L2, one 128-byte line per instruction, through the load
+    // path (the TMA unit is busy with this product's own copies).  Nothing waits for these.
+    const long long lines = a.prefetch_bytes / 128;
+    for (long long i = (long long)blockIdx.x * CONSUMERS + threadIdx.x; i < lines; i += (long long)gridDim.x * CONSUMERS)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(a.prefetch + i * 128));
+  }
   if (PRO == PRO_NORM) {     // the norm's weight is no kernel's output: fetch it before waiting
     for (int i = threadIdx.x; i < a.k; i += CONSUMERS)
       norm_ws[i] = a.norm_w_dtype == DT_BF16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.norm_w)[i])
@@ -658,7 +650,6 @@ extern "C" int llm_gemv_fused(const void* w, int w_rows, int k, int tokens, int 
   a.cache = PagedCache{k_base, v_base, block_table, page_stride, table_stride, page_tokens, kv_heads, head_dim};
   a.positions = positions, a.row_seq = row_seq, a.inv_freq = inv_freq, a.q_heads = q_heads, a.write_cache = write_cache;
   a.prefetch = static_cast<const uint8_t*>(prefetch), a.prefetch_bytes = prefetch_bytes;
-  a.prefetch_chunk = 4096;
   a.sq_in = sq_in, a.sq_items = sq_items;
   a.pre_x = static_cast<__nv_bfloat16*>(pre_x), a.pre_x_stride = pre_x_stride, a.pre_w = pre_w, a.pre_w_dtype = pre_w_dtype;
   a.pre_sq = pre_sq;
