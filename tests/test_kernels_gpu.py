@@ -263,8 +263,10 @@ def test_gemm_tcgen05_swiglu(m, inter, k):
 
 # ------------------------------------------------------------------------------ tensor-core attention
 
-def _attention_case(seqs, heads, kv_heads, d, page, window, seed, far_key=False):
-    """seqs: [(q_len, kv_len)].  Fills a scrambled paged cache, runs attention_mma and the dense reference."""
+def _attention_case(seqs, heads, kv_heads, d, page, window, seed, far_key=False, drop_passed=False):
+    """seqs: [(q_len, kv_len)].  Fills a scrambled paged cache, runs the attention the launcher picks
+    and the dense reference.  `drop_passed` (with a window): pages that every query of the step has
+    passed are taken out of the block table and filled with NaN, as the cache manager gives them back."""
     from bare_cuda_4gib_b200.kernels import attention as fast
     from bare_cuda_4gib_b200.kernels.lib import CacheView
 
@@ -295,6 +297,11 @@ def _attention_case(seqs, heads, kv_heads, d, page, window, seed, far_key=False)
             lo, hi = b * page, min(kv_len, (b + 1) * page)
             sv[pg, 0, :, : hi - lo] = k[lo:hi].transpose(0, 1)
             sv[pg, 1, :, : hi - lo] = v[lo:hi].transpose(0, 1)
+        if drop_passed and window > 0:
+            passed = max(0, kv_len - q_len - window + 1) // page      # blocks wholly below the first query's window
+            for b in range(passed):
+                sv[pages[b]] = float("nan")
+            table[s, :passed] = -1
         ks.append(k)
         vs.append(v)
     esize = 2
@@ -351,6 +358,11 @@ def test_attention_mma_decode_split(heads, kv_heads, d, page):
 def test_attention_mma_window_and_far_key():
     got, want, _ = _attention_case([(40, 200), (1, 150), (90, 90)], 4, 2, 64, 16, 50, seed=1)
     _close(got, want, 2 ** -7, 4e-3)
+    # prompt portions behind a window whose passed pages are gone (the tcgen05 kernel at head size 64,
+    # the mma.sync kernel at 32)
+    for d in (64, 32):
+        got, want, _ = _attention_case([(40, 300), (3, 150), (70, 500)], 4, 2, d, 16, 60, seed=3, drop_passed=True)
+        _close(got, want, 2 ** -7, 4e-3)
     # one early key dominates every query: the output must be that key's value row
     got, want, _ = _attention_case([(1, 900), (33, 500)], 8, 2, 64, 64, 0, seed=2, far_key=True)
     _close(got, want, 2 ** -7, 4e-3)
@@ -488,6 +500,13 @@ def test_attention_decode_two_tokens_window_and_far_key(monkeypatch):
     # a window: keys older than 50 positions do not count, whole key blocks below it are never read
     got, want, _ = _attention_case([(1, 200), (2, 150), (1, 40)], 4, 2, 64, 16, 50, seed=12)
     _close(got, want, 2 ** -7, 4e-3)
+    # ... and the pages the window has passed are gone from the block table (a key block of 64 then
+    # straddles pages that are held and pages that are not)
+    for page in (16, 32, 64):
+        got, want, ctx = _attention_case([(1, 300), (2, 131), (1, 40), (1, 1000)], 8, 2, 64, page, 70, seed=14,
+                                         drop_passed=True)
+        assert [v for k, v in ctx.extras.items() if isinstance(k, tuple)][0][5] >= 1
+        _close(got, want, 2 ** -7, 4e-3)
     # one early key among a thousand dominates: the output must be that key's value row
     monkeypatch.setenv("BARE_CUDA_B200_ATTN_SPLITS", "8")
     got, want, _ = _attention_case([(1, 1900), (1, 500)], 8, 2, 64, 64, 0, seed=13, far_key=True)
