@@ -124,9 +124,14 @@ class StepRunner:
         T, S, P, G = self.max_step_tokens, padded_batch(self.max_batch_seqs), cache.max_blocks, len(cache.groups)
         self._sizes = (T, S, P, G)
         total = 4 * T + 4 * S + G * S * P
-        self._host = torch.empty(total, dtype=torch.int32).pin_memory()
-        self._host_np = self._host.numpy()
-        self._host_np.fill(0)
+        self._host_np = np.zeros(total, dtype=np.int32)        # where a step's metadata is put together
+        # ... and what is sent: a few pinned copies taken in turn, each guarded by an event, because
+        # the asynchronous copy reads pinned memory when the GPU gets to it, which may be after the
+        # host has begun the next step (a caller need not wait for a step before it starts another)
+        self._send = [torch.empty(total, dtype=torch.int32).pin_memory() for _ in range(4)]
+        self._send_np = [t.numpy() for t in self._send]
+        self._sent = [None] * len(self._send)
+        self._turn = 0
         self._dev = torch.zeros(total, dtype=torch.int32, device=self.device)
         self.ctx = StepContext()
         self.ctx.ws = self.ws
@@ -282,7 +287,14 @@ class StepRunner:
             row += 1
             w += 1
         used = self._rows_offset + 4 * rows
-        self._dev[:used].copy_(self._host[:used], non_blocking=True)
+        turn, self._turn = self._turn, (self._turn + 1) % len(self._send)
+        if self._sent[turn] is not None:
+            self._sent[turn].synchronize()       # the copy that last read this buffer has run (almost always long ago)
+        self._send_np[turn][:used] = self._host_np[:used]
+        self._dev[:used].copy_(self._send[turn][:used], non_blocking=True)
+        if self._sent[turn] is None:
+            self._sent[turn] = torch.cuda.Event()
+        self._sent[turn].record()
         if device_fed:
             if any(len(e.tokens) != 1 for e in entries):
                 raise EngineError("step: device-fed token ids need one token per request")

@@ -132,14 +132,26 @@ class AttentionPlan:
         return self.tc is not None and cache.pool_ptr != 0 and math.gcd(128, cache.page_tokens) >= 8
 
     def buffers(self, ctx, n: int, device):
-        """Pinned and device int32 buffers for the tile list, sized once for the largest step so
-        that their addresses never change (captured CUDA graphs keep them)."""
-        if self._host is None or self._host.numel() < 2 * n:
+        """A pinned and the device int32 buffer for the tile list, sized once for the largest step
+        so that the device address never changes (captured CUDA graphs keep it).  The pinned side
+        is one of four taken in turn; `sent()` records the event that guards its reuse (the copy
+        reads pinned memory when the GPU gets to it, possibly after the host has begun another step)."""
+        if self._host is None or self._host[0].numel() < 2 * n:
             most = -(-ctx.max_rows * self.group // 64) + ctx.max_seqs + 8
             cap = 2 * max(n, most)
-            self._host = torch.empty(cap, dtype=torch.int32).pin_memory()
+            self._host = [torch.empty(cap, dtype=torch.int32).pin_memory() for _ in range(4)]
+            self._host_events = [None] * 4
+            self._host_turn = 0
             self._dev = torch.empty(cap, dtype=torch.int32, device=device)
-        return self._host, self._dev
+        self._host_turn = (self._host_turn + 1) % 4
+        if self._host_events[self._host_turn] is not None:
+            self._host_events[self._host_turn].synchronize()
+        return self._host[self._host_turn], self._dev
+
+    def sent(self) -> None:
+        if self._host_events[self._host_turn] is None:
+            self._host_events[self._host_turn] = torch.cuda.Event()
+        self._host_events[self._host_turn].record()
 
     def scratch(self, ctx, floats: int, device) -> torch.Tensor:
         """Scratch for split keys; a split step has at most TARGET_BLOCKS + tiles * kv_heads items."""
@@ -176,6 +188,7 @@ def step_tiles(ctx, plan: AttentionPlan):
     h[at: n_tiles] = -1
     h[n_tiles + at: 2 * n_tiles] = 0
     dev[: 2 * n_tiles].copy_(host[: 2 * n_tiles], non_blocking=True)
+    plan.sent()
     n_splits = 1
     if rows_per_tile == 16:
         key_blocks = -(-ctx.max_kv_len // KEY_BLOCK)

@@ -117,3 +117,39 @@ def test_async_engine_surface():
         assert engine.submit(5, [1], 1)[0] == "unavailable"
     finally:
         engine.stop()
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_steps_started_without_waiting_keep_their_own_metadata(graphs):
+    """A caller may start step after step without waiting for the GPU (the step's metadata is
+    copied from pinned memory when the GPU gets to it): every step must still see its own positions,
+    lengths and tables.  Steps of changing shape, started back to back, against the same steps
+    with a full synchronisation after each."""
+    from bare_cuda_4gib_b200.cache.manager import CacheManager
+    from bare_cuda_4gib_b200.engine.model import load_model
+    from bare_cuda_4gib_b200.engine.step import StepEntry, StepRunner
+
+    folder, page = H.model_folder("B"), 32
+    model, cfg = load_model(folder, "bfloat16", "cuda")
+    rng = random.Random(5)
+    vocab = cfg.vocab_size
+    plan = [[(0, 9), (1, 3)], [(0, 1), (1, 1)], [(0, 1), (1, 1)], [(0, 1), (1, 5), (2, 7)], [(0, 1), (1, 1), (2, 1)],
+            [(0, 1), (1, 1), (2, 1)], [(2, 2)], [(0, 1), (1, 1), (2, 1)], [(0, 1), (1, 1), (2, 1)], [(0, 1), (1, 1), (2, 1)]]
+    tokens = [[(s, [rng.randrange(vocab) for _ in range(n)]) for s, n in step] for step in plan]
+
+    def run(wait):
+        cache = CacheManager(model.cache_demands(), page_tokens=page, max_seqs=4, max_tokens=128, num_pages=16,
+                             dtype=model.dtype, device="cuda")
+        runner = StepRunner(model, cache, max_step_tokens=64, max_batch_seqs=4, use_cuda_graphs=graphs)
+        slots = [cache.acquire_slot() for _ in range(3)]
+        kept = []
+        for step in tokens:
+            logits = runner.step([StepEntry(slots[s], ids, [len(ids) - 1]) for s, ids in step])
+            kept.append(logits.clone())
+            if wait:
+                torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        return kept
+
+    for a, b in zip(run(True), run(False)):
+        assert torch.equal(a, b)
