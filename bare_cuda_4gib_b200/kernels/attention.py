@@ -190,7 +190,8 @@ def step_tiles(ctx, plan: AttentionPlan):
     dev[: 2 * n_tiles].copy_(host[: 2 * n_tiles], non_blocking=True)
     plan.sent()
     n_splits = 1
-    if rows_per_tile == 16:
+    use_decode = rows_per_tile == 16 and plan.decode is not None and n_tiles * plan.kv_heads <= DECODE_MAX_TILES
+    if rows_per_tile == 16 and not use_decode:
         key_blocks = -(-ctx.max_kv_len // KEY_BLOCK)
         n_splits = max(1, min(key_blocks, -(-TARGET_BLOCKS // (n_tiles * plan.kv_heads))))
         if os.environ.get("BARE_CUDA_B200_ATTN_SPLITS"):     # experiments only
@@ -198,15 +199,16 @@ def step_tiles(ctx, plan: AttentionPlan):
         if n_tiles * plan.kv_heads > COUNTER_WORDS:
             n_splits = 1
     dec_splits = dec_slots = 0
-    if rows_per_tile == 16 and plan.decode is not None and n_tiles * plan.kv_heads <= DECODE_MAX_TILES:
+    if use_decode:
         # The cluster decode kernel: up to 8 blocks of 4 warps share a tile, a warp keeps one key
         # block in flight.  As many blocks per tile as still lets every block be resident at once
-        # (a block holds 4 key blocks in shared memory), and no more than there are key blocks.
-        key_blocks = -(-ctx.max_kv_len // KEY_BLOCK)
+        # (a block holds 4 key blocks in shared memory).  The number does not depend on the context
+        # length (a short context leaves some warps without a key block), so a captured graph of the
+        # step stays valid while the requests grow.
         d = plan.head_dim       # shared memory of a block: alignment slack, 4 key blocks (K and V), Q, merge states, barriers
         block_smem = 1024 + 4 * 2 * KEY_BLOCK * d * 2 + 16 * (d + 8) * 2 + 24 * (d + 4) * 4 + 128
         resident = N_SMS * max(1, (227 * 1024) // block_smem)
-        dec_splits = max(1, min(8, resident // (n_tiles * plan.kv_heads), -(-key_blocks // 4)))
+        dec_splits = max(1, min(8, resident // (n_tiles * plan.kv_heads)))
         dec_slots = 1
         if os.environ.get("BARE_CUDA_B200_ATTN_SPLITS"):     # experiments only
             dec_splits = max(1, min(8, int(os.environ["BARE_CUDA_B200_ATTN_SPLITS"])))

@@ -221,7 +221,9 @@ def main() -> int:
 
     def measure_e2e(batch, steps, warm):
         """The scheduler's loop: host token lists in, sampled ids out, every step."""
-        cached = context - steps - warm - 2
+        # prompts are prefilled one a step, so the first request is `batch` tokens ahead of the last:
+        # leave room for all of them to decode through the timed steps before any reaches the context's end
+        cached = context - steps - warm - batch - 2
         sched = engine.scheduler
         for i in range(batch):
             sched.submit(Request(id=i, prompt=[rng.randrange(vocab) for _ in range(cached)],
