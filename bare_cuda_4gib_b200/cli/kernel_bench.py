@@ -139,6 +139,12 @@ def bench_gemv(a):
         inv = (1.0 / (10000.0 ** (torch.arange(d // 2, dtype=torch.float32) * 2.0 / d))).cuda()
         q_out = torch.empty(a.tokens, heads * d, device="cuda", dtype=torch.bfloat16)
         epilogue = K.RotateAndCache(q_out, view, pos, seq, inv, heads, True)
+    prenormed = None
+    if a.prenormed:      # the input as the product before it would have left it (see kernels.lib.Prenormed)
+        items = -(-a.inner // 16)
+        prenormed = K.Prenormed(None, (residual * norm_w.float()).to(torch.bfloat16),
+                                (residual.square().sum(-1) / items).repeat(items, 1).contiguous().float().new_zeros(items, 32), items)
+        prenormed.sq[:, : a.tokens] = (residual.square().sum(-1) / items)[None, :]
     state = {"i": 0}
 
     def run():
@@ -148,7 +154,7 @@ def bench_gemv(a):
             nxt = weights[state["i"] % copies]
             ctx.gemv_prev = [(w.data_ptr(), weight_bytes), (nxt.data_ptr(), weight_bytes)]
             ctx.gemv_now = []
-        x = K.LazyNorm(ctx, residual, norm_w, 1e-5, a.tokens, None, "normed") if a.norm else x_plain
+        x = K.LazyNorm(ctx, residual, norm_w, 1e-5, a.tokens, None, "normed", prenormed) if a.norm else x_plain
         gemv.run(ctx, w, x, a.tokens, torch.bfloat16 if a.form == "swiglu" else torch.float32, "out",
                  a.form == "swiglu", epilogue)
 
@@ -245,6 +251,7 @@ def main(argv=None) -> int:
     v.add_argument("--in", dest="inner", type=int, required=True)
     v.add_argument("--form", default="plain", choices=["plain", "add", "swiglu", "rope"])
     v.add_argument("--norm", action="store_true")
+    v.add_argument("--prenormed", action="store_true", help="with --norm: the input prepared by the product before")
     v.add_argument("--prefetch", action="store_true", help="each launch prefetches the next launch's weights into L2")
     v.add_argument("--kv-heads", type=int, default=4)
     v.add_argument("--head-dim", type=int, default=64)

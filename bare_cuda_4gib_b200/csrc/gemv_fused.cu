@@ -48,6 +48,7 @@ constexpr int MAX_STAGES = 12;
 constexpr int ROW_PAD = 64;                    // bytes between row pieces of a stage beyond their data:
                                                // keeps the 16-byte reads of a quarter warp on distinct banks
 constexpr int SMEM_BUDGET = 220 * 1024;        // dynamic shared memory of one block per SM
+constexpr int SMEM_HALF = 110 * 1024;          // ... of two blocks per SM
 constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;
 constexpr int ERR_GEMV_PRODUCER = 21, ERR_GEMV_CONSUMER = 22;
 
@@ -191,7 +192,7 @@ __device__ __forceinline__ void item_rows(const GemvArgs& a, int item, int g, in
 }
 
 template <int NT, int PRO, int EPI>
-__global__ void __launch_bounds__(THREADS, 1) gemv_fused_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(THREADS, PRO == PRO_NORM ? 1 : 2) gemv_fused_kernel(const GemvArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int row_stride = a.kc * 2 + ROW_PAD, stage_bytes = 16 * row_stride;
   uint8_t* ring = smem;                                                              // [stages][16][row_stride]
@@ -632,7 +633,6 @@ extern "C" int llm_gemv_fused(const void* w, int w_rows, int k, int tokens, int 
                               long long prefetch_bytes, int max_blocks, int* error_word, cudaStream_t stream) {
   SmemPlan plan;
   if (!plan_smem(tokens, k, pro, SMEM_BUDGET, 2, plan)) return ERR_BAD_SIZE;
-  const size_t smem = plan.bytes;
   if (out_dtype != DT_F32 && out_dtype != DT_BF16) return ERR_BAD_DTYPE;
   if (epi == EPI_ADD && out_dtype != DT_F32) return ERR_BAD_DTYPE;
   if (tokens > SQ_SLOTS || (pro == PRO_PRENORMED && (!sq_in || sq_items < 1)) || (pre_x && (epi != EPI_ADD || !pre_w || !pre_sq)))
@@ -664,8 +664,20 @@ extern "C" int llm_gemv_fused(const void* w, int w_rows, int k, int tokens, int 
     a.n_items = (n_out + 15) / 16;
   }
   const int nt = (tokens + 7) / 8;
-  const int grid = a.n_items < max_blocks ? a.n_items : max_blocks;
+  int grid = a.n_items < max_blocks ? a.n_items : max_blocks;
   if (grid < 1) return ERR_BAD_SIZE;
+  // A product with a few more items than SMs (one and a bit per block) would keep most SMs waiting
+  // for the blocks that run two.  If a block with one whole-row stage fits twice on an SM, every
+  // item gets a block of its own instead and all of them stream at once.
+  SmemPlan one;
+  if (pro != PRO_NORM && a.n_items > max_blocks && a.n_items <= 2 * max_blocks &&
+      plan_smem(tokens, k, pro, SMEM_HALF, 1, one) && one.kc == k) {
+    plan = one;
+    plan.stages = 1, plan.bytes = plan.bytes - (size_t)(one.stages - 1) * 16 * (one.kc * 2 + ROW_PAD);
+    a.kc = plan.kc, a.stages = 1, a.first_aliased = 1;
+    grid = a.n_items;
+  }
+  const size_t smem = plan.bytes;
   switch (nt) {
     case 1: return launch_pro<1>(pro, epi, a, smem, grid, stream);
     case 2: return launch_pro<2>(pro, epi, a, smem, grid, stream);
