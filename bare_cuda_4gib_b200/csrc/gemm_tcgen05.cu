@@ -65,6 +65,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
                : "memory");
 }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -462,6 +466,226 @@ gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same product for many tokens (ORIENT 1, no K split) as a persistent kernel: one block per SM
+// walks over output tiles, the stage ring runs on across tile boundaries (no pipeline drain and
+// refill per tile, all of shared memory for one ring), and the accumulator alternates between two
+// halves of tensor memory, so that the epilogue warps drain tile j while the MMA warp already
+// works on tile j + 1.  Consecutive tiles of a block's neighbours share activation rows and weight
+// rows (tile index -> token tile fastest), which keeps both operands in L2.
+constexpr int ACC_COLS = 256;   // tensor-memory columns per accumulator half
+
+template <int MODE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_persistent_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_w,
+                               const __grid_constant__ CUtensorMap map_a, void* __restrict__ out, int out_is_f32,
+                               int n_tokens, int n_features, int n_kb, long long ld_out, int up_row_offset,
+                               int f_tiles, int t_tiles, int* __restrict__ error_word) {
+  const int BN = geo.bn;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + geo.stages * geo.stage_bytes);
+  uint64_t* empty_bar = full_bar + geo.stages;
+  uint64_t* acc_full = empty_bar + geo.stages;      // [2]: the accumulator half holds a finished tile
+  uint64_t* acc_empty = acc_full + 2;               // [2]: the epilogue has read it out
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int F_TILE = MODE == 1 ? BN / 2 : BN;
+  const int n_tiles = f_tiles * t_tiles;
+
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+    for (int s = 0; s < geo.stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);   // the four epilogue warps
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)),
+                 "r"(2 * ACC_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  pdl_wait();
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    // Issuing a copy costs its thread a few hundred cycles, about what the tensor core needs for
+    // a stage of a narrow tile.  So four lanes issue: lanes 0 and 1 take the even k blocks of the
+    // block's sequence (weights and barrier / activations), lanes 2 and 3 the odd ones.
+    if (lane < 4) {
+      const int role = lane & 1, turn = lane >> 1;
+      int s = turn % geo.stages, armed = 0;
+      uint32_t phase = 0;
+      int q = 0;   // k blocks of this thread block so far, over all its tiles
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const int f0 = (tile / t_tiles) * F_TILE, t0 = (tile % t_tiles) * BM;
+        for (int i = 0; i < n_kb; ++i, ++q) {
+          if ((q & 1) != turn) continue;
+          if (!mbar_wait(&empty_bar[s], phase ^ 1, abort_flag)) {
+            *abort_flag = 1;
+            atomicCAS(error_word, 0, ERR_TIMEOUT_PRODUCER);
+            ok = false;
+            break;
+          }
+          uint8_t* stage = smem + s * geo.stage_bytes;
+          const int k0 = i * BK;
+          if (role == 0) {
+            mbar_expect_tx(&full_bar[s], geo.stage_bytes);
+            uint8_t* b_tile = stage + A_BYTES;
+            tma_load_2d(b_tile, &map_w, &full_bar[s], k0, f0);
+            if (MODE == 1) tma_load_2d(b_tile + geo.b_bytes / 2, &map_w, &full_bar[s], k0, up_row_offset + f0);
+          } else {
+            tma_load_2d(stage, &map_a, &full_bar[s], k0, t0);
+          }
+          armed = q + 1;
+          s += 2;
+          if (s >= geo.stages) { s -= geo.stages; phase ^= 1; }
+        }
+      }
+      armed = max(armed, __shfl_sync(0xfu, armed, 2));
+      if (lane == 0 && *abort_flag) {
+        // copies already issued still land in shared memory: wait for them (bounded) before leaving
+        for (int i = max(0, armed - geo.stages); i < armed; ++i) {
+          const unsigned long long start = global_timer();
+          while (!mbar_try_wait(&full_bar[i % geo.stages], (i / geo.stages) & 1) &&
+                 global_timer() - start < WAIT_LIMIT_NS / 10) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = geo.idesc, smem_base = smem_u32(smem);
+      int s = 0, j = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++j) {
+        const int buf = j & 1;
+        if (!mbar_wait(&acc_empty[buf], ((j >> 1) & 1) ^ 1, abort_flag)) {
+          *abort_flag = 1;
+          atomicCAS(error_word, 0, ERR_TIMEOUT_MMA);
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t acc_addr = tmem_base + buf * ACC_COLS;
+        for (int i = 0; i < n_kb; ++i) {
+          if (!mbar_wait(&full_bar[s], phase, abort_flag)) {
+            *abort_flag = 1;
+            atomicCAS(error_word, 0, ERR_TIMEOUT_MMA);
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = smem_base + s * geo.stage_bytes;
+          const uint64_t desc_a = smem_desc_sw128(a_addr), desc_b = smem_desc_sw128(a_addr + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);
+            umma_bf16(acc_addr, desc_a + koff, desc_b + koff, idesc, (i > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);
+          if (++s == geo.stages) { s = 0; phase ^= 1; }
+        }
+        umma_commit(&acc_full[buf]);   // (after giving up this still releases the epilogue)
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5)
+    const int quad = warp & 3;
+    int j = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++j) {
+      const int buf = j & 1;
+      const int f0 = (tile / t_tiles) * F_TILE, t0 = (tile % t_tiles) * BM;
+      if (!mbar_wait(&acc_full[buf], (j >> 1) & 1, abort_flag) || *abort_flag) {
+        *abort_flag = 1;
+        atomicCAS(error_word, 0, ERR_TIMEOUT_EPILOGUE);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * ACC_COLS;
+      float* out_f32 = reinterpret_cast<float*>(out);
+      __nv_bfloat16* out_bf16 = reinterpret_cast<__nv_bfloat16*>(out);
+      const int t = t0 + quad * 32 + lane;
+      const bool vec_ok = out_is_f32 ? (ld_out % 4 == 0 && (reinterpret_cast<uintptr_t>(out_f32) & 15) == 0)
+                                     : (ld_out % 8 == 0 && (reinterpret_cast<uintptr_t>(out_bf16) & 15) == 0);
+#pragma unroll 1
+      for (int c0 = 0; c0 < F_TILE; c0 += 16) {
+        if (f0 + c0 >= n_features) break;  // uniform across the block
+        uint32_t g[16], u[16];
+        if (n_kb > 0) {
+          tmem_load16(lane_base + c0, g);
+          if (MODE == 1) tmem_load16(lane_base + BN / 2 + c0, u);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        } else {
+#pragma unroll
+          for (int q = 0; q < 16; ++q) g[q] = u[q] = 0u;
+        }
+        float v[16];
+#pragma unroll
+        for (int q = 0; q < 16; ++q) {
+          v[q] = __uint_as_float(g[q]);
+          if (MODE == 1) v[q] = v[q] / (1.0f + expf(-v[q])) * __uint_as_float(u[q]);
+        }
+        if (t >= n_tokens) continue;
+        const int f = f0 + c0;
+        const long long at = (long long)t * ld_out + f;
+        if (vec_ok && f + 16 <= n_features) {
+          if (out_is_f32) {
+            float4* dst = reinterpret_cast<float4*>(out_f32 + at);
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) dst[q4] = make_float4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
+          } else {
+            uint32_t pk[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * q], v[2 * q + 1]);
+              pk[q] = *reinterpret_cast<uint32_t*>(&b);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(out_bf16 + at);
+            dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+          }
+        } else {
+#pragma unroll
+          for (int q = 0; q < 16; ++q) {
+            if (f + q < n_features) {
+              if (out_is_f32) out_f32[at + q] = v[q];
+              else out_bf16[at + q] = __float2bfloat16_rn(v[q]);
+            }
+          }
+        }
+      }
+      // this warp has read its lanes of the half out: the MMA warp may overwrite it
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * ACC_COLS) : "memory");
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -500,6 +724,28 @@ int launch(int bn, const CUtensorMap* map_w, const CUtensorMap* map_a, void* out
   if (grid.y > 65535 || grid.z > 65535) return ERR_BAD_SIZE;
   launch_kernel(kern, grid, NUM_THREADS, smem, stream, g, *map_w, *map_a, out, out_is_f32, n_tokens, n_features,
                 k_blocks, per_split, ld_out, partial_stride, up_row_offset, error_word);
+  return launch_status();
+}
+
+template <int MODE>
+int launch_persistent(int bn, const CUtensorMap* map_w, const CUtensorMap* map_a, void* out, int out_is_f32, int n_tokens,
+                      int n_features, int K, long long ld_out, int up_row_offset, int* error_word, cudaStream_t stream) {
+  const Geometry g = make_geometry(bn, MODE, 1, 1);
+  if (g.stages < 2 || g.tmem_cols > ACC_COLS) return ERR_BAD_SIZE;
+  auto kern = gemm_tcgen05_persistent_kernel<MODE>;
+  static size_t configured = 0;
+  const size_t smem = smem_bytes(g);
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return launch_status();
+    configured = smem;
+  }
+  const int f_tile = MODE == 1 ? bn / 2 : bn;
+  const int f_tiles = (n_features + f_tile - 1) / f_tile, t_tiles = (n_tokens + BM - 1) / BM;
+  const long long tiles = (long long)f_tiles * t_tiles;
+  const int grid = tiles < 148 ? (int)tiles : 148;
+  launch_kernel(kern, grid, NUM_THREADS, smem, stream, g, *map_w, *map_a, out, out_is_f32, n_tokens, n_features,
+                (K + BK - 1) / BK, ld_out, up_row_offset, f_tiles, t_tiles, error_word);
   return launch_status();
 }
 
@@ -552,6 +798,19 @@ extern "C" int llm_gemm_bf16(const void* map_w, const void* map_a, void* out, in
   const long long f_tile = orient == 0 ? (mode == 1 ? BM / 2 : BM) : (mode == 1 ? bn / 2 : bn), t_tile = orient == 0 ? bn : BM;
   const long long tiles = ((n_features + f_tile - 1) / f_tile) * ((n_tokens + t_tile - 1) / t_tile) * splits;
   const bool pair = tiles > 148 && two.tmem_cols <= 256 && two.stages >= ((orient == 1 && mode == 1) ? 2 : 3);
+  static int persistent_wish = -1;
+  if (persistent_wish < 0) {
+    const char* v = getenv("BARE_CUDA_B200_GEMM_PERSISTENT");
+    persistent_wish = (v && v[0] == '0') ? 0 : 1;
+  }
+  if (persistent_wish && orient == 1 && splits == 1 && tiles > 148 && bn >= 192) {
+    // More tiles than SMs: one block per SM walks over them (see the persistent kernel).  Only for
+    // wide tiles: a stage of a narrow tile is shorter on the tensor core than the one issuing
+    // thread's round of waiting for it, issuing its instructions and committing, and then two
+    // blocks per SM with an issuing thread each are faster.
+    if (mode == 0) return launch_persistent<0>(bn, mw, ma, out, f32, n_tokens, n_features, K, ld_out, up_row_offset, error_word, stream);
+    return launch_persistent<1>(bn, mw, ma, out, f32, n_tokens, n_features, K, ld_out, up_row_offset, error_word, stream);
+  }
 #define GEMM_CASE(MODE_, ORIENT_)                                                                            \
   if (mode == MODE_ && orient == ORIENT_)                                                                    \
     return pair ? launch<MODE_, ORIENT_, 2>(bn, mw, ma, out, f32, n_tokens, n_features, K, ld_out,           \
