@@ -431,7 +431,14 @@ gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_
             if (out_is_f32) {
               float4* dst = reinterpret_cast<float4*>(out_f32 + at);
 #pragma unroll
-              for (int q4 = 0; q4 < 4; ++q4) dst[q4] = make_float4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
+              for (int q4 = 0; q4 < 4; ++q4) {
+                float4 w4 = make_float4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
+                if (out_is_f32 == 2) {   // accumulate: the output is the float32 residual stream
+                  const float4 old = dst[q4];
+                  w4.x += old.x, w4.y += old.y, w4.z += old.z, w4.w += old.w;
+                }
+                dst[q4] = w4;
+              }
             } else {
               uint32_t pk[8];
 #pragma unroll
@@ -447,7 +454,7 @@ gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               if (f + j < n_features) {
-                if (out_is_f32) out_f32[at + j] = v[j];
+                if (out_is_f32) out_f32[at + j] = out_is_f32 == 2 ? out_f32[at + j] + v[j] : v[j];
                 else out_bf16[at + j] = __float2bfloat16_rn(v[j]);
               }
             }
@@ -649,7 +656,14 @@ gemm_tcgen05_persistent_kernel(const Geometry geo, const __grid_constant__ CUten
           if (out_is_f32) {
             float4* dst = reinterpret_cast<float4*>(out_f32 + at);
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) dst[q4] = make_float4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
+            for (int q4 = 0; q4 < 4; ++q4) {
+              float4 w4 = make_float4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
+              if (out_is_f32 == 2) {   // accumulate: the output is the float32 residual stream
+                const float4 old = dst[q4];
+                w4.x += old.x, w4.y += old.y, w4.z += old.z, w4.w += old.w;
+              }
+              dst[q4] = w4;
+            }
           } else {
             uint32_t pk[8];
 #pragma unroll
@@ -665,7 +679,7 @@ gemm_tcgen05_persistent_kernel(const Geometry geo, const __grid_constant__ CUten
 #pragma unroll
           for (int q = 0; q < 16; ++q) {
             if (f + q < n_features) {
-              if (out_is_f32) out_f32[at + q] = v[q];
+              if (out_is_f32) out_f32[at + q] = out_is_f32 == 2 ? out_f32[at + q] + v[q] : v[q];
               else out_bf16[at + q] = __float2bfloat16_rn(v[q]);
             }
           }
@@ -774,11 +788,13 @@ extern "C" int llm_gemm_tensor_map(void* map_out, const void* base, long long ro
 // out[z][t, f] (z < splits) = partial sums of act[t, :] . w[f, :]; mode 1: silu(gate) * up with
 // w = [gate; up], the up rows starting at `up_row_offset` (splits must be 1 then).
 // `bn` is the N tile, a multiple of 16 up to 256 (of 32 for orient 1 with mode 1).
+// `accumulate` (orient 1, mode 0, float32 out, no split): out[t, f] += the product, which is how a
+// projection adds itself into the residual stream.
 // orient 0: bn tokens per tile; map_a's box must have bn rows, map_w's 128 (64 in mode 1).
 // orient 1: bn weight rows per tile; map_a's box must have 128 rows, map_w's bn rows (bn / 2 in mode 1).
 extern "C" int llm_gemm_bf16(const void* map_w, const void* map_a, void* out, int out_dtype, int n_tokens,
                              int n_features, int K, long long ld_out, long long partial_stride, int splits,
-                             int bn, int mode, int orient, int up_row_offset, int* error_word,
+                             int bn, int mode, int orient, int up_row_offset, int accumulate, int* error_word,
                              cudaStream_t stream) {
   if (n_tokens <= 0 || n_features <= 0) return 0;
   if (K <= 0 || splits <= 0 || (mode == 1 && splits != 1)) return ERR_BAD_SIZE;
@@ -789,7 +805,8 @@ extern "C" int llm_gemm_bf16(const void* map_w, const void* map_a, void* out, in
   memcpy(&ma_copy, map_a, sizeof(CUtensorMap));
   const CUtensorMap* mw = &mw_copy;
   const CUtensorMap* ma = &ma_copy;
-  const int f32 = out_dtype == DT_F32;
+  if (accumulate && (orient != 1 || mode != 0 || splits != 1 || out_dtype != DT_F32)) return ERR_BAD_SIZE;
+  const int f32 = out_dtype == DT_F32 ? (accumulate ? 2 : 1) : 0;   // 2: out[t, f] += result
   if (bn < 16 || bn > 256 || bn % 16 || (mode == 1 && orient == 1 && bn % 32)) return ERR_BAD_SIZE;
   // Two thread blocks per SM let one block's epilogue overlap the other's main loop, at the price
   // of half the pipeline depth each: worth it only when there are more tiles than SMs and at

@@ -28,7 +28,7 @@ def lib():
         P, I, L = c_void_p, c_int, c_longlong
         l.llm_gemm_tensor_map.argtypes = [P, P, L, L, L, I]
         l.llm_gemm_tensor_map.restype = c_int
-        l.llm_gemm_bf16.argtypes = [P, P, P, I, I, I, I, L, L, I, I, I, I, I, P, P]
+        l.llm_gemm_bf16.argtypes = [P, P, P, I, I, I, I, L, L, I, I, I, I, I, I, P, P]
         l.llm_gemm_bf16.restype = c_int
         _lib = l
     return _lib
@@ -157,7 +157,9 @@ def feature_tile(rows: int, n_out: int, swiglu: bool) -> int:
 
 
 def run(ctx, plan: GemmPlan, a: torch.Tensor, rows: int, out_dtype: torch.dtype, buffer: str,
-        allow_partials: bool, swiglu: bool) -> Partials:
+        allow_partials: bool, swiglu: bool, add_to: Optional[torch.Tensor] = None) -> Optional[Partials]:
+    """`add_to` (a float32 [rows, n] matrix, the residual stream): where the kernel can, the product is
+    added into it and None comes back; otherwise the plain result comes back as without it."""
     if a.dtype != torch.bfloat16 or a.stride(-1) != 1 or a.shape[-1] != plan.k or a.data_ptr() % 16 or a.stride(0) % 8:
         raise KernelLaunchError(f"gemm_tcgen05: activations {tuple(a.shape)} {a.dtype} do not fit weight "
                                 f"[{plan.n}, {plan.k}]")
@@ -167,12 +169,14 @@ def run(ctx, plan: GemmPlan, a: torch.Tensor, rows: int, out_dtype: torch.dtype,
     if rows > TOKENS_ON_ROWS_ABOVE:
         n_out = plan.n // 2 if swiglu else plan.n
         bn = feature_tile(rows, n_out, swiglu)
-        out = ctx.ws.get(buffer, (rows, n_out), out_dtype)
+        fused_add = (add_to is not None and not swiglu and out_dtype == torch.float32 and add_to.dtype == torch.float32
+                     and add_to.shape[-1] == n_out and add_to.stride(-1) == 1)
+        out = add_to if fused_add else ctx.ws.get(buffer, (rows, n_out), out_dtype)
         _check(l.llm_gemm_bf16(ctypes.addressof(plan.weight_map(bn // 2 if swiglu else bn)),
                                ctypes.addressof(plan.act_map(a, BM)), out.data_ptr(), code, rows, n_out, plan.k,
                                out.stride(0), 0, 1, bn, 1 if swiglu else 0, 1, n_out if swiglu else 0,
-                               err.data_ptr(), ctx.stream), "gemm_tcgen05 (tokens on rows)")
-        return Partials(out)
+                               1 if fused_add else 0, err.data_ptr(), ctx.stream), "gemm_tcgen05 (tokens on rows)")
+        return None if fused_add else Partials(out)
     bn = token_tile(rows)
     if swiglu:
         inter = plan.n // 2
@@ -181,7 +185,7 @@ def run(ctx, plan: GemmPlan, a: torch.Tensor, rows: int, out_dtype: torch.dtype,
             # 64 gate rows and the matching 64 up rows share a block's 128 MMA rows: SwiGLU in the
             # epilogue and no partial results, when that alone gives every SM a block
             _check(l.llm_gemm_bf16(ctypes.addressof(plan.weight_map(BM // 2)), ctypes.addressof(plan.act_map(a, bn)),
-                                   out.data_ptr(), code, rows, inter, plan.k, out.stride(0), 0, 1, bn, 1, 0, inter,
+                                   out.data_ptr(), code, rows, inter, plan.k, out.stride(0), 0, 1, bn, 1, 0, inter, 0,
                                    err.data_ptr(), ctx.stream), "gemm_tcgen05 (swiglu)")
             return Partials(out)
         # a narrow feed-forward: stream [gate; up] as one product split over K so that every SM takes
@@ -199,6 +203,6 @@ def run(ctx, plan: GemmPlan, a: torch.Tensor, rows: int, out_dtype: torch.dtype,
         stride = 0
     _check(l.llm_gemm_bf16(ctypes.addressof(plan.map_w), ctypes.addressof(plan.act_map(a, bn)), out.data_ptr(),
                            DT_BF16 if out_dtype == torch.bfloat16 else DT_F32, rows, plan.n, plan.k,
-                           out.stride(-2), stride, splits, bn, 0, 0, 0, err.data_ptr(), ctx.stream),
+                           out.stride(-2), stride, splits, bn, 0, 0, 0, 0, err.data_ptr(), ctx.stream),
            "gemm_tcgen05")
     return Partials(out, splits)

@@ -46,6 +46,8 @@ class Linear:
         a = K.materialize(a)
         if self.fast is not None and ctx.use_fast_gemm:
             from ..kernels import gemm
+            # (the many-token kernel can add into the residual stream itself, `add_to=`; measured
+            # slower than leaving the add to the norm kernel that follows, so it is not asked to)
             return gemm.run(ctx, self.fast, a, rows, out_dtype, buffer, allow_partials, swiglu)
         if swiglu:
             full = ctx.ws.get(buffer + ".gate_up", (rows, self.out_features), out_dtype)

@@ -243,6 +243,28 @@ def test_gemm_tcgen05(m, n, k, out_dtype):
         _close(got, want, 2 ** -8, 1e-4 * math.sqrt(k))
 
 
+@pytest.mark.parametrize("m,n,k,bn", [(300, 1000, 96, 0), (513, 130, 176, 0), (2048, 2048, 512, 0), (2048, 5120, 128, 256),
+                                      (1100, 3000, 192, 256), (257, 72, 64, 0)])
+def test_gemm_tcgen05_adds_into_the_residual(m, n, k, bn, monkeypatch):
+    """Many-token products that add themselves into a float32 matrix (both the two-blocks-per-SM
+    kernel and, with wide tiles and more tiles than SMs, the persistent one)."""
+    from bare_cuda_4gib_b200.kernels import gemm
+    if bn:
+        monkeypatch.setenv("BARE_CUDA_B200_GEMM_BN", str(bn))
+    torch.manual_seed(m + n)
+    ctx = _ctx()
+    a = ctx.ws.get("a", (m, k), torch.bfloat16)
+    a.copy_(torch.randn(m, k, device=DEV))
+    w = torch.randn(n, k, device=DEV).to(torch.bfloat16)
+    residual = torch.randn(m + 5, n, device=DEV)
+    before = residual.double().clone()
+    assert gemm.run(ctx, gemm.plan_for(w), a, m, torch.float32, "out", True, False, add_to=residual[:m]) is None
+    gemm.check_errors()
+    want = before.clone()
+    want[:m] += a.double() @ w.double().t()
+    _close(residual, want, 1e-5, 1e-4 * math.sqrt(k))
+
+
 @pytest.mark.parametrize("m,inter,k", [(3, 176, 64), (40, 5632, 256), (130, 256, 96), (300, 200, 128), (9, 2816, 512),
                                        (700, 176, 64), (2048, 5632, 128), (257, 1000, 96)])
 def test_gemm_tcgen05_swiglu(m, inter, k):
