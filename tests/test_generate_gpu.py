@@ -153,3 +153,49 @@ def test_steps_started_without_waiting_keep_their_own_metadata(graphs):
 
     for a, b in zip(run(True), run(False)):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_stop_ids_and_lengths_while_running_ahead(dtype):
+    """Greedy requests decode with the scheduler a step ahead; one of them stops on a token id it
+    generates midway, the others run to different lengths.  Every request must give exactly the
+    tokens it gives alone up to its end, the stop token included, and everything must be given back."""
+    from bare_cuda_4gib_b200.engine.engine import LLMEngine
+    from bare_cuda_4gib_b200.engine.scheduler import Request
+
+    folder, page = H.model_folder("A"), H.TINY["A"][1]
+    vocab = H.TINY["A"][0]["vocab_size"]
+    rng = random.Random(33)
+    prompts = [H.random_ids(rng, n, vocab) for n in (9, 21, 5, 14)]
+    lengths = [30, 12, 25, 18]
+    engine = LLMEngine(folder, max_tokens=64, max_seqs=4, dtype=dtype, page_tokens=page)
+    alone = [engine.generate(p, n) for p, n in zip(prompts, lengths)]
+    # request 0 stops at the first token of its own run that did not occur earlier in that run, at or after index 6
+    stop_at = next(i for i in range(6, 30) if alone[0][i] not in alone[0][:i])
+    stop_id = alone[0][stop_at]
+    sched = engine.scheduler
+    for i, (p, n) in enumerate(zip(prompts, lengths)):
+        sched.submit(Request(id=i, prompt=p, max_new_tokens=n, stop_ids=[stop_id] if i == 0 else []))
+    got = {i: [] for i in range(4)}
+    finish = {}
+    fed = 0
+    launch = engine.executor.launch
+
+    def counting(entries, params, rngs, device_fed=False):
+        nonlocal fed
+        fed += device_fed
+        return launch(entries, params, rngs, device_fed=device_fed)
+
+    engine.executor.launch = counting
+    while not sched.idle:
+        for e in sched.step():
+            if e.token >= 0:
+                got[e.id].append(e.token)
+            if e.finish:
+                finish[e.id] = e.finish
+    assert fed > 5, "the scheduler never ran ahead"
+    assert got[0] == alone[0][: stop_at + 1] and finish[0] == "stop"
+    for i in (1, 2, 3):
+        assert got[i] == alone[i] and finish[i] == "length"
+    assert engine.cache.free_slots == 4 and all(g.pool.pages_in_use == 0 for g in engine.cache.groups)
+    engine.cache.check_consistency()
