@@ -2,8 +2,8 @@
 // for up to 32 tokens (the decode step and short prompt portions), bfloat16 weights, float32 sums.
 //
 // With so few tokens the product is bound by reading W once, and a step's time by the number of
-// kernels and the memory round trips between them.  So this kernel takes its input in one of two
-// forms and finishes its output in one of four:
+// kernels and the memory round trips between them.  So this kernel takes its input in one of
+// three forms and finishes its output in one of four:
 //   input   PRO_BF16   x is a bfloat16 matrix in global memory
 //           PRO_NORM   x = rms_norm(residual row) * weight, computed here from the float32
 //                      residual stream (cuongvng/bare-cuda-4gib engine/kernels/rmsnorm.cu:26-40)
@@ -28,12 +28,13 @@
 // as long as A and B agree: a thread reads 16 contiguous bytes (8 values of k) of each of its two
 // rows and of its token's x and feeds them to two instructions.
 //
-// One block per SM.  A producer warp streams the block's items through a ring of shared-memory
-// stages (16 row pieces of up to `kc` values each, one bulk copy per piece, landing on an
-// mbarrier); it starts before the kernel has waited for its predecessor in the stream, since
-// weights are never written.  Eight consumer warps split each stage's k range, multiply out of shared memory, and at
-// the end of an item add their partial sums in warp order, so a result depends neither on the
-// batch nor on the grid.  x for all tokens sits in shared memory for the whole kernel.  Every
+// One block per SM (two, with one item each, when there are a few more items than SMs).  A
+// producer warp streams the block's items through a ring of shared-memory stages (16 row pieces
+// of up to `kc` values each, one bulk copy per piece, landing on an mbarrier); it starts before
+// the kernel has waited for its predecessor in the stream, since weights are never written.
+// Eight consumer warps split each stage's k range, multiply out of shared memory, and at the end
+// of an item add their partial sums in warp order, so a result depends neither on the batch nor
+// on the grid.  x for all tokens sits in shared memory for the whole kernel.  Every
 // wait on an mbarrier is bounded: after about a second without progress the thread records an
 // error code, and from then on every wait of the block returns at once, so the block still
 // reaches its barriers and returns (its results are then invalid, which the error word tells).
