@@ -343,26 +343,36 @@ rope_cache_write_kernel(const TI* __restrict__ qkv, int n_partials, long long pa
   }
 }
 
-// The same for many tokens of a bfloat16 step: one thread rotates eight neighbouring pairs with
-// 16-byte loads and stores (head sizes that are multiples of 16, one finished input, no partials).
-__global__ void __launch_bounds__(256)
+// The same for many tokens of a bfloat16 step (head sizes that are multiples of 16 up to 256, one
+// finished input, no partials): one block per token.  A token's angles are the same for every
+// head, so the block first computes its head_dim / 2 sines and cosines once into shared memory
+// (the precise sincosf is what the kernel's time would otherwise go to: 36 heads would each repeat
+// it), then each thread rotates eight neighbouring pairs with 16-byte loads and stores.
+constexpr int ROPE_VEC_THREADS = 128;
+__global__ void __launch_bounds__(ROPE_VEC_THREADS)
 rope_cache_write_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out, PagedCache cache,
                             const int32_t* __restrict__ positions, const int32_t* __restrict__ row_seq,
                             const float* __restrict__ inv_freq, int q_heads, int write_cache, int n_tokens) {
   pdl_launch_dependents();
   pdl_wait();
+  __shared__ float cs[128], sn[128];
   const int d = cache.head_dim, half = d / 2;
   const int groups = half / 8;                         // 8-pair groups per rotated head
   const int n_heads = q_heads + 2 * cache.kv_heads;
-  const int per_token = (q_heads + cache.kv_heads) * groups + cache.kv_heads * (d / 8);
-  const long long total = (long long)n_tokens * per_token;
-  for (long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x; item < total;
-       item += (long long)gridDim.x * blockDim.x) {
-    const int t = (int)(item / per_token);
-    int w = (int)(item % per_token);
-    const int pos = positions[t];
-    const __nv_bfloat16* row = qkv + (long long)t * n_heads * d;
-    const int rotated = (q_heads + cache.kv_heads) * groups;
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  for (int p = threadIdx.x; p < half; p += ROPE_VEC_THREADS) {
+    float c = 1.0f, s = 0.0f;
+    if (inv_freq) sincosf((float)pos * inv_freq[p], &s, &c);
+    cs[p] = c;
+    sn[p] = s;
+  }
+  __syncthreads();
+  const int rotated = (q_heads + cache.kv_heads) * groups;
+  const int per_token = rotated + cache.kv_heads * (d / 8);
+  const __nv_bfloat16* row = qkv + (long long)t * n_heads * d;
+  const int seq = row_seq[t];
+  for (int w = threadIdx.x; w < per_token; w += ROPE_VEC_THREADS) {
     if (w < rotated) {
       const int h = w / groups, p0 = (w % groups) * 8;
       __nv_bfloat16* dst;
@@ -370,7 +380,7 @@ rope_cache_write_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16
         dst = q_out + ((long long)t * q_heads + h) * d;
       } else {
         if (!write_cache) continue;
-        const long long off = cache_offset(cache, row_seq[t], pos, h - q_heads);
+        const long long off = cache_offset(cache, seq, pos, h - q_heads);
         if (off < 0) continue;
         dst = (__nv_bfloat16*)cache.k + off;
       }
@@ -383,8 +393,7 @@ rope_cache_write_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16
       __nv_bfloat16* hi_o = reinterpret_cast<__nv_bfloat16*>(&hi_out);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        float c = 1.0f, s = 0.0f;
-        if (inv_freq) sincosf((float)pos * inv_freq[p0 + j], &s, &c);
+        const float c = cs[p0 + j], s = sn[p0 + j];
         const float a = __bfloat162float(lo[j]), b = __bfloat162float(hi[j]);
         lo_o[j] = __float2bfloat16_rn(a * c - b * s);
         hi_o[j] = __float2bfloat16_rn(b * c + a * s);
@@ -393,9 +402,9 @@ rope_cache_write_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16
       *reinterpret_cast<uint4*>(dst + half + p0) = hi_out;
     } else {
       if (!write_cache) continue;
-      w -= rotated;
-      const int kvh = w / (d / 8), c0 = (w % (d / 8)) * 8;
-      const long long off = cache_offset(cache, row_seq[t], pos, kvh);
+      const int v = w - rotated;
+      const int kvh = v / (d / 8), c0 = (v % (d / 8)) * 8;
+      const long long off = cache_offset(cache, seq, pos, kvh);
       if (off < 0) continue;
       *reinterpret_cast<uint4*>((__nv_bfloat16*)cache.v + off + c0) =
           *reinterpret_cast<const uint4*>(row + (long long)(q_heads + cache.kv_heads + kvh) * d + c0);
@@ -415,11 +424,9 @@ extern "C" int llm_rope_cache_write(const void* qkv, int in_dtype, int n_partial
   PagedCache c{k_base, v_base, block_table, page_stride, table_stride, page_tokens, kv_heads, head_dim};
   const int n_heads = q_heads + 2 * kv_heads;
   const auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
-  if (in_dtype == DT_BF16 && out_dtype == DT_BF16 && n_partials == 1 && head_dim % 16 == 0 && n_tokens >= 64 &&
+  if (in_dtype == DT_BF16 && out_dtype == DT_BF16 && n_partials == 1 && head_dim % 16 == 0 && head_dim <= 256 && n_tokens >= 64 &&
       aligned16(qkv) && aligned16(q_out) && aligned16(k_base) && aligned16(v_base)) {
-    const long long items = (long long)n_tokens * ((q_heads + kv_heads) * (head_dim / 16) + kv_heads * (head_dim / 8));
-    const int blocks = (int)((items + 255) / 256 < 148 * 8 ? (items + 255) / 256 : 148 * 8);
-    launch_kernel(rope_cache_write_vec_kernel, blocks, 256, 0, stream, (const __nv_bfloat16*)qkv,
+    launch_kernel(rope_cache_write_vec_kernel, n_tokens, ROPE_VEC_THREADS, 0, stream, (const __nv_bfloat16*)qkv,
                   (__nv_bfloat16*)q_out, c, positions, row_seq, inv_freq, q_heads, write_cache, n_tokens);
     return launch_status();
   }
