@@ -142,6 +142,75 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const float
   }
 }
 
+// The same for many rows (prompt portions): one warp per row, the row kept in registers between
+// the sum of squares and the scaling, no block barrier, so that an SM has dozens of rows' loads
+// in flight at once.  HOLD float4 values per lane: rows of up to 128 * HOLD values.
+template <int HOLD>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_rows_kernel(float* __restrict__ residual, const float* __restrict__ delta, int n_partials,
+                        long long partial_stride, const __nv_bfloat16* __restrict__ weight,
+                        __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ row_index, int rows, int hidden,
+                        float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const long long src = row_index ? row_index[r] : r;
+  float4* x = reinterpret_cast<float4*>(residual + src * hidden);
+  const int n4 = hidden / 4;
+  float4 v[HOLD];
+#pragma unroll
+  for (int j = 0; j < HOLD; ++j)
+    if (lane + 32 * j < n4) v[j] = x[lane + 32 * j];
+  if (delta) {
+    for (int p = 0; p < n_partials; ++p) {
+      const float4* d4 = reinterpret_cast<const float4*>(delta + p * partial_stride + src * hidden);
+      float4 d[HOLD];
+#pragma unroll
+      for (int j = 0; j < HOLD; ++j)
+        if (lane + 32 * j < n4) d[j] = d4[lane + 32 * j];
+#pragma unroll
+      for (int j = 0; j < HOLD; ++j)
+        if (lane + 32 * j < n4) {
+          v[j].x += d[j].x;
+          v[j].y += d[j].y;
+          v[j].z += d[j].z;
+          v[j].w += d[j].w;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < HOLD; ++j)
+      if (lane + 32 * j < n4) x[lane + 32 * j] = v[j];
+  }
+  float sq = 0.0f;
+#pragma unroll
+  for (int j = 0; j < HOLD; ++j)
+    if (lane + 32 * j < n4) {
+      sq += v[j].x * v[j].x;
+      sq += v[j].y * v[j].y;
+      sq += v[j].z * v[j].z;
+      sq += v[j].w * v[j].w;
+    }
+  const float scale = 1.0f / sqrtf(warp_sum(sq) / (float)hidden + eps);
+  if (out) {
+    uint2* dst = reinterpret_cast<uint2*>(out + (long long)r * hidden);
+#pragma unroll
+    for (int j = 0; j < HOLD; ++j)
+      if (lane + 32 * j < n4) {
+        const uint2 wraw = reinterpret_cast<const uint2*>(weight)[lane + 32 * j];
+        const __nv_bfloat162 w01 = *reinterpret_cast<const __nv_bfloat162*>(&wraw.x);
+        const __nv_bfloat162 w23 = *reinterpret_cast<const __nv_bfloat162*>(&wraw.y);
+        const __nv_bfloat162 o01 = __floats2bfloat162_rn(v[j].x * scale * __low2float(w01), v[j].y * scale * __high2float(w01));
+        const __nv_bfloat162 o23 = __floats2bfloat162_rn(v[j].z * scale * __low2float(w23), v[j].w * scale * __high2float(w23));
+        uint2 o;
+        o.x = *reinterpret_cast<const uint32_t*>(&o01);
+        o.y = *reinterpret_cast<const uint32_t*>(&o23);
+        dst[lane + 32 * j] = o;
+      }
+  }
+}
+
 template <typename TD, typename TW>
 static int add_rmsnorm_out(float* residual, const void* delta, int n_partials,
                            long long partial_stride, const void* weight, void* out, int out_dtype,
@@ -176,6 +245,16 @@ extern "C" int llm_add_rmsnorm(float* residual, const void* delta, int delta_dty
       (partial_stride % 4 == 0) && (reinterpret_cast<uintptr_t>(weight) & 7) == 0 &&
       (reinterpret_cast<uintptr_t>(out) & 7) == 0) {
     const int n4 = hidden / 4;
+    if (rows >= 64 && n4 <= 32 * 32) {   // many rows: a warp per row
+      const int blocks = (rows + 7) / 8;
+      if (n4 <= 32 * 16)
+        launch_kernel(add_rmsnorm_rows_kernel<16>, blocks, 256, 0, stream, residual, (const float*)delta, n_partials,
+                      partial_stride, (const __nv_bfloat16*)weight, (__nv_bfloat16*)out, row_index, rows, hidden, eps);
+      else
+        launch_kernel(add_rmsnorm_rows_kernel<32>, blocks, 256, 0, stream, residual, (const float*)delta, n_partials,
+                      partial_stride, (const __nv_bfloat16*)weight, (__nv_bfloat16*)out, row_index, rows, hidden, eps);
+      return launch_status();
+    }
     int threads = 128;
     while (threads < 1024 && threads * 2 <= n4) threads *= 2;   // <= 2 float4 per thread when wide
     while (threads * 4 < n4) threads *= 2;

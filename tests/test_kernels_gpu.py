@@ -62,6 +62,32 @@ def test_add_rmsnorm(hidden, out_dtype):
     _close(out2, want[index.long()], 1e-5, 1e-5)
 
 
+@pytest.mark.parametrize("rows,hidden,partials", [(7, 2048, 1), (70, 2048, 2), (300, 352, 1), (65, 4096, 3), (129, 5120, 1)])
+def test_add_rmsnorm_bfloat16_paths(rows, hidden, partials):
+    """The bfloat16 step's variants (bfloat16 weight and output): a block per row for few rows, a
+    warp per row for many (rows kept in registers, widths up to 4,096), with partial results to
+    add, with gathered rows and without anything to add."""
+    from bare_cuda_4gib_b200.kernels import lib as K
+    eps = 1e-5
+    torch.manual_seed(rows + hidden)
+    x = torch.randn(rows + 3, hidden, device=DEV)
+    delta = torch.randn(partials, rows + 3, hidden, device=DEV)
+    w = (1 + 0.1 * torch.randn(hidden, device=DEV)).to(torch.bfloat16)
+    res = x.clone()
+    out = torch.empty(rows, hidden, device=DEV, dtype=torch.bfloat16)
+    K.add_rmsnorm(res, K.Partials(delta, partials) if partials > 1 else K.Partials(delta[0]), w, out, eps, rows)
+    want_res = x.double()
+    want_res[:rows] += delta.double().sum(0)[:rows]
+    want = want_res * torch.rsqrt(want_res.pow(2).mean(-1, keepdim=True) + eps) * w.double()
+    _close(res, want_res, 1e-6, 1e-6)           # the rows beyond `rows` are untouched
+    _close(out, want[:rows], 2 ** -8, 1e-5)
+    index = torch.randperm(rows + 3, device=DEV)[:rows].to(torch.int32)
+    out2 = torch.empty(rows, hidden, device=DEV, dtype=torch.bfloat16)
+    K.add_rmsnorm(res, None, w, out2, eps, rows, index)
+    _close(out2, want[index.long()], 2 ** -8, 1e-5)
+    _close(res, want_res, 1e-6, 1e-6)           # nothing to add: the stream is only read
+
+
 @pytest.mark.parametrize("m,n,k", [(1, 70, 300), (17, 130, 64), (150, 64, 176), (5, 258, 96)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_matmul_plain(m, n, k, dtype):
