@@ -6,7 +6,10 @@
 // The order in which any output element's sum is formed depends only on the operation's own
 // sizes (hidden width, head size, absolute key position), never on how many rows a launch
 // carries or where a row sits in the batch: cutting the same tokens into other steps gives the
-// same bits.
+// same bits.  (This holds for the float32 kernels.  The vector variants that only bfloat16 steps
+// use - the norm for few and for many rows, the rotation for many tokens - pick their shape from
+// the number of rows, so there a row's sum may be formed in another order in another step; the
+// difference is float32 rounding under a bfloat16 result.)
 //
 // Formulas follow cuongvng/bare-cuda-4gib: embedding (engine/kernels/embedding_lookup.cu:22-30),
 // RMSNorm (engine/kernels/rmsnorm.cu:26-40), matmul against [out, in] weights
@@ -245,7 +248,7 @@ extern "C" int llm_add_rmsnorm(float* residual, const void* delta, int delta_dty
       (partial_stride % 4 == 0) && (reinterpret_cast<uintptr_t>(weight) & 7) == 0 &&
       (reinterpret_cast<uintptr_t>(out) & 7) == 0) {
     const int n4 = hidden / 4;
-    if (rows >= 64 && n4 <= 32 * 32) {   // many rows: a warp per row
+    if (rows >= 256 && n4 <= 32 * 32) {   // many rows (enough warps to fill the GPU): a warp per row
       const int blocks = (rows + 7) / 8;
       if (n4 <= 32 * 16)
         launch_kernel(add_rmsnorm_rows_kernel<16>, blocks, 256, 0, stream, residual, (const float*)delta, n_partials,

@@ -62,7 +62,7 @@ def test_add_rmsnorm(hidden, out_dtype):
     _close(out2, want[index.long()], 1e-5, 1e-5)
 
 
-@pytest.mark.parametrize("rows,hidden,partials", [(7, 2048, 1), (70, 2048, 2), (300, 352, 1), (65, 4096, 3), (129, 5120, 1)])
+@pytest.mark.parametrize("rows,hidden,partials", [(7, 2048, 1), (70, 2048, 2), (300, 352, 1), (257, 4096, 3), (260, 2048, 2), (300, 5120, 1)])
 def test_add_rmsnorm_bfloat16_paths(rows, hidden, partials):
     """The bfloat16 step's variants (bfloat16 weight and output): a block per row for few rows, a
     warp per row for many (rows kept in registers, widths up to 4,096), with partial results to
