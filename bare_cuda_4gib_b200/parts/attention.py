@@ -80,8 +80,17 @@ class Attention(Part):
         qkv_dtype = torch.float32 if n <= 256 else ctx.dtype
         q = ctx.ws.get("q", (n, qd), ctx.dtype)
         inv_freq = self.position.fused_rotation()
-        rotate = K.RotateAndCache(q, call.cache, ctx.positions, ctx.row_seq, inv_freq, self.heads, call.writes_cache)
-        qkv = self.qkv.forward(ctx, h, n, qkv_dtype, "qkv", allow_partials=True, epilogue=rotate)
+        apply = getattr(self.position, "apply", None)
+        if apply is not None:
+            # a position encoding with kernels of its own: it changes q and k in place, as [tokens, heads,
+            # head_dim] views of the finished projection, before k and v go into the cache
+            qkv = self.qkv.forward(ctx, h, n, ctx.dtype, "qkv")
+            kvd = self.kv_heads * self.head_dim
+            apply(ctx, qkv.tensor[:, :qd].unflatten(1, (self.heads, self.head_dim)),
+                  qkv.tensor[:, qd: qd + kvd].unflatten(1, (self.kv_heads, self.head_dim)))
+        else:
+            rotate = K.RotateAndCache(q, call.cache, ctx.positions, ctx.row_seq, inv_freq, self.heads, call.writes_cache)
+            qkv = self.qkv.forward(ctx, h, n, qkv_dtype, "qkv", allow_partials=True, epilogue=rotate)
         if qkv is not None:
             K.rope_cache_write(qkv, q, call.cache, ctx.positions, ctx.row_seq, inv_freq, self.heads,
                                call.writes_cache, n, ctx.stream)

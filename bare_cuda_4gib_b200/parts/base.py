@@ -8,8 +8,11 @@ Families and the one method each must have besides `weight_specs` / `bind`:
                 it may return a `LazyNorm` (see kernels.lib) instead, which the consumer either
                 hands to a `Linear` or turns into a matrix with `materialize()`; the block asks
                 for that only of consumers that declare `takes_lazy_input = True`.
-* position      either `fused_rotation()` -> float32 inverse frequencies [head_dim / 2] that the
-                attention kernels apply themselves, or `apply(ctx, q, k)` on separate tensors.
+* position      `fused_rotation()` -> float32 inverse frequencies [head_dim / 2] that the attention
+                kernels apply themselves (rotate_half pairing), or None; a part that also defines
+                `apply(ctx, q, k)` gets q [tokens, heads, head_dim] and k [tokens, kv_heads,
+                head_dim] as views of the finished projection and changes them in place (row t is
+                at position `ctx.positions[t]`) before k and v are written to the cache.
 * mixer         `forward(ctx, call, h) -> Partials` (the mixer's contribution to the residual), or
                 None if it has added the contribution into `ctx.residual` itself;
                 `cache_request()` -> `KVCacheRequest` or None; `state_request()` ->

@@ -290,3 +290,114 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
     assert sc == sa
     again = runner.step([StepEntry(sc, a, list(range(30)))]).float().cpu()
     assert H.row_error(again[29], want_a[29]) < 2e-5
+
+
+def test_toy_position_encoding_and_routed_feed_forward_are_registered_built_and_stepped():
+    """Two more toy parts defined here, with no change to the framework's files: a position
+    encoding with a step of its own (it scales q by a function of the position and shifts k along a
+    learned direction, instead of rotating), and a feed-forward that routes every token to one of two
+    small experts.  Layer 0 uses both, layer 1 is the plain Llama layer; whole prompts and cut ones
+    against the same model written out plainly."""
+    import bare_cuda_4gib_b200.models  # noqa: F401
+    from bare_cuda_4gib_b200.config import LlamaConfig
+    from bare_cuda_4gib_b200.engine.model import expected_weights
+    from bare_cuda_4gib_b200.engine.step import StepEntry
+    from bare_cuda_4gib_b200.kernels.lib import Partials
+    from bare_cuda_4gib_b200.models.llama import llama_spec
+    from bare_cuda_4gib_b200.parts import Part, PartSpec, register_feed_forward, register_position
+    from bare_cuda_4gib_b200.weights import random_tensors
+
+    @register_position("toy_scale_and_shift")
+    class ScaleAndShift(Part):
+        def local_weights(self):
+            return {"direction": ((self.params["head_dim"],), "norm")}
+
+        def fused_rotation(self):
+            return None                       # the attention kernels rotate nothing
+
+        def apply(self, ctx, q, k):
+            pos = ctx.positions[: q.shape[0]].to(torch.float32)
+            q.mul_((1.0 / (1.0 + self.params["rate"] * pos)).to(q.dtype)[:, None, None])
+            k.add_((torch.sin(pos)[:, None, None] * self.tensors["direction"].float()[None, None, :]).to(k.dtype))
+
+    @register_feed_forward("toy_two_experts")
+    class TwoExperts(Part):
+        def local_weights(self):
+            h, i = self.params["hidden"], self.params["inner"]
+            return {"router": ((2, h), "matrix"), "w_in": ((2 * i, h), "matrix"), "w_out": ((2 * h, i), "matrix")}
+
+        def forward(self, ctx, h):
+            hf = h.float()
+            i, hidden = self.params["inner"], self.params["hidden"]
+            choice = (hf @ self.tensors["router"].float().t()).argmax(-1)          # float32 router logits, top 1
+            outs = []
+            for e in range(2):
+                w_in = self.tensors["w_in"].float()[e * i: (e + 1) * i]
+                w_out = self.tensors["w_out"].float()[e * hidden: (e + 1) * hidden]
+                outs.append(torch.relu(hf @ w_in.t()) @ w_out.t())
+            return Partials(torch.where((choice == 0)[:, None], outs[0], outs[1]).contiguous())
+
+    cfg = LlamaConfig.from_dict(H.TINY_A)
+    spec = llama_spec(cfg)
+    rate, inner = 0.05, 40
+    spec.layers[0].mixer.params["position"] = PartSpec("toy_scale_and_shift", {"head_dim": cfg.head_dim, "rate": rate},
+                                                       {"direction": "model.layers.0.toy.direction"})
+    spec.layers[0].ffn = PartSpec("toy_two_experts", {"hidden": cfg.hidden_size, "inner": inner},
+                                  {"router": "model.layers.0.toy.router", "w_in": "model.layers.0.toy.w_in",
+                                   "w_out": "model.layers.0.toy.w_out"})
+    expected, model = expected_weights(spec)
+    assert "model.layers.0.toy.router" in expected and "model.layers.0.mlp.gate_proj.weight" not in expected
+    tensors = {k: v.to("cuda", torch.float32) for k, v in random_tensors(expected, seed=9).items()}
+    tensors["model.layers.0.toy.router"] *= 30.0        # clear choices: no token sits on the fence between experts
+    model.bind(tensors, torch.float32, "cuda")
+    runner, cache = _runner(model, 16, 64)
+
+    t64 = {k: v.double().cpu() for k, v in tensors.items()}
+    plain = pl.PlainModel(cfg.vocab_size, cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads,
+                          cfg.head_dim, cfg.intermediate_size, cfg.rope_theta, cfg.rms_norm_eps,
+                          t64["model.embed_tokens.weight"], t64["model.norm.weight"], t64["lm_head.weight"])
+    g0 = lambda n: t64["model.layers.0." + n]
+    g1 = lambda n: t64["model.layers.1." + n]
+    l1 = pl.PlainLayer(g1("input_layernorm.weight"), g1("self_attn.q_proj.weight"), g1("self_attn.k_proj.weight"),
+                       g1("self_attn.v_proj.weight"), g1("self_attn.o_proj.weight"), g1("post_attention_layernorm.weight"),
+                       g1("mlp.gate_proj.weight"), g1("mlp.up_proj.weight"), g1("mlp.down_proj.weight"))
+
+    def plain_forward(ids):
+        n, nh, nkv, d = len(ids), cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        pos = torch.arange(n, dtype=F64)
+        x = pl.embedding(plain.embed, torch.tensor(ids))
+        h = pl.rms_norm(x, g0("input_layernorm.weight"), plain.rms_norm_eps)
+        q = pl.linear(h, g0("self_attn.q_proj.weight")).view(n, nh, d)
+        k = pl.linear(h, g0("self_attn.k_proj.weight")).view(n, nkv, d)
+        v = pl.linear(h, g0("self_attn.v_proj.weight")).view(n, nkv, d)
+        q = q / (1.0 + rate * pos.float().double())[:, None, None]
+        k = k + torch.sin(pos.float()).double()[:, None, None] * g0("toy.direction")[None, None, :]
+        probs = torch.softmax(pl.attention_scores(q, k), dim=-1)
+        x = x + pl.linear(pl.attention_values(probs, v).reshape(n, nh * d), g0("self_attn.o_proj.weight"))
+        h = pl.rms_norm(x, g0("post_attention_layernorm.weight"), plain.rms_norm_eps)
+        choice = (h @ g0("toy.router").t()).argmax(-1)
+        outs = [torch.relu(h @ g0("toy.w_in")[e * inner: (e + 1) * inner].t())
+                @ g0("toy.w_out")[e * cfg.hidden_size: (e + 1) * cfg.hidden_size].t() for e in range(2)]
+        x = x + torch.where((choice == 0)[:, None], outs[0], outs[1])
+        x, _ = pl.decoder_block(plain, l1, x, torch.arange(n))
+        return pl.output_head(plain, x), choice
+
+    rng = random.Random(4)
+    a, b = H.random_ids(rng, 33, cfg.vocab_size), H.random_ids(rng, 18, cfg.vocab_size)
+    (want_a, choice_a), (want_b, _) = plain_forward(a), plain_forward(b)
+    assert 0 < int(choice_a.sum()) < len(a), "both experts must be used"
+    sa, sb = cache.acquire_slot(), cache.acquire_slot()
+    got_a = [runner.step([StepEntry(sa, a[:7], list(range(7)))]).float().cpu().clone()]
+    mix = runner.step([StepEntry(sb, b[:16], list(range(16))), StepEntry(sa, a[7:9], [0, 1])]).float().cpu().clone()
+    got_b, got_a = [mix[:16]], got_a + [mix[16:]]
+    for p in range(9, 33):                      # request a goes on token by token beside the rest of b
+        entries = [StepEntry(sa, [a[p]], [0])] + ([StepEntry(sb, b[16:], [0, 1])] if p == 9 else [])
+        out = runner.step(entries).float().cpu().clone()
+        got_a.append(out[:1])
+        if p == 9:
+            got_b.append(out[1:])
+    got_a, got_b = torch.cat(got_a), torch.cat(got_b)
+    for p in range(33):
+        assert H.row_error(got_a[p], want_a[p]) < 2e-5, p
+    for p in range(18):
+        assert H.row_error(got_b[p], want_b[p]) < 2e-5, p
