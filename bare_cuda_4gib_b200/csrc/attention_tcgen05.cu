@@ -250,7 +250,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
   const uint32_t tmem_base = *tmem_slot;
 
   // ---- what this block works on (uniform across the block)
-  const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;   // later tiles see more keys: first
+  // blocks are handed out with x fastest: all key/value heads of the latest tile first (it sees
+  // the most keys), then of the tile before it, ... so the longest blocks of the whole grid start first
+  const int tile = gridDim.y - 1 - blockIdx.y, kvh = blockIdx.x;
   const int seq = a.tile_seq[tile];
   int n_kb = 0, kb_lo = 0;
   int q_start = 0, q_len = 0, kv_len = 0, row0 = 0, n_rows = 0, pos0 = 0, group = 1;
@@ -666,7 +668,8 @@ extern "C" int llm_attention_tcgen05(const void* pool_map, const void* pool_base
   a.scale_log2 = scale * 1.4426950408889634f;
   a.window = window;
   a.error_word = error_word;
-  dim3 grid(n_tiles, kv_heads);
+  if (n_tiles > 65535) return ERR_BAD_SIZE;
+  dim3 grid(kv_heads, n_tiles);
   launch_kernel(attention_tcgen05_kernel, grid, NUM_THREADS, SMEM_BYTES, stream, map, a);
   return launch_status();
 }
