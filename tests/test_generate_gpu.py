@@ -199,3 +199,52 @@ def test_stop_ids_and_lengths_while_running_ahead(dtype):
         assert got[i] == alone[i] and finish[i] == "length"
     assert engine.cache.free_slots == 4 and all(g.pool.pages_in_use == 0 for g in engine.cache.groups)
     engine.cache.check_consistency()
+
+
+@pytest.mark.parametrize("policy", ["reserve", "on_demand"])
+def test_many_random_requests_match_their_solo_runs(policy):
+    """Forty requests of random lengths, stop ids and arrival times through a small engine (four
+    slots, few pages, so admission blocks and, on demand, requests are preempted and recomputed; the
+    scheduler runs ahead whenever it can): float32, so every request must produce exactly the tokens
+    of the plain greedy decode, cut at its stop id or length."""
+    from bare_cuda_4gib_b200.engine.engine import LLMEngine
+    from bare_cuda_4gib_b200.engine.scheduler import Request
+
+    folder, page = H.model_folder("A"), H.TINY["A"][1]
+    vocab = H.TINY["A"][0]["vocab_size"]
+    model = H.plain_model(folder)
+    rng = random.Random(77 if policy == "reserve" else 78)
+    engine = LLMEngine(folder, max_tokens=96, max_seqs=4, kv_pages=8, dtype="float32", page_tokens=page,
+                       max_step_tokens=24, policy=policy)
+    requests, expected = [], {}
+    for i in range(40):
+        prompt = H.random_ids(rng, rng.randrange(1, 40), vocab)
+        new = rng.randrange(1, 30)
+        full = pl.greedy_decode(model, prompt, new)
+        stop = []
+        if rng.random() < 0.4 and new > 3:
+            stop = [full[rng.randrange(1, new)]]
+            full = full[: min(i for i, t in enumerate(full) if t in stop) + 1]
+        requests.append(Request(id=i, prompt=prompt, max_new_tokens=new, stop_ids=stop))
+        expected[i] = full
+    sched = engine.scheduler
+    got = {i: [] for i in range(40)}
+    done = set()
+    pending = list(requests)
+    while pending or not sched.idle:
+        for _ in range(rng.randrange(0, 3)):           # requests arrive while others run
+            if pending:
+                sched.submit(pending.pop(0))
+        for e in sched.step():
+            if e.token >= 0:
+                got[e.id].append(e.token)
+            if e.finish:
+                assert e.finish in ("stop", "length") and e.id not in done
+                done.add(e.id)
+    assert done == set(range(40))
+    for i in range(40):
+        assert got[i] == expected[i], (i, got[i], expected[i])
+    assert engine.cache.free_slots == 4 and all(g.pool.pages_in_use == 0 for g in engine.cache.groups)
+    engine.cache.check_consistency()
+    if policy == "on_demand":
+        assert sched.stats().preemptions > 0, "the pool was never short: the test does not reach preemption"
