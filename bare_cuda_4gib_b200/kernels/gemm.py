@@ -126,6 +126,10 @@ def choose_splits(rows: int, n: int, k: int, bn: int) -> int:
 
 
 TOKENS_ON_ROWS_ABOVE = 256    # steps with more rows put 128 tokens on the MMA rows (orientation 1)
+# The SwiGLU product changes over earlier: with the weights on the MMA rows a block holds only 64
+# outputs, so from about a hundred tokens on the other orientation's wider tiles measured faster
+# (TinyLlama's feed-forward at 128 / 256 tokens: 16 / 19 us against 23 / 48 us).
+SWIGLU_TOKENS_ON_ROWS_ABOVE = 96
 N_SMS = 148
 
 
@@ -166,7 +170,7 @@ def run(ctx, plan: GemmPlan, a: torch.Tensor, rows: int, out_dtype: torch.dtype,
     err = error_word(a.device)
     l = lib()
     code = DT_BF16 if out_dtype == torch.bfloat16 else DT_F32
-    if rows > TOKENS_ON_ROWS_ABOVE:
+    if rows > (SWIGLU_TOKENS_ON_ROWS_ABOVE if swiglu else TOKENS_ON_ROWS_ABOVE):
         n_out = plan.n // 2 if swiglu else plan.n
         bn = feature_tile(rows, n_out, swiglu)
         fused_add = (add_to is not None and not swiglu and out_dtype == torch.float32 and add_to.dtype == torch.float32

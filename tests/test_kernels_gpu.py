@@ -292,7 +292,8 @@ def test_gemm_tcgen05_adds_into_the_residual(m, n, k, bn, monkeypatch):
 
 
 @pytest.mark.parametrize("m,inter,k", [(3, 176, 64), (40, 5632, 256), (130, 256, 96), (300, 200, 128), (9, 2816, 512),
-                                       (700, 176, 64), (2048, 5632, 128), (257, 1000, 96)])
+                                       (700, 176, 64), (2048, 5632, 128), (257, 1000, 96), (90, 1408, 128), (100, 5632, 128),
+                                       (200, 1000, 96), (256, 2816, 320)])
 def test_gemm_tcgen05_swiglu(m, inter, k):
     from bare_cuda_4gib_b200.kernels import gemm
     torch.manual_seed(m)
