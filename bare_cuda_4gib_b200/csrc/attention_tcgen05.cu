@@ -9,10 +9,10 @@
 // blocks of 128 positions:
 //   loader warp    one thread copies the block's keys and values from the request's pages into
 //                  128-byte-swizzled shared memory with TMA (one tensor map over the cache group's
-//                  whole pool, a box per page piece; four stages, two for head size 128); Q is staged
-//                  once with cp.async;
+//                  whole pool, a box per page piece; four stages, two for head size 128);
 //   MMA thread     S = Q K^T (M 128, N 128, K head size) into tensor memory columns [0, 128);
-//   softmax warps  two groups of four warps; group g takes the key blocks j with j % 2 == g and
+//   softmax warps  first stage Q with cp.async (all 256 threads, a few chunks each).  Then
+//                  two groups of four warps; group g takes the key blocks j with j % 2 == g and
 //                  keeps a running softmax of its own.  One thread per row: read the row of S from
 //                  tensor memory, scale, mask, running maximum and sum in float32 (base 2), write
 //                  P as bfloat16 into swizzled shared memory (the A operand of the second product);
@@ -54,7 +54,6 @@ constexpr int NUM_THREADS = SOFTMAX_THREADS + 32 + LOADER_THREADS;   // warps 0-
 constexpr int TMEM_COLS = 512;
 constexpr int O_COL = 256;       // first tensor-memory column of the P V results (S buffers at 0 and 128)
 constexpr int GROUP_THREADS = 128;
-constexpr int DH = D / 2;        // output channels per thread in the final merge
 constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;
 constexpr size_t SMEM_BYTES = Q_BYTES + STAGES * KV_BYTES + 2 * P_BYTES + 192;   // 17 barriers + 2 words
 static_assert((size_t)STAGES * KV_BYTES + 2 * P_BYTES >= (size_t)2 * 128 * (D + 2) * 4, "the merge area reuses the stages");
@@ -166,7 +165,10 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // -DATTN_TRACE: thread block (0, 0) records SM clock stamps per role and key block into
 // `trace` ([role][block], 64 blocks per role); a development aid, absent from normal builds.
 #ifdef ATTN_TRACE
-#define TRACE(role, j) do { if (blockIdx.x == 0 && blockIdx.y == 0 && a.trace && (j) < 64) a.trace[(role) * 64 + (j)] = clock64(); } while (0)
+#ifndef TRACE_BY
+#define TRACE_BY 0
+#endif
+#define TRACE(role, j) do { if (blockIdx.x == 0 && blockIdx.y == TRACE_BY && a.trace && (j) < 64) a.trace[(role) * 64 + (j)] = clock64(); } while (0)
 #else
 #define TRACE(role, j) do { } while (0)
 #endif
@@ -200,7 +202,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
   uint8_t* kv_smem = q_smem + Q_BYTES;              // [STAGES][keys: KA sub-tiles | values: KA sub-tiles]
   uint8_t* p_smem = kv_smem + STAGES * KV_BYTES;    // [2][two sub-tiles of 64 keys]
   uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + 2 * P_BYTES);
-  uint64_t* q_full = bars;                // loaders -> MMA: Q staged
+  uint64_t* q_full = bars;                // softmax threads -> MMA: Q staged
   uint64_t* kv_full = bars + 1;           // [STAGES] loaders -> MMA
   uint64_t* kv_empty = kv_full + STAGES;  // [STAGES] MMA (commit) -> loaders
   uint64_t* s_full = kv_empty + STAGES;   // [2] MMA (commit) -> softmax, per S buffer
@@ -215,13 +217,40 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) TRACE(11, 0);
   if (smem_u32(smem) & 1023) {   // never seen; refuse rather than compute with a broken layout
     if (threadIdx.x == 0) atomicCAS(a.error_word, 0, ERR_LAYOUT);
     return;
   }
+  // ---- what this block works on (uniform across the block).  The tile list and the requests'
+  // lengths are written by the host before the step's first kernel, so they may be read ahead of
+  // pdl_wait(); their latency then hides behind the barrier set-up and the tensor-memory allocation.
+  // blocks are handed out with x fastest: all key/value heads of the latest tile first (it sees
+  // the most keys), then of the tile before it, ... so the longest blocks of the whole grid start first
+  const int tile = gridDim.y - 1 - blockIdx.y, kvh = blockIdx.x;
+  const int seq = a.tile_seq[tile];
+  int n_kb = 0, kb_lo = 0;
+  int q_start = 0, q_len = 0, kv_len = 0, row0 = 0, n_rows = 0, pos0 = 0, group = 1;
+  int tile_min_pos = 0, tile_max_pos = 0;
+  if (seq >= 0) {
+    group = a.q_heads / a.cache.kv_heads;
+    q_start = a.seq_q_start[seq];
+    q_len = a.seq_q_len[seq];
+    kv_len = a.seq_kv_len[seq];
+    row0 = a.tile_index[tile] * BM;
+    n_rows = q_len * group;
+    pos0 = kv_len - q_len;
+    const int last_token = min(q_len - 1, (row0 + BM - 1) / group), first_token = row0 / group;
+    tile_min_pos = pos0 + first_token;
+    tile_max_pos = pos0 + last_token;
+    const int lo_key = a.window > 0 ? max(0, tile_min_pos - a.window + 1) : 0;
+    kb_lo = lo_key / BN;
+    n_kb = tile_max_pos / BN - kb_lo + 1;
+  }
+
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&pool_map)) : "memory");
-    mbar_init(q_full, LOADER_THREADS);
+    mbar_init(q_full, SOFTMAX_THREADS);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
@@ -248,47 +277,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
-
-  // ---- what this block works on (uniform across the block)
-  // blocks are handed out with x fastest: all key/value heads of the latest tile first (it sees
-  // the most keys), then of the tile before it, ... so the longest blocks of the whole grid start first
-  const int tile = gridDim.y - 1 - blockIdx.y, kvh = blockIdx.x;
-  const int seq = a.tile_seq[tile];
-  int n_kb = 0, kb_lo = 0;
-  int q_start = 0, q_len = 0, kv_len = 0, row0 = 0, n_rows = 0, pos0 = 0, group = 1;
-  int tile_min_pos = 0, tile_max_pos = 0;
-  if (seq >= 0) {
-    group = a.q_heads / a.cache.kv_heads;
-    q_start = a.seq_q_start[seq];
-    q_len = a.seq_q_len[seq];
-    kv_len = a.seq_kv_len[seq];
-    row0 = a.tile_index[tile] * BM;
-    n_rows = q_len * group;
-    pos0 = kv_len - q_len;
-    const int last_token = min(q_len - 1, (row0 + BM - 1) / group), first_token = row0 / group;
-    tile_min_pos = pos0 + first_token;
-    tile_max_pos = pos0 + last_token;
-    const int lo_key = a.window > 0 ? max(0, tile_min_pos - a.window + 1) : 0;
-    kb_lo = lo_key / BN;
-    n_kb = tile_max_pos / BN - kb_lo + 1;
-  }
+  if (threadIdx.x == 0) TRACE(11, 1);
 
   if (warp > MMA_WARP) {
     // ------------------------------------------------------------------ loader warp
-    const int lt = threadIdx.x - (SOFTMAX_THREADS + 32);
-    // Q: 128 rows x D, 16-byte chunks; rows past the request's packed rows are zero
-    for (int i = lt; i < BM * (D / 8); i += LOADER_THREADS) {
-      const int r = i / (D / 8), c = i % (D / 8);
-      const int R = row0 + r;
-      const bool valid = seq >= 0 && R < n_rows;
-      const int token = valid ? R / group : 0, head = valid ? kvh * group + R % group : 0;
-      const __nv_bfloat16* src = a.q + ((long long)(q_start + token) * a.q_heads + head) * D + c * 8;
-      cp_async16(smem_u32(q_smem) + (c >> 3) * SUB + swizzled(r, c & 7), src, valid);
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    mbar_arrive(q_full);
     // Keys and values: one TMA box per piece of a page (a page holds box_rows or more positions
     // of a key block).  A piece whose page is not held (given back by a window) is filled with
     // zeros by the warp instead; its keys are masked, but stale shared memory must not reach P V.
@@ -428,6 +420,22 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
     }
   } else {
     // ------------------------------------------------------------------ softmax: two groups, one thread per row
+    // Q: 128 rows x D in 16-byte chunks, staged by all softmax threads (a few chunks each, so one
+    // round of global latency; one warp alone took most of a short block's time over it); rows past
+    // the request's packed rows are zero
+    for (int i = threadIdx.x; i < BM * (D / 8); i += SOFTMAX_THREADS) {
+      const int qr = i / (D / 8), c = i % (D / 8);
+      const int QR = row0 + qr;
+      const bool valid = seq >= 0 && QR < n_rows;
+      const int token = valid ? QR / group : 0, head = valid ? kvh * group + QR % group : 0;
+      const __nv_bfloat16* src = a.q + ((long long)(q_start + token) * a.q_heads + head) * D + c * 8;
+      cp_async16(smem_u32(q_smem) + (c >> 3) * SUB + swizzled(qr, c & 7), src, valid);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    mbar_arrive(q_full);
+    if (threadIdx.x == 0) TRACE(11, 2);
     const int quad = warp & 3, g = warp >> 2;        // tensor-memory lanes 32 * quad ..; group g takes blocks j % 2 == g
     const int r = quad * 32 + lane;                  // row of the tile = tensor-memory lane
     const int R = row0 + r;
@@ -502,6 +510,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           mbar_arrive(&s_free[g]);
         }
+        // P(j) goes where P(j - 2) lay: the product that read it must be complete (its commit on
+        // o_full says so; O_block itself is added later, after P(j) is handed over).  Without this wait
+        // only the length of pass 1 kept the two apart.
+        if (h == 0 && last >= 0 && !mbar_wait(&o_full[g], (last >> 1) & 1, abort_flag)) ok = false;
         if (!all_visible) {
 #pragma unroll
           for (int i = 0; i < 64; ++i) {
@@ -540,41 +552,50 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
     }
     // ---- merge the two groups.  First everybody must be done with the stages (the MMAs that read
     // them have all completed once both groups have added their last O_block), then each thread
-    // parks (maximum, sum, O) of its row there, then each thread finishes half of its row.
-    float* park = reinterpret_cast<float*>(kv_smem);   // [2 groups][128 rows][D + 2]
+    // parks O of its row there as float4 units (unit i of row r in slot i ^ (r % units), so that the
+    // threads of a warp, who write the same unit of 32 rows, hit different banks) and (maximum, sum)
+    // behind them.  Then the threads take the units in order: a warp reads consecutive slots of a few
+    // rows and writes 256 contiguous bytes of the output (heads that share a key/value head lie side
+    // by side in a token's output row, as their rows do in the tile).
+    constexpr int UNITS = D / 4;                         // float4 units per row
+    float4* park = reinterpret_cast<float4*>(kv_smem);   // [2 groups][128 rows][UNITS]
+    float2* park_ml = reinterpret_cast<float2*>(park + 2 * 128 * UNITS);   // [2 groups][128 rows]
+    if (threadIdx.x == 0) TRACE(11, 3);
     mbar_arrive(done_bar);
     if (ok) ok = mbar_wait(done_bar, 0, abort_flag);
-    float* mine = park + ((size_t)g * 128 + r) * (D + 2);
-    mine[0] = m;
-    mine[1] = l;
+    float4* mine = park + ((size_t)g * 128 + r) * UNITS;
 #pragma unroll
-    for (int i = 0; i < D; ++i) mine[2 + i] = o[i];
+    for (int i = 0; i < UNITS; ++i) mine[i ^ (r & (UNITS - 1))] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+    park_ml[g * 128 + r] = make_float2(m, l);
+    if (threadIdx.x == 0) TRACE(11, 4);
     mbar_arrive(merge_bar);
     if (ok) ok = mbar_wait(merge_bar, 0, abort_flag);
-    if (ok && row_valid) {
-      const float* a0 = park + ((size_t)0 * 128 + r) * (D + 2);
-      const float* a1 = park + ((size_t)1 * 128 + r) * (D + 2);
-      const float m0 = a0[0], m1 = a1[0];
-      const float mm = fmaxf(m0, m1);
-      const float f0 = m0 == -INFINITY ? 0.0f : fast_exp2(m0 - mm), f1 = m1 == -INFINITY ? 0.0f : fast_exp2(m1 - mm);
-      const float total = a0[1] * f0 + a1[1] * f1;
-      const float inv = total > 0.0f ? 1.0f / total : 0.0f;
-      const int token = R / group, head = kvh * group + R % group;
-      uint4* dst = reinterpret_cast<uint4*>(a.out + ((long long)(q_start + token) * a.q_heads + head) * D + g * DH);
-      const float* x0 = a0 + 2 + g * DH;
-      const float* x1 = a1 + 2 + g * DH;
+    if (threadIdx.x == 0) TRACE(11, 5);
+    if (ok && seq >= 0) {
 #pragma unroll
-      for (int c = 0; c < DH / 8; ++c) {
-        float y[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) y[e] = (x0[8 * c + e] * f0 + x1[8 * c + e] * f1) * inv;
-        dst[c] = make_uint4(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]), pack_bf16(y[4], y[5]), pack_bf16(y[6], y[7]));
+      for (int q = threadIdx.x; q < BM * UNITS; q += SOFTMAX_THREADS) {
+        const int rr = q / UNITS, i = q % UNITS;
+        const int RR = row0 + rr;
+        if (RR >= n_rows) continue;
+        const float2 ml0 = park_ml[rr], ml1 = park_ml[128 + rr];
+        const float mm = fmaxf(ml0.x, ml1.x);
+        const float f0 = ml0.x == -INFINITY ? 0.0f : fast_exp2(ml0.x - mm), f1 = ml1.x == -INFINITY ? 0.0f : fast_exp2(ml1.x - mm);
+        const float total = ml0.y * f0 + ml1.y * f1;
+        const float inv = total > 0.0f ? 1.0f / total : 0.0f;
+        const float4 x0 = park[(size_t)rr * UNITS + (i ^ (rr & (UNITS - 1)))];
+        const float4 x1 = park[((size_t)128 + rr) * UNITS + (i ^ (rr & (UNITS - 1)))];
+        const int token = RR / group, head = kvh * group + RR % group;
+        uint2* dst = reinterpret_cast<uint2*>(a.out + ((long long)(q_start + token) * a.q_heads + head) * D + i * 4);
+        *dst = make_uint2(pack_bf16((x0.x * f0 + x1.x * f1) * inv, (x0.y * f0 + x1.y * f1) * inv),
+                          pack_bf16((x0.z * f0 + x1.z * f1) * inv, (x0.w * f0 + x1.w * f1) * inv));
       }
     }
   }
 
+  if (threadIdx.x == 0) TRACE(11, 6);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (threadIdx.x == 0) TRACE(11, 7);
   if (warp == MMA_WARP) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
