@@ -131,6 +131,26 @@ class LLMEngine:
                                   on_token=(lambda rid, i, t: on_token(i, t)) if on_token else None)
         return out[0]
 
+    def score(self, ids: Sequence[int]) -> torch.Tensor:
+        """Logits at every position of `ids` (float32 [len, vocab], on the host): one fresh request
+        fed in portions under the step's token budget, nothing sampled.  What the reference's tools
+        read with `forward` + `logits_host` (bench/src/ppl_main.cc:104-105, batch_check_main.cc:121-123)."""
+        if not self.scheduler.idle:
+            raise EngineError("score: the scheduler still holds requests")
+        ids = list(ids)
+        if not ids or len(ids) > self.max_tokens:
+            raise EngineError(f"score: {len(ids)} ids do not fit a cache of {self.max_tokens} tokens")
+        slot = self.cache.acquire_slot()
+        rows = []
+        try:
+            portion = max(1, self.max_step_tokens - 1)
+            for at in range(0, len(ids), portion):
+                piece = ids[at: at + portion]
+                rows.append(self.runner.step([StepEntry(slot, piece, list(range(len(piece))))]).float().cpu())
+        finally:
+            self.cache.release_slot(slot)
+        return torch.cat(rows, 0)
+
     def generate_batch(self, prompts: Sequence[Sequence[int]], new_tokens: int,
                        sampling: Optional[SamplingParams] = None, stop_ids: Sequence[int] = (),
                        on_token: Optional[Callable[[int, int, int], None]] = None) -> List[List[int]]:

@@ -1,5 +1,6 @@
 """The command line tools end to end on a tiny random model: `llm-infer` against the plain
-implementation's greedy decode, `llm-bench` and `llm-kernel-bench` for their tables."""
+implementation's greedy decode, `llm-bench` and `llm-kernel-bench` for their tables, `llm-ppl` against
+the plain implementation's perplexity, `llm-batch-check` and `llm-devinfo`."""
 
 import os
 import pathlib
@@ -60,3 +61,63 @@ def test_llm_kernel_bench_reports_a_roofline_fraction():
                "--iters", 3, "--warmup", 1)
     line = json.loads([l for l in out.splitlines() if l.startswith("{")][-1])
     assert line["us"] > 0 and 0 < line["hbm_frac"] < 1.5
+
+
+def _ids_file(name, n, vocab, seed):
+    import random
+
+    import numpy as np
+    path = H.tmp_root() / name
+    np.asarray(H.random_ids(random.Random(seed), n, vocab), dtype="<i4").tofile(path)
+    return path
+
+
+def test_llm_ppl_matches_the_plain_implementation():
+    import math
+
+    import torch
+    folder = H.model_folder("A")
+    ctx, windows, vocab = 33, 3, 256
+    ids_path = _ids_file("ppl.ids", 120, vocab, 5)
+    out = _run("llm-ppl", "--model", folder, "--ids", ids_path, "--ctx", ctx, "--windows", windows, "--dtype", "float32")
+    assert f"120 ids, {windows} windows of {ctx} (BOS + {ctx - 1}), {windows * (ctx - 1)} predictions" in out
+    import numpy as np
+    text = np.fromfile(ids_path, dtype="<i4").tolist()
+    nll = 0.0
+    for w in range(windows):
+        window = [1] + text[w * (ctx - 1): (w + 1) * (ctx - 1)]
+        logp = torch.log_softmax(H.plain_logits(folder, window).double(), dim=1)
+        nll -= float(sum(logp[t, window[t + 1]] for t in range(ctx - 1)))
+    want = math.exp(nll / (windows * (ctx - 1)))
+    got = float([l for l in out.splitlines() if l.startswith("perplexity")][0].split()[1])
+    assert abs(got - want) <= 2e-4 * want, (got, want)
+    assert f"tokens scored {windows * (ctx - 1)}" in out
+
+
+def test_llm_batch_check_passes_and_reports_every_prompt():
+    import torch
+
+    from bare_cuda_4gib_b200.models.presets import preset_config
+    from bare_cuda_4gib_b200.weights import write_random_model
+    folder = H.tmp_root() / "batch-check-model"
+    cfg = preset_config("tinyB", max_position_embeddings=512)
+    write_random_model(folder, cfg, 3, torch.bfloat16)
+    ids_path = _ids_file("check.ids", 600, cfg.vocab_size, 9)
+    for dtype in ("float32", "bfloat16"):
+        out = _run("llm-batch-check", "--model", folder, "--ids", ids_path, "--tokens", 9, "--batch", 3,
+                   "--spacing", 40, "--dtype", dtype)
+        assert "8 prompts of 6-301 tokens, 9 new tokens each, 3 decoding at once" in out
+        assert sum(line.startswith("prompt ") for line in out.splitlines()) == 8
+        assert "PASS: batched decode agrees with decoding alone" in out and "0 diverge" in out
+    short = subprocess.run([sys.executable, str(ROOT / "bin" / "llm-batch-check"), "--model", str(folder), "--ids",
+                            str(ids_path), "--tokens", "4"], capture_output=True, text=True, timeout=600)
+    assert short.returncode == 1 and "too few for prompt" in short.stderr
+
+
+def test_llm_devinfo_lines():
+    log = H.tmp_root() / "devinfo.log"
+    kv = _run("llm-devinfo", "--kv", "--out", log)
+    assert kv.startswith('name="') and " sms=" in kv and " free_post_mib=" in kv
+    assert log.read_text().strip().endswith(kv.strip())
+    long_form = _run("llm-devinfo")
+    assert "=> allocatable budget" in long_form and "SMs" in long_form

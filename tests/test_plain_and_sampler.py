@@ -94,3 +94,11 @@ def test_host_sampler_agrees_with_plain_kept_set_on_a_large_vocabulary():
     for u in (0.0, 0.3, 0.77, 0.999999):
         want = pl.inverse_cdf_pick([float(w[i]) for i in kept], kept, u)
         assert host_sample(logits, p, u) == want
+
+
+def test_perplexity_tool_scores_rows_like_log_softmax():
+    from bare_cuda_4gib_b200.cli.ppl import window_nll
+    torch.manual_seed(3)
+    rows, targets = torch.randn(7, 19) * 4, [0, 18, 5, 5, 9, 1, 12]
+    want = -float(sum(torch.log_softmax(rows.double(), 1)[i, t] for i, t in enumerate(targets)))
+    assert abs(window_nll(rows, targets) - want) < 1e-12
