@@ -194,6 +194,9 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap pool_map, const Deco
     pdl_wait();
     return;
   }
+  // Every block of the cluster reports that it runs; the wait for this phase stands before the
+  // first store into another block's shared memory, by when it has long completed.
+  if (n_splits > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
   const int group = a.q_heads / a.kv_heads;
   const int q_start = a.seq_q_start[seq], q_len = a.seq_q_len[seq], kv_len = a.seq_kv_len[seq];
   const int row0 = a.tile_index[tile] * BM;
@@ -419,6 +422,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap pool_map, const Deco
     }
   }
   __syncthreads();
+  if (n_splits > 1) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");   // all blocks of the cluster have started
   TRACE(8);
   // ---- this block's warps merged, per row and eight columns a thread; row r goes to block r % n_splits
   constexpr int STATE = D + 4;   // floats per row state: D sums (relative to m), then m and l (16-byte rows)
