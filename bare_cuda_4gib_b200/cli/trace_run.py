@@ -21,7 +21,6 @@ import json
 import pathlib
 import sys
 
-import numpy as np
 
 
 def main(argv=None) -> int:
@@ -41,7 +40,6 @@ def main(argv=None) -> int:
     from ..cache.manager import CacheManager
     from ..engine.model import load_model
     from ..engine.step import StepEntry, StepRunner
-    from ..errors import EngineError
 
     if not torch.cuda.is_available():
         print("trace_run: no CUDA device; the engine has no CPU path", file=sys.stderr)

@@ -14,7 +14,7 @@ from __future__ import annotations
 import json
 import math
 import pathlib
-from dataclasses import asdict, dataclass, field
+from dataclasses import asdict, dataclass
 from typing import Any, Dict, List, Optional
 
 from ..errors import ConfigError

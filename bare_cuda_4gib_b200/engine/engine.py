@@ -16,7 +16,6 @@ refuse new work.
 from __future__ import annotations
 
 import threading
-import time
 from collections import deque
 from typing import Callable, Dict, List, Optional, Sequence, Tuple
 

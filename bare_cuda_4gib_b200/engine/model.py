@@ -9,7 +9,6 @@ which parts to build and in which order layers run.
 
 from __future__ import annotations
 
-import pathlib
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -18,7 +17,7 @@ from ..cache.manager import CacheDemand
 from ..config.llama import read_config_json
 from ..config.registry import resolve_architecture
 from ..errors import ConfigError
-from ..parts.base import CallContext, Part
+from ..parts.base import Part
 from ..parts.registry import build_part, lookup
 from ..parts.spec import ModelSpec, WeightSpec
 from ..weights.loader import load_weights

@@ -14,7 +14,7 @@ from that block, so a step of the same padded shape can be replayed as a CUDA gr
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np

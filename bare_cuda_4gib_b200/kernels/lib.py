@@ -8,7 +8,6 @@ Nothing here computes on the CPU: without the compiled libraries the calls fail.
 
 from __future__ import annotations
 
-import ctypes
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 

@@ -9,7 +9,6 @@ part returns None.
 
 from __future__ import annotations
 
-from ..kernels import lib as K
 from .registry import build_part, register_block
 
 

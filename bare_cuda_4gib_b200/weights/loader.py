@@ -10,7 +10,7 @@ first: engine/src/model.cpp:24-32, engine/src/loader.cpp:142-148).
 from __future__ import annotations
 
 import pathlib
-from typing import Dict, List, Tuple
+from typing import Dict, Tuple
 
 import torch
 

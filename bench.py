@@ -28,7 +28,6 @@ from __future__ import annotations
 
 import argparse
 import json
-import os
 import pathlib
 import random
 import statistics
@@ -36,7 +35,6 @@ import subprocess
 import sys
 import tempfile
 import threading
-import time
 
 ROOT = pathlib.Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))

@@ -1,6 +1,5 @@
 """Shared fixtures: markers, the two tiny configurations and model folders with random weights."""
 
-import os
 import pathlib
 import sys
 

@@ -5,13 +5,11 @@ engine's own step function, and the comparison with the plain implementation."""
 from __future__ import annotations
 
 import functools
-import json
 import pathlib
 import random
 import tempfile
 from typing import Dict, List, Sequence, Tuple
 
-import numpy as np
 import torch
 
 import plain_llama as pl

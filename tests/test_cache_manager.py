@@ -4,7 +4,6 @@ random orders of requests; windows give pages back; state slots are zeroed."""
 import random
 
 import pytest
-import torch
 
 from bare_cuda_4gib_b200.cache import CacheDemand, CacheManager, PagePool
 from bare_cuda_4gib_b200.errors import CacheError, OutOfPages

@@ -193,7 +193,7 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
     state slot - is registered, put into one layer of a model beside attention layers, and stepped
     in portions and in a batch; the engine's files are not touched."""
     from bare_cuda_4gib_b200.config import LlamaConfig
-    from bare_cuda_4gib_b200.engine.model import expected_weights, Model
+    from bare_cuda_4gib_b200.engine.model import expected_weights
     from bare_cuda_4gib_b200.engine.step import StepEntry
     from bare_cuda_4gib_b200.kernels.lib import Partials
     from bare_cuda_4gib_b200.models.llama import llama_spec

@@ -1,6 +1,5 @@
 """The plain implementation's parts against each other and the host sampler's distributions (no GPU)."""
 
-import math
 import random
 
 import numpy as np
