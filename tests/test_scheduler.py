@@ -260,3 +260,44 @@ def test_running_ahead_stops_for_waiting_requests_deadlines_and_sampling():
     assert ex.fed_from_device >= 1
     assert s.cancel(1) and not s.idle                # a step is still in flight
     assert s.step() == [] and s.idle                 # its row is dropped
+
+
+@pytest.mark.parametrize("policy", ["reserve", "on_demand"])
+@pytest.mark.parametrize("asynchronous", [False, True])
+@pytest.mark.parametrize("seed", [0, 1, 2, 3])
+def test_random_arrivals_and_cancellations_lose_nothing(policy, asynchronous, seed):
+    """Requests of random lengths arrive between steps and some are cancelled: every request ends
+    exactly once, its tokens are those it would get alone, and slots and pages all come back."""
+    import random
+    rng = random.Random(seed)
+    maker = make_async if asynchronous else make
+    s, ex, cache = maker(pages=rng.choice([9, 14, 40]), max_seqs=rng.choice([2, 3, 4]), max_tokens=64,
+                         budget=rng.choice([6, 16, 40]), policy=policy)
+    todo = [(i, rng.randrange(1, 30), rng.randrange(1, 12)) for i in range(14)]
+    prompt_len = {i: p for i, p, _ in todo}
+    wanted = {i: n for i, _, n in todo}
+    events, cancelled, submitted = [], set(), set()
+    for _ in range(4000):
+        while todo and rng.random() < 0.4:
+            i, p, n = todo.pop(0)
+            s.submit(Request(i, [1] * p, n))
+            submitted.add(i)
+        if submitted - cancelled and rng.random() < 0.05:
+            victim = rng.choice(sorted(submitted - cancelled))
+            if s.cancel(victim):
+                cancelled.add(victim)
+        events += s.step()
+        if not todo and s.idle:
+            break
+    assert s.idle and not todo
+    for i in sorted(submitted):
+        mine = [e for e in events if e.id == i and e.token >= 0]
+        assert [e.index for e in mine] == list(range(len(mine)))
+        assert [e.token for e in mine] == [1000 + prompt_len[i] + k for k in range(len(mine))]
+        endings = [e.finish for e in events if e.id == i and e.finish]
+        if i in cancelled:
+            assert len(mine) <= wanted[i] and endings in ([], ["cancelled"])
+        else:
+            assert len(mine) == wanted[i] and endings == ["length"]
+    assert cache.free_slots == cache.max_seqs and cache.pages_in_use() == [0]
+    cache.check_consistency()
