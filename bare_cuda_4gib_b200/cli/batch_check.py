@@ -54,12 +54,17 @@ def main(argv=None) -> int:
     longest = max(len(p) for p in prompts)
 
     from ..engine.engine import LLMEngine
+    from ..errors import EngineError
     if args.random:
         from ..models.presets import preset_config
         from ..weights.random_init import write_random_model
         write_random_model(args.model, preset_config(args.random), 0)
-    engine = LLMEngine(args.model, max_tokens=longest + args.tokens, max_seqs=args.batch, dtype=args.dtype,
-                       page_tokens=args.page_tokens)
+    try:
+        engine = LLMEngine(args.model, max_tokens=longest + args.tokens, max_seqs=args.batch, dtype=args.dtype,
+                           page_tokens=args.page_tokens)
+    except EngineError as e:
+        print(f"[llm] {e}", file=sys.stderr)
+        return 1
     print(f"model      {args.model}")
     print(f"check      {len(prompts)} prompts of {len(prompts[0])}-{longest} tokens, {args.tokens} new tokens each, "
           f"{args.batch} decoding at once")

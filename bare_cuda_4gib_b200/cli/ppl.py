@@ -63,11 +63,16 @@ def main(argv=None) -> int:
         return 1
 
     from ..engine.engine import LLMEngine
+    from ..errors import EngineError
     if args.random:
         from ..models.presets import preset_config
         from ..weights.random_init import write_random_model
         write_random_model(args.model, preset_config(args.random), 0)
-    engine = LLMEngine(args.model, max_tokens=args.ctx, max_seqs=1, dtype=args.dtype, page_tokens=args.page_tokens)
+    try:
+        engine = LLMEngine(args.model, max_tokens=args.ctx, max_seqs=1, dtype=args.dtype, page_tokens=args.page_tokens)
+    except EngineError as e:
+        print(f"[llm] {e}", file=sys.stderr)
+        return 1
     vocab = engine.vocab_size
     bad = [t for t in text[: windows * stride] if not 0 <= t < vocab]
     if bad:
