@@ -12,8 +12,13 @@ with the same needs, and slots of fixed-size per-request state beside them.
   group with a window, first gives back the pages that every later query has moved past;
   `commit(slot, n)` moves the length once a step has written all layers; `release_slot` gives
   everything back (engine/src/kv_cache.cpp:52-71,131-149).
-* `StateSlots`: one tensor [slots, *shape] per run of a layer whose mixer asks for state, zeroed
-  when a request takes the slot.  Llama asks for none; the interface is whole regardless.
+* State slots: one tensor [slots + 1, *shape] per demand that asks for state, zeroed when a
+  request takes the slot.  The last row (`idle_slot`) belongs to no request: the idle rows that
+  pad a decode step to a fixed batch size point there, so a mixer that updates its state on the
+  device never touches a live request's state for them.  Llama asks for none; the interface is
+  whole regardless.
+* A run of a layer may state several demands (a block with two mixers, say): `demands[run]` is one
+  `CacheDemand` or a list of them, and caches and states are addressed by (run, index in that list).
 
 All bookkeeping is host-side and runs without a GPU (`device="cpu"` or storage disabled).
 """
@@ -34,7 +39,9 @@ from .page_pool import PagePool
 
 @dataclass
 class CacheDemand:
-    """What one entry of the run order wants: paged keys/values, state, or another run's cache."""
+    """What one part of one entry of the run order wants: paged keys/values, state, or (with
+    `cache_from`, the index of an earlier run) the cache and state of that run's part in the same
+    place."""
 
     kv: Optional[KVCacheRequest] = None
     state: Optional[StateRequest] = None
@@ -44,7 +51,7 @@ class CacheDemand:
 class CacheGroup:
     def __init__(self, request: KVCacheRequest, members: List[int], page_tokens: int, num_pages: int,
                  max_blocks: int, dtype: torch.dtype, device, allocate: bool):
-        self.request, self.members = request, members
+        self.request, self.members = request, members      # members: (run, index in the run's demands)
         self.page_tokens, self.num_pages, self.max_blocks = page_tokens, num_pages, max_blocks
         self.pool = PagePool(num_pages)
         self.tables: Dict[int, List[int]] = {}      # slot -> page per block (-1 = none)
@@ -93,37 +100,52 @@ class CacheManager:
         self.page_tokens, self.max_seqs, self.max_tokens = page_tokens, max_seqs, max_tokens
         self.max_blocks = -(-max_tokens // page_tokens)
         self.device, self.dtype = torch.device(device), dtype
-        self.demands = list(demands)
+        # per run a list of demands (most blocks state one: their mixer's)
+        self.demands: List[List[CacheDemand]] = [list(d) if isinstance(d, (list, tuple)) else [d] for d in demands]
         self.groups: List[CacheGroup] = []
-        self.cache_group: Dict[int, Tuple[int, int]] = {}    # run index -> (group, index in group)
-        by_request: Dict[KVCacheRequest, List[int]] = {}
-        for i, d in enumerate(self.demands):
-            if d.cache_from is not None:
-                if not (0 <= d.cache_from < i) or self.demands[d.cache_from].cache_from is not None:
-                    raise CacheError(f"run {i} reads the cache of run {d.cache_from}, which must be an "
-                                     "earlier run with a cache of its own")
-                continue
-            if d.kv is not None:
-                by_request.setdefault(d.kv, []).append(i)
+        self.cache_group: Dict[Tuple[int, int], Tuple[int, int]] = {}    # (run, j) -> (group, index in group)
+        by_request: Dict[KVCacheRequest, List[Tuple[int, int]]] = {}
+        for i, run in enumerate(self.demands):
+            for j, d in enumerate(run):
+                if d.cache_from is not None:
+                    src = d.cache_from
+                    if not (0 <= src < i) or j >= len(self.demands[src]) or self.demands[src][j].cache_from is not None:
+                        raise CacheError(f"run {i} reads the cache of run {src}, which must be an "
+                                         "earlier run with a cache of its own")
+                    continue
+                if d.kv is not None:
+                    by_request.setdefault(d.kv, []).append((i, j))
         for request, members in by_request.items():
             pages = num_pages if num_pages is not None else max_seqs * self.max_blocks
             g = CacheGroup(request, members, page_tokens, pages, self.max_blocks, dtype, self.device, allocate)
-            for j, run in enumerate(members):
-                self.cache_group[run] = (len(self.groups), j)
+            for at, key in enumerate(members):
+                self.cache_group[key] = (len(self.groups), at)
             self.groups.append(g)
-        for i, d in enumerate(self.demands):
-            if d.cache_from is not None and d.cache_from in self.cache_group:
-                self.cache_group[i] = self.cache_group[d.cache_from]
         self.lengths: Dict[int, int] = {}
         self._free_slots = list(range(max_seqs - 1, -1, -1))
-        self.states: Dict[int, torch.Tensor] = {}
-        for i, d in enumerate(self.demands):
-            if d.state is not None and d.cache_from is None:
-                self.states[i] = torch.zeros((max_seqs, *d.state.shape), dtype=d.state.dtype,
-                                             device=self.device if allocate else "cpu")
-        for i, d in enumerate(self.demands):
-            if d.cache_from is not None and d.cache_from in self.states:
-                self.states[i] = self.states[d.cache_from]
+        self.idle_slot = max_seqs          # a state row that no request owns (see the module's text)
+        self.states: Dict[Tuple[int, int], torch.Tensor] = {}
+        for i, run in enumerate(self.demands):
+            for j, d in enumerate(run):
+                if d.state is not None and d.cache_from is None:
+                    self.states[(i, j)] = torch.zeros((max_seqs + 1, *d.state.shape), dtype=d.state.dtype,
+                                                      device=self.device if allocate else "cpu")
+        for i, run in enumerate(self.demands):
+            for j, d in enumerate(run):
+                if d.cache_from is None:
+                    continue
+                if (d.cache_from, j) in self.cache_group:
+                    self.cache_group[(i, j)] = self.cache_group[(d.cache_from, j)]
+                if (d.cache_from, j) in self.states:
+                    self.states[(i, j)] = self.states[(d.cache_from, j)]
+
+    def group_of(self, run: int, j: int = 0) -> Optional[Tuple[int, int]]:
+        """(group, index in the group) of the cache that part `j` of run `run` reads, or None."""
+        return self.cache_group.get((run, j))
+
+    def state_of(self, run: int, j: int = 0) -> Optional[torch.Tensor]:
+        """[slots + 1, *shape] state of part `j` of run `run`, or None."""
+        return self.states.get((run, j))
 
     # ------------------------------------------------------------------ slots
     @property
@@ -137,8 +159,8 @@ class CacheManager:
         self.lengths[slot] = 0
         for g in self.groups:
             g.tables[slot] = []
-        for run, state in self.states.items():
-            if self.demands[run].cache_from is None:
+        for (run, j), state in self.states.items():
+            if self.demands[run][j].cache_from is None:
                 state[slot].zero_()
         return slot
 
@@ -225,11 +247,12 @@ class CacheManager:
             table = g.tables[slot]
             out[i, : len(table)] = table
 
-    def cache_view(self, run: int, block_table: torch.Tensor) -> Optional[CacheView]:
-        """The kernel-side description of the cache that run `run` reads (its own or a borrowed one)."""
-        if run not in self.cache_group:
+    def cache_view(self, run: int, block_table: torch.Tensor, j: int = 0) -> Optional[CacheView]:
+        """The kernel-side description of the cache that part `j` of run `run` reads (its own or a
+        borrowed one)."""
+        if (run, j) not in self.cache_group:
             return None
-        gi, j = self.cache_group[run]
+        gi, j = self.cache_group[(run, j)]
         g = self.groups[gi]
         if g.storage is None:
             return None

@@ -150,10 +150,6 @@ def bench_gemv(a):
     def run():
         w = weights[state["i"] % copies]
         state["i"] += 1
-        if getattr(a, "prefetch", False):       # as inside a step: each launch pulls the next launch's weights towards L2
-            nxt = weights[state["i"] % copies]
-            ctx.gemv_prev = [(w.data_ptr(), weight_bytes), (nxt.data_ptr(), weight_bytes)]
-            ctx.gemv_now = []
         x = K.LazyNorm(ctx, residual, norm_w, 1e-5, a.tokens, None, "normed", prenormed) if a.norm else x_plain
         gemv.run(ctx, w, x, a.tokens, torch.bfloat16 if a.form == "swiglu" else torch.float32, "out",
                  a.form == "swiglu", epilogue)
@@ -252,7 +248,6 @@ def main(argv=None) -> int:
     v.add_argument("--form", default="plain", choices=["plain", "add", "swiglu", "rope"])
     v.add_argument("--norm", action="store_true")
     v.add_argument("--prenormed", action="store_true", help="with --norm: the input prepared by the product before")
-    v.add_argument("--prefetch", action="store_true", help="each launch prefetches the next launch's weights into L2")
     v.add_argument("--kv-heads", type=int, default=4)
     v.add_argument("--head-dim", type=int, default=64)
     v.add_argument("--l2-mb", type=int, default=126)

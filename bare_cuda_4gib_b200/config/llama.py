@@ -11,9 +11,7 @@ is written anywhere else in the package.
 
 from __future__ import annotations
 
-import json
 import math
-import pathlib
 from dataclasses import asdict, dataclass
 from typing import Any, Dict, List, Optional
 
@@ -125,18 +123,3 @@ class LlamaConfig:
         if isinstance(self.eos_token_id, (list, tuple)):
             return [int(t) for t in self.eos_token_id]
         return [int(self.eos_token_id)]
-
-
-def read_config_json(folder) -> Dict[str, Any]:
-    path = pathlib.Path(folder) / "config.json"
-    try:
-        text = path.read_text()
-    except OSError as e:
-        raise ConfigError(f"cannot read {path}: {e}") from e
-    try:
-        d = json.loads(text)
-    except json.JSONDecodeError as e:
-        raise ConfigError(f"{path} is not valid JSON: {e}") from e
-    if not isinstance(d, dict):
-        raise ConfigError(f"{path} must hold a JSON object")
-    return d

@@ -131,14 +131,6 @@ __device__ __forceinline__ uint32_t peer_smem(uint32_t local, uint32_t rank) {
 // the 128-byte swizzle (the tile starts on a 1024-byte boundary).
 __device__ __forceinline__ uint32_t swizzled(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
 
-// -DDECODE_TRACE: thread 0 of block (0, 0, 0) records SM clock stamps of the kernel's phases into
-// a buffer set with llm_attention_decode_set_trace; a development aid, absent from normal builds.
-#ifdef DECODE_TRACE
-__device__ long long* g_trace = nullptr;
-#define TRACE(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0 && g_trace) g_trace[i] = clock64(); } while (0)
-#else
-#define TRACE(i) do { } while (0)
-#endif
 
 struct DecodeArgs {
   const __nv_bfloat16* q;      // [tokens, q_heads, D]
@@ -175,7 +167,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap pool_map, const Deco
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_splits = gridDim.z, split = blockIdx.z;
-  TRACE(0);
   if (threadIdx.x == 0) {
     for (int i = 0; i < WARPS * MAX_SLOTS; ++i) mbar_init(&full[i], 1);
     *gave_up = 0;
@@ -184,7 +175,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap pool_map, const Deco
   }
   __syncthreads();
   pdl_launch_dependents();
-  TRACE(1);
 
   // The step's metadata is written by the host before the step's first kernel and by no kernel:
   // it is read without waiting for the kernel before this one.
@@ -257,7 +247,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap pool_map, const Deco
   };
   // key blocks wholly below the step's first new position hold what earlier steps wrote: they
   // are requested at once; the others after the kernel before this one has finished
-  TRACE(3);
   const int first_wave = min(my_blocks, a.slots);
   uint32_t deferred = 0;
   for (int j = 0; j < first_wave; ++j) {
@@ -265,10 +254,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap pool_map, const Deco
     else deferred |= 1u << j;
   }
   pdl_wait();
-  TRACE(2);
   for (int j = 0; j < first_wave; ++j)
     if ((deferred >> j) & 1u) request(j);
-  TRACE(4);
 
   // ---- Q (rows beyond the request's packed rows are zero), then its fragments into registers
   constexpr int CHUNKS = D / 8;
@@ -300,11 +287,9 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap pool_map, const Deco
   for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
 
   constexpr int NT = BN / 8;
-  TRACE(5);
   for (int j = 0; j < my_blocks; ++j) {
     const int slot = j % a.slots;
     mbar_wait(&my_full[slot], (uint32_t)(j / a.slots) & 1u, gave_up, a.error_word);
-    TRACE(6);
     const uint32_t k_base = smem_u32(my_kv) + slot * KV_BYTES, v_base = k_base + SUBS * SUB_BYTES;
     const int kb = kb_lo + gw + j * stride;
     const int key0 = kb * BN;
@@ -405,7 +390,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap pool_map, const Deco
   }
 
   // ---- the warps' states into shared memory (every warp of the block is done with its slots)
-  TRACE(7);
   __syncthreads();
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -423,7 +407,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap pool_map, const Deco
   }
   __syncthreads();
   if (n_splits > 1) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");   // all blocks of the cluster have started
-  TRACE(8);
   // ---- this block's warps merged, per row and eight columns a thread; row r goes to block r % n_splits
   constexpr int STATE = D + 4;   // floats per row state: D sums (relative to m), then m and l (16-byte rows)
   for (int i = threadIdx.x; i < BM * (D / 8); i += THREADS) {
@@ -452,7 +435,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap pool_map, const Deco
   }
   if (n_splits > 1) cluster_sync();
   else __syncthreads();
-  TRACE(9);
 
   // ---- the rows this block owns, merged over the blocks in index order
   for (int i = threadIdx.x; i < owned_rows * (D / 4); i += THREADS) {
@@ -482,7 +464,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap pool_map, const Deco
     packed.y = pack_bf16(acc.z * inv, acc.w * inv);
     *reinterpret_cast<uint2*>(a.out + ((long long)(q_start + token) * a.q_heads + head) * D + c4 * 4) = packed;
   }
-  TRACE(11);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -512,11 +493,6 @@ size_t smem_bytes(int slots) {
 
 extern "C" int llm_attention_decode_head_dim() { return D; }
 
-#ifdef DECODE_TRACE
-extern "C" int llm_attention_decode_set_trace(long long* p) {
-  return cudaMemcpyToSymbol(g_trace, &p, sizeof(p)) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 // Writes the 128-byte tensor map of a cache group's pool: `rows` rows of D bfloat16 starting at
 // `base` (16-byte aligned), boxes of 64 columns x `box_rows` rows, 128-byte swizzle.

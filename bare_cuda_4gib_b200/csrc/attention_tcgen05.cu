@@ -162,19 +162,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// -DATTN_TRACE: thread block (0, 0) records SM clock stamps per role and key block into
-// `trace` ([role][block], 64 blocks per role); a development aid, absent from normal builds.
-#ifdef ATTN_TRACE
-#ifndef TRACE_BY
-#define TRACE_BY 0
-#endif
-#define TRACE(role, j) do { if (blockIdx.x == 0 && blockIdx.y == TRACE_BY && a.trace && (j) < 64) a.trace[(role) * 64 + (j)] = clock64(); } while (0)
-#else
-#define TRACE(role, j) do { } while (0)
-#endif
 
 struct AttnArgs {
-  long long* trace;
   // the cache group's pool seen as rows of D elements: row = page * page_rows + k_row0 (or v_row0)
   // + kv head * page_tokens + position in page; the tensor map's box is 64 columns x box_rows rows
   long long page_rows, k_row0, v_row0;
@@ -217,7 +206,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) TRACE(11, 0);
   if (smem_u32(smem) & 1023) {   // never seen; refuse rather than compute with a broken layout
     if (threadIdx.x == 0) atomicCAS(a.error_word, 0, ERR_LAYOUT);
     return;
@@ -277,8 +265,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) TRACE(11, 1);
-
   if (warp > MMA_WARP) {
     // ------------------------------------------------------------------ loader warp
     // Keys and values: one TMA box per piece of a page (a page holds box_rows or more positions
@@ -305,7 +291,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
       }
       const uint32_t held = __ballot_sync(0xffffffffu, my_row >= 0) & ((pieces < 32) ? ((1u << pieces) - 1u) : 0xffffffffu);
       const uint32_t missing = ~held & ((pieces < 32) ? ((1u << pieces) - 1u) : 0xffffffffu);
-      if (lane == 0) TRACE(8, j);
       if (missing) {   // rare: zero the pieces without a page, and make the stores visible to the MMA
         for (int piece = 0; piece < pieces; ++piece) {
           if (!((missing >> piece) & 1u)) continue;
@@ -320,7 +305,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
         __syncwarp();
       }
       if (lane == 0) mbar_expect_tx(&kv_full[s], (uint32_t)__popc(held) * 2u * KA * a.box_rows * 128u);   // also the one arrival
-      if (lane == 0) TRACE(9, j);
       __syncwarp();
       // lane 0 issues the key copies, lane 1 the value copies: issuing is what takes the time
       for (int piece = 0; piece < pieces; ++piece) {
@@ -331,7 +315,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
         for (int at = 0; at < KA; ++at)
           tma_load_2d(base + at * SUB + piece * a.box_rows * 128, &pool_map, &kv_full[s], at * 64, (int)(row + row0_of_cache));
       }
-      if (lane == 0) TRACE(10, j);
     };
     // Block j + 1 is requested as soon as its stage is free (the MMA thread frees it with P V of
     // block j - 1, which it issues after S of block j).
@@ -348,7 +331,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
         ok = false;
         break;
       }
-      if (lane == 0) TRACE(1, j + 1);
       issue_block(j + 1);
     }
   } else if (warp == MMA_WARP) {
@@ -361,7 +343,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
       auto issue_s = [&](int j) -> bool {
         const int s = j % STAGES, b = j & 1;
         if (!mbar_wait(&kv_full[s], (j / STAGES) & 1, abort_flag)) return false;
-        TRACE(0, j);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t k_addr = smem_u32(kv_smem) + s * KV_BYTES;
 #pragma unroll
@@ -371,7 +352,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
             umma_bf16(tmem_base + b * BN, smem_desc_sw128(q_addr + at * SUB) + 2 * k,
                       smem_desc_sw128(k_addr + at * SUB) + 2 * k, idesc_s, (at > 0 || k > 0) ? 1u : 0u);
         umma_commit(&s_full[b]);
-        TRACE(2, j);
         return true;
       };
       // O_block(j) = P(j) V(j) into the group's O_block, once the group has read its O_block(j - 2)
@@ -388,7 +368,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
                       smem_desc_sw128(v_addr + vt * SUB) + (uint64_t)(kk * 2048 >> 4), idesc_o, kk > 0 ? 1u : 0u);
         umma_commit(&o_full[b]);
         umma_commit(&kv_empty[s]);
-        TRACE(3, j);
         return true;
       };
       // Both groups get their first S at once.  A group reports when it holds S(j) in registers:
@@ -435,7 +414,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     mbar_arrive(q_full);
-    if (threadIdx.x == 0) TRACE(11, 2);
     const int quad = warp & 3, g = warp >> 2;        // tensor-memory lanes 32 * quad ..; group g takes blocks j % 2 == g
     const int r = quad * 32 + lane;                  // row of the tile = tensor-memory lane
     const int R = row0 + r;
@@ -470,7 +448,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
       const int key0 = (kb_lo + j) * BN;
       ok = mbar_wait(&s_full[g], (j >> 1) & 1, abort_flag) && !*abort_flag;
       if (!ok) break;
-      if (threadIdx.x == 0) TRACE(4, j);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const bool all_visible = key0 + BN - 1 <= tile_min_pos && (a.window <= 0 || key0 > tile_max_pos - a.window);
       // pass 1: the row's maximum
@@ -493,7 +470,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
           }
         }
       }
-      if (threadIdx.x == 0) TRACE(5, j);
       const float m_new = fmaxf(m, mx * a.scale_log2);       // scale > 0: the maximum commutes with it
       const float m_use = m_new == -INFINITY ? 0.0f : m_new;
       const float corr = fast_exp2(m - m_use);                 // m = -inf gives 0
@@ -539,9 +515,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(&p_full[g]);
-      if (threadIdx.x == 0) TRACE(6, j);
       if (last >= 0) ok = add_block(last, corr_prev);   // the group's block before, whose P V ran meanwhile
-      if (threadIdx.x == 0) TRACE(7, j);
       corr_prev = corr;
       last = j;
     }
@@ -560,17 +534,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
     constexpr int UNITS = D / 4;                         // float4 units per row
     float4* park = reinterpret_cast<float4*>(kv_smem);   // [2 groups][128 rows][UNITS]
     float2* park_ml = reinterpret_cast<float2*>(park + 2 * 128 * UNITS);   // [2 groups][128 rows]
-    if (threadIdx.x == 0) TRACE(11, 3);
     mbar_arrive(done_bar);
     if (ok) ok = mbar_wait(done_bar, 0, abort_flag);
     float4* mine = park + ((size_t)g * 128 + r) * UNITS;
 #pragma unroll
     for (int i = 0; i < UNITS; ++i) mine[i ^ (r & (UNITS - 1))] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
     park_ml[g * 128 + r] = make_float2(m, l);
-    if (threadIdx.x == 0) TRACE(11, 4);
     mbar_arrive(merge_bar);
     if (ok) ok = mbar_wait(merge_bar, 0, abort_flag);
-    if (threadIdx.x == 0) TRACE(11, 5);
     if (ok && seq >= 0) {
 #pragma unroll
       for (int q = threadIdx.x; q < BM * UNITS; q += SOFTMAX_THREADS) {
@@ -591,11 +562,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
       }
     }
   }
-
-  if (threadIdx.x == 0) TRACE(11, 6);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (threadIdx.x == 0) TRACE(11, 7);
   if (warp == MMA_WARP) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -636,9 +604,6 @@ extern "C" int llm_attention_tc_pool_map(void* map_out, const void* base, long l
   return r == CUDA_SUCCESS ? 0 : 2000 + (int)r;
 }
 
-static long long* g_trace = nullptr;
-extern "C" void llm_attention_tc_set_trace(long long* buffer) { g_trace = buffer; }   // development aid
-
 extern "C" int llm_attention_tc_head_dim() { return D; }
 extern "C" int llm_attention_tc_rows() { return BM; }
 
@@ -672,7 +637,6 @@ extern "C" int llm_attention_tcgen05(const void* pool_map, const void* pool_base
   CUtensorMap map;   // the caller's buffer need not be 64-byte aligned
   memcpy(&map, pool_map, sizeof(CUtensorMap));
   AttnArgs a;
-  a.trace = g_trace;
   a.page_rows = page_stride / D;
   a.k_row0 = k_off / (D * 2);
   a.v_row0 = v_off / (D * 2);

@@ -57,14 +57,6 @@ enum { PRO_BF16 = 0, PRO_NORM = 1, PRO_PRENORMED = 2 };
 constexpr int SQ_SLOTS = 32;                  // token slots per item in the sums-of-squares parts
 enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_ROPE = 3 };
 
-// -DGEMV_TRACE: lane 0 of warp 0 of thread block 0 records SM clock stamps of the kernel's phases
-// into a buffer set with llm_gemv_set_trace; a development aid, absent from normal builds.
-#ifdef GEMV_TRACE
-__device__ long long* g_trace = nullptr;
-#define TRACE(i) do { if (blockIdx.x == 0 && threadIdx.x == 0 && trace_to) trace_to[i] = clock64(); } while (0)
-#else
-#define TRACE(i) do { } while (0)
-#endif
 
 struct GemvArgs {
   const __nv_bfloat16* w;   // [w_rows, k] row-major
@@ -101,9 +93,6 @@ struct GemvArgs {
   const int32_t* row_seq;
   const float* inv_freq;    // [d / 2], null: no rotation
   int q_heads, write_cache;
-  // weights of a later product to pull into L2
-  const uint8_t* prefetch;
-  long long prefetch_bytes;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -210,10 +199,6 @@ __global__ void __launch_bounds__(THREADS, PRO == PRO_NORM ? 1 : 2) gemv_fused_k
   // the producer leaves alone until the norm is done
   float* staging = reinterpret_cast<float*>(ring + (size_t)a.first_aliased * stage_bytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-#ifdef GEMV_TRACE
-  long long* const trace_to = g_trace;
-#endif
-  TRACE(0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < a.stages; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -274,21 +259,12 @@ __global__ void __launch_bounds__(THREADS, PRO == PRO_NORM ? 1 : 2) gemv_fused_k
   }
 
   // ---- consumers
-  if (a.prefetch_bytes > 0) {
-    // A later product's weights towards L2, one 128-byte line per instruction, through the load
-    // path (the TMA unit is busy with this product's own copies).  Nothing waits for these.
-    const long long lines = a.prefetch_bytes / 128;
-    for (long long i = (long long)blockIdx.x * CONSUMERS + threadIdx.x; i < lines; i += (long long)gridDim.x * CONSUMERS)
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(a.prefetch + i * 128));
-  }
   if (PRO == PRO_NORM) {     // the norm's weight is no kernel's output: fetch it before waiting
     for (int i = threadIdx.x; i < a.k; i += CONSUMERS)
       norm_ws[i] = a.norm_w_dtype == DT_BF16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.norm_w)[i])
                                              : static_cast<const float*>(a.norm_w)[i];
   }
-  TRACE(1);
   pdl_wait();
-  TRACE(2);
   // x for every token into shared memory (rows past the last token are zero).  Rows come in as
   // bulk copies, which unlike loads into registers are not limited by the SM's load queue.
   if (PRO == PRO_NORM) {
@@ -309,7 +285,6 @@ __global__ void __launch_bounds__(THREADS, PRO == PRO_NORM ? 1 : 2) gemv_fused_k
           }
         }
         mbar_wait(x_bar, x_phase, gave_up, a.error_word, ERR_GEMV_CONSUMER);
-        TRACE(6);
         x_phase ^= 1u;
       }
       for (int j = warp; j < a.norm_rows && r0 + j < 8 * NT; j += WARPS) {
@@ -368,10 +343,8 @@ __global__ void __launch_bounds__(THREADS, PRO == PRO_NORM ? 1 : 2) gemv_fused_k
     }
     mbar_wait(x_bar, 0, gave_up, a.error_word, ERR_GEMV_CONSUMER);
   }
-  TRACE(3);
   consumer_barrier();
   if (PRO == PRO_NORM && threadIdx.x == 0) mbar_arrive(norm_done);
-  TRACE(4);
 
   int buf = 0, stage = 0;
   uint32_t phase = 0;
@@ -432,7 +405,6 @@ __global__ void __launch_bounds__(THREADS, PRO == PRO_NORM ? 1 : 2) gemv_fused_k
         phase ^= 1u;
       }
     }
-    TRACE(5);
 
     float* mine = red + ((size_t)(buf * WARPS + warp) * NT * 4) * 32;
 #pragma unroll
@@ -525,7 +497,6 @@ __global__ void __launch_bounds__(THREADS, PRO == PRO_NORM ? 1 : 2) gemv_fused_k
       }
     }
     buf ^= 1;
-    TRACE(8);
   }
 }
 
@@ -611,11 +582,6 @@ static bool plan_smem(int tokens, int k, int pro, size_t budget, int min_stages,
 
 }  // namespace
 
-#ifdef GEMV_TRACE
-extern "C" int llm_gemv_set_trace(long long* p) {
-  return cudaMemcpyToSymbol(g_trace, &p, sizeof(p)) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 // Shared memory the kernel needs for `tokens` tokens and inner dimension k (0: not supported).
 extern "C" long long llm_gemv_fused_smem(int tokens, int k) {
@@ -630,8 +596,7 @@ extern "C" int llm_gemv_fused(const void* w, int w_rows, int k, int tokens, int 
                               long long page_stride, int table_stride, int page_tokens, int kv_heads, int head_dim,
                               const int32_t* positions, const int32_t* row_seq, const float* inv_freq, int q_heads,
                               int write_cache, const float* sq_in, int sq_items, void* pre_x, long long pre_x_stride,
-                              const void* pre_w, int pre_w_dtype, float* pre_sq, const void* prefetch,
-                              long long prefetch_bytes, int max_blocks, int* error_word, cudaStream_t stream) {
+                              const void* pre_w, int pre_w_dtype, float* pre_sq, int max_blocks, int* error_word, cudaStream_t stream) {
   SmemPlan plan;
   if (!plan_smem(tokens, k, pro, SMEM_BUDGET, 2, plan)) return ERR_BAD_SIZE;
   if (out_dtype != DT_F32 && out_dtype != DT_BF16) return ERR_BAD_DTYPE;
@@ -640,7 +605,7 @@ extern "C" int llm_gemv_fused(const void* w, int w_rows, int k, int tokens, int 
     return ERR_BAD_SIZE;
   const auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   if (!aligned16(w) || !aligned16(x) || (pro != PRO_NORM && x_stride % 8) || (pro == PRO_NORM && x_stride % 4) ||
-      (pro == PRO_NORM && !aligned16(norm_w)) || (prefetch_bytes > 0 && !aligned16(prefetch)))
+      (pro == PRO_NORM && !aligned16(norm_w)))
     return ERR_BAD_ALIGN;
   GemvArgs a = {};
   a.w = static_cast<const __nv_bfloat16*>(w);
@@ -650,7 +615,6 @@ extern "C" int llm_gemv_fused(const void* w, int w_rows, int k, int tokens, int 
   a.out = out, a.out_dtype = out_dtype, a.out_stride = out_stride, a.n_out = n_out, a.up_offset = up_offset;
   a.cache = PagedCache{k_base, v_base, block_table, page_stride, table_stride, page_tokens, kv_heads, head_dim};
   a.positions = positions, a.row_seq = row_seq, a.inv_freq = inv_freq, a.q_heads = q_heads, a.write_cache = write_cache;
-  a.prefetch = static_cast<const uint8_t*>(prefetch), a.prefetch_bytes = prefetch_bytes;
   a.sq_in = sq_in, a.sq_items = sq_items;
   a.pre_x = static_cast<__nv_bfloat16*>(pre_x), a.pre_x_stride = pre_x_stride, a.pre_w = pre_w, a.pre_w_dtype = pre_w_dtype;
   a.pre_sq = pre_sq;

@@ -14,7 +14,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ..cache.manager import CacheDemand
-from ..config.llama import read_config_json
+from ..config.reader import read_config_json
 from ..config.registry import resolve_architecture
 from ..errors import ConfigError
 from ..parts.base import Part
@@ -70,12 +70,11 @@ class Model:
         parts.extend(_walk(self.head))
         return parts
 
-    def cache_demands(self) -> List[CacheDemand]:
-        out = []
-        for call in self.order:
-            mixer = self.blocks[call.layer].mixer
-            out.append(CacheDemand(mixer.cache_request(), mixer.state_request(), call.cache_from))
-        return out
+    def cache_demands(self) -> List[List[CacheDemand]]:
+        """Per entry of the run order, what its block keeps per request (the block says; a block
+        with one mixer states one demand)."""
+        return [[CacheDemand(kv, state, call.cache_from) for kv, state in self.blocks[call.layer].cache_demands()]
+                for call in self.order]
 
     # ------------------------------------------------------------------ weights
     def bind(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype, device) -> None:

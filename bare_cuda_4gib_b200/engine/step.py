@@ -37,29 +37,48 @@ class StepEntry:
 
 
 class Workspace:
-    """Named activation buffers, allocated once for the largest step and handed out as views."""
+    """Named activation buffers, allocated once for the largest step and handed out as views.
+
+    A buffer's address is part of every CUDA graph that was captured while it was in use, so a
+    buffer is never freed while the workspace lives: callers state the largest extent they can
+    ever ask for (`max_rows`, `max_lead`), and should a request still outgrow its buffer, the old
+    one is kept (`retired`) beside the new one, so that a graph captured earlier keeps writing
+    into memory that is still this workspace's own.  `generation` counts such replacements."""
 
     def __init__(self, device, max_rows: int):
         self.device, self.max_rows = device, max_rows
         self._buffers: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self.retired: List[torch.Tensor] = []
+        self.generation = 0
 
-    def get(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype, max_rows: Optional[int] = None) -> torch.Tensor:
+    def get(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype, max_rows: Optional[int] = None,
+            max_lead: Optional[int] = None) -> torch.Tensor:
         """A [rows, width] (or [n, rows, width]) view; the rows axis is sized for the largest step
-        (or for `max_rows` when the caller only uses the buffer for small steps)."""
+        (or for `max_rows` when the caller only uses the buffer for small steps), the leading axis
+        of a three-dimensional buffer for `max_lead` (the most the caller will ever stack)."""
         rows_axis = len(shape) - 2
         full = list(shape)
         full[rows_axis] = max(min(self.max_rows, max_rows) if max_rows else self.max_rows, shape[rows_axis])
+        if rows_axis == 1 and max_lead:
+            full[0] = max(full[0], int(max_lead))
         need = int(np.prod(full))
         key = (name, dtype)
         buf = self._buffers.get(key)
         if buf is None or buf.numel() < need:
+            if buf is not None:
+                self.retired.append(buf)
+                self.generation += 1
             buf = torch.empty(need, dtype=dtype, device=self.device)
             self._buffers[key] = buf
-        view = buf[:need].view(full)
-        return view[: shape[0]] if rows_axis == 0 else view[:, : shape[1]]
+        if rows_axis == 0:
+            return buf[:need].view(full)[: shape[0]]
+        # the stride of the leading axis follows from the rows axis and the width only, so it is
+        # the same whatever `lead` a call asks for
+        per = full[1] * int(np.prod(full[2:]))
+        return buf[: shape[0] * per].view([shape[0]] + full[1:])[:, : shape[1]]
 
     def bytes(self) -> int:
-        return sum(b.numel() * b.element_size() for b in self._buffers.values())
+        return sum(b.numel() * b.element_size() for b in list(self._buffers.values()) + self.retired)
 
 
 class StepContext:
@@ -91,8 +110,6 @@ class StepContext:
         self.following_norm = None # the norm part that reads the stream after the part that runs now
         self.norm_after_layer = None
         self.prenormed = None      # what the last adding product left for that norm (kernels.lib.Prenormed)
-        self.gemv_prev: list = []  # the few-token products of the previous step, in call order
-        self.gemv_now: list = []
 
 
 def padded_batch(n: int) -> int:
@@ -163,9 +180,12 @@ class StepRunner:
                                                                 self._seq_q_len[1], self._seq_kv_len[1])
         c.calls = []
         for i, call in enumerate(model.order):
-            table = self._tables[cache.cache_group[i][0]][1] if i in cache.cache_group else None
-            view = cache.cache_view(i, table) if table is not None else None
-            c.calls.append(CallContext(i, view, call.cache_from is None, cache.states.get(i)))
+            views, states = [], []
+            for j in range(len(cache.demands[i])):
+                where = cache.group_of(i, j)
+                views.append(cache.cache_view(i, self._tables[where[0]][1], j) if where is not None else None)
+                states.append(cache.state_of(i, j))
+            c.calls.append(CallContext(i, views, call.cache_from is None, states))
 
     def _row_views(self, rows: int):
         """token ids, positions, batch sequence of a row, wanted rows: four arrays of `rows` entries at
@@ -277,10 +297,12 @@ class StepRunner:
         slots = [e.slot for e in entries]
         for gi in range(len(self.cache.groups)):
             self.cache.block_table_rows(gi, slots, self._tables[gi][0])
-        for i in range(pad):      # idle rows: token 0 at position 0 of a sequence that holds no page
+        # idle rows: token 0 at position 0 of a sequence that holds no page and whose state row is
+        # the spare one that no request owns
+        for i in range(pad):
             s = n_seqs + i
             tok_h[row], pos_h[row], rs_h[row], want_h[w] = 0, 0, s, row
-            self._seq_slot[0][s], self._seq_q_start[0][s] = 0, row
+            self._seq_slot[0][s], self._seq_q_start[0][s] = self.cache.idle_slot, row
             self._seq_q_len[0][s], self._seq_kv_len[0][s] = 0, 0
             for gi in range(len(self.cache.groups)):
                 self._tables[gi][0][s].fill(-1)
@@ -304,7 +326,6 @@ class StepRunner:
         c.host_slots = slots
         c.stream = torch.cuda.current_stream().cuda_stream
         c.extras.clear()
-        c.gemv_prev, c.gemv_now = c.gemv_now, []
         self.model.plan_step(c)
         return decode, n_want
 

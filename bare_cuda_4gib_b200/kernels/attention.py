@@ -17,17 +17,15 @@ import torch
 
 from . import build
 from ..errors import KernelLaunchError
-from .lib import CacheView, _check
+from .lib import CacheView, _check, sm_count
 
 KEY_BLOCK = 64
-TARGET_BLOCKS = 148 * 2
 COUNTER_WORDS = 4096          # per-tile split counters at the start of the scratch (see the kernel)
 _libs: Dict[int, object] = {}
 _tc_libs: Dict[int, object] = {}
 _decode_libs: Dict[int, object] = {}
 TC_HEAD_DIMS = (64, 128)      # head sizes the tcgen05 prefill kernel and the decode kernel are built for
 DECODE_MAX_TILES = 65535 // 4 # (tiles x kv heads) up to which the cluster decode kernel runs
-N_SMS = 148
 
 
 def supports(head_dim: int) -> bool:
@@ -154,9 +152,9 @@ class AttentionPlan:
         self._host_events[self._host_turn].record()
 
     def scratch(self, ctx, floats: int, device) -> torch.Tensor:
-        """Scratch for split keys; a split step has at most TARGET_BLOCKS + tiles * kv_heads items."""
+        """Scratch for split keys; a split step has at most (2 * sm_count()) + tiles * kv_heads items."""
         if self._scratch is None or self._scratch.numel() < floats:
-            most = COUNTER_WORDS + (TARGET_BLOCKS + (ctx.max_seqs + 8) * self.kv_heads) * 16 * (self.head_dim + 1)
+            most = COUNTER_WORDS + ((2 * sm_count()) + (ctx.max_seqs + 8) * self.kv_heads) * 16 * (self.head_dim + 1)
             self._scratch = torch.zeros(max(floats, most), dtype=torch.float32, device=device)   # counters start at zero
         return self._scratch
 
@@ -193,7 +191,7 @@ def step_tiles(ctx, plan: AttentionPlan):
     use_decode = rows_per_tile == 16 and plan.decode is not None and n_tiles * plan.kv_heads <= DECODE_MAX_TILES
     if rows_per_tile == 16 and not use_decode:
         key_blocks = -(-ctx.max_kv_len // KEY_BLOCK)
-        n_splits = max(1, min(key_blocks, -(-TARGET_BLOCKS // (n_tiles * plan.kv_heads))))
+        n_splits = max(1, min(key_blocks, -(-(2 * sm_count()) // (n_tiles * plan.kv_heads))))
         if os.environ.get("BARE_CUDA_B200_ATTN_SPLITS"):     # experiments only
             n_splits = min(key_blocks, int(os.environ["BARE_CUDA_B200_ATTN_SPLITS"]))
         if n_tiles * plan.kv_heads > COUNTER_WORDS:
@@ -207,13 +205,11 @@ def step_tiles(ctx, plan: AttentionPlan):
         # step stays valid while the requests grow.
         d = plan.head_dim       # shared memory of a block: alignment slack, 4 key blocks (K and V), Q, merge states, barriers
         block_smem = 1024 + 4 * 2 * KEY_BLOCK * d * 2 + 16 * (d + 8) * 2 + 24 * (d + 4) * 4 + 128
-        resident = N_SMS * max(1, (227 * 1024) // block_smem)
+        resident = sm_count() * max(1, (227 * 1024) // block_smem)
         dec_splits = max(1, min(8, resident // (n_tiles * plan.kv_heads)))
         dec_slots = 1
         if os.environ.get("BARE_CUDA_B200_ATTN_SPLITS"):     # experiments only
             dec_splits = max(1, min(8, int(os.environ["BARE_CUDA_B200_ATTN_SPLITS"])))
-        if os.environ.get("BARE_CUDA_B200_ATTN_SLOTS"):
-            dec_slots = int(os.environ["BARE_CUDA_B200_ATTN_SLOTS"])
     out = (dev[:n_tiles], dev[n_tiles: 2 * n_tiles], n_tiles, rows_per_tile, n_splits, dec_splits, dec_slots)
     ctx.extras[key] = out
     return out

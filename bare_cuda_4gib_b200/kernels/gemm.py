@@ -12,10 +12,9 @@ import torch
 
 from ..errors import KernelLaunchError
 from . import build
-from .lib import DT_BF16, DT_F32, Partials, _check
+from .lib import DT_BF16, DT_F32, Partials, _check, sm_count
 
 BM, BK = 128, 64
-TARGET_BLOCKS = 148 * 2
 SPLIT_MAX_ROWS = 256          # steps with more rows never split K
 _lib = None
 _error_word: Optional[torch.Tensor] = None
@@ -119,10 +118,17 @@ def choose_splits(rows: int, n: int, k: int, bn: int) -> int:
         return 1
     tiles = -(-n // BM) * -(-rows // bn)
     k_blocks = -(-k // BK)
-    splits = min(k_blocks // 4, TARGET_BLOCKS // tiles, max(1, k // (4 * rows)))
+    splits = min(k_blocks // 4, (2 * sm_count()) // tiles, max(1, k // (4 * rows)))
     splits = max(1, splits)
     per = -(-k_blocks // splits)
     return -(-k_blocks // per)
+
+
+def max_splits(n: int, k: int) -> int:
+    """The most blocks `choose_splits` ever puts on one output tile of an [n, k] weight, whatever
+    the number of rows: the scratch for partial results is sized for it once, so that its address
+    never changes under a captured graph."""
+    return max(1, min(-(-k // BK) // 4, (2 * sm_count()) // -(-n // BM)))
 
 
 TOKENS_ON_ROWS_ABOVE = 256    # steps with more rows put 128 tokens on the MMA rows (orientation 1)
@@ -130,7 +136,6 @@ TOKENS_ON_ROWS_ABOVE = 256    # steps with more rows put 128 tokens on the MMA r
 # outputs, so from about a hundred tokens on the other orientation's wider tiles measured faster
 # (TinyLlama's feed-forward at 128 / 256 tokens: 16 / 19 us against 23 / 48 us).
 SWIGLU_TOKENS_ON_ROWS_ABOVE = 96
-N_SMS = 148
 
 
 def feature_tile(rows: int, n_out: int, swiglu: bool) -> int:
@@ -152,8 +157,8 @@ def feature_tile(rows: int, n_out: int, swiglu: bool) -> int:
             continue
         out_per_tile = bn // 2 if swiglu else bn
         tiles = -(-rows // BM) * -(-n_out // out_per_tile)
-        cost = -(-tiles // N_SMS) * (bn / 256.0 + 0.12)
-        if bn >= 192 and tiles > N_SMS:
+        cost = -(-tiles // sm_count()) * (bn / 256.0 + 0.12)
+        if bn >= 192 and tiles > sm_count():
             cost *= 0.88
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = bn, cost
@@ -185,7 +190,7 @@ def run(ctx, plan: GemmPlan, a: torch.Tensor, rows: int, out_dtype: torch.dtype,
     if swiglu:
         inter = plan.n // 2
         out = ctx.ws.get(buffer, (rows, inter), out_dtype)
-        if -(-inter // (BM // 2)) * -(-rows // bn) >= N_SMS:
+        if -(-inter // (BM // 2)) * -(-rows // bn) >= sm_count():
             # 64 gate rows and the matching 64 up rows share a block's 128 MMA rows: SwiGLU in the
             # epilogue and no partial results, when that alone gives every SM a block
             _check(l.llm_gemm_bf16(ctypes.addressof(plan.weight_map(BM // 2)), ctypes.addressof(plan.act_map(a, bn)),
@@ -200,7 +205,8 @@ def run(ctx, plan: GemmPlan, a: torch.Tensor, rows: int, out_dtype: torch.dtype,
         return Partials(out)
     splits = choose_splits(rows, plan.n, plan.k, bn) if (allow_partials and out_dtype == torch.float32) else 1
     if splits > 1:
-        out = ctx.ws.get(buffer + ".partials", (splits, rows, plan.n), torch.float32, max_rows=SPLIT_MAX_ROWS)
+        out = ctx.ws.get(buffer + ".partials", (splits, rows, plan.n), torch.float32, max_rows=SPLIT_MAX_ROWS,
+                         max_lead=max_splits(plan.n, plan.k))
         stride = out.stride(0)
     else:
         out = ctx.ws.get(buffer, (rows, plan.n), out_dtype)

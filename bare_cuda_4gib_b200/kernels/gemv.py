@@ -4,8 +4,7 @@ computed in the kernel) and finish its output itself (residual add, SwiGLU, or r
 cache write), so that a decode step launches five kernels a layer instead of nine.
 
 `BARE_CUDA_B200_GEMV_MAX_TOKENS=0` switches the path off (every product then goes to the tcgen05
-kernel); `BARE_CUDA_B200_GEMV_PREFETCH=1` makes each kernel pull the next product's weights
-towards L2 (measured: no gain on B200, so it is off)."""
+kernel)."""
 
 from __future__ import annotations
 
@@ -16,16 +15,13 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from . import build
-from .lib import DT_BF16, DT_F32, AddTo, LazyNorm, Partials, Prenormed, RotateAndCache, _check, _ptr
+from .lib import DT_BF16, DT_F32, AddTo, LazyNorm, Partials, Prenormed, RotateAndCache, _check, _ptr, sm_count
 
 PRO_BF16, PRO_NORM, PRO_PRENORMED = 0, 1, 2
 SQ_SLOTS = 32
 EPI_STORE, EPI_ADD, EPI_SWIGLU, EPI_ROPE = 0, 1, 2, 3
 MAX_TOKENS = int(os.environ.get("BARE_CUDA_B200_GEMV_MAX_TOKENS", "24"))     # measured: 24 rows still gain, 32 lose
-PREFETCH = os.environ.get("BARE_CUDA_B200_GEMV_PREFETCH", "0") not in ("0", "")
-PREFETCH_MAX_BYTES = 64 << 20      # never more than about half of L2
 PRENORM = os.environ.get("BARE_CUDA_B200_GEMV_PRENORM", "1") not in ("0", "")
-N_SMS = 148
 _lib = None
 _smem: Dict[Tuple[int, int], int] = {}
 
@@ -38,7 +34,7 @@ def lib():
         l.llm_gemv_fused_smem.argtypes = [I, I]
         l.llm_gemv_fused_smem.restype = L
         l.llm_gemv_fused.argtypes = [P, I, I, I, I, I, P, L, P, I, F, P, P, I, L, I, I, P, P, P, L, I, I, I, I,
-                                     P, P, P, I, I, P, I, P, L, P, I, P, P, L, I, P, P]
+                                     P, P, P, I, I, P, I, P, L, P, I, P, I, P, P]
         l.llm_gemv_fused.restype = c_int
         _lib = l
     return _lib
@@ -60,21 +56,6 @@ def smem_bytes(tokens: int, k: int) -> int:
 def takes(rows: int, k: int) -> bool:
     """Whether the kernel runs `rows` tokens against an inner dimension k (x must fit in shared memory)."""
     return 0 < rows <= MAX_TOKENS and smem_bytes(rows, k) > 0
-
-
-def _next_weights(ctx, weight: torch.Tensor):
-    """The weights of the product that followed this one in the previous step (steps repeat the
-    same sequence of products), for the L2 prefetch."""
-    now = getattr(ctx, "gemv_now", None)
-    if now is None:
-        return 0, 0
-    i = len(now)
-    now.append((weight.data_ptr(), weight.numel() * weight.element_size()))
-    prev = getattr(ctx, "gemv_prev", None) or []
-    if not PREFETCH or len(prev) < 2 or i >= len(prev) or prev[i][0] != weight.data_ptr():
-        return 0, 0
-    ptr, size = prev[(i + 1) % len(prev)]
-    return ptr, min(size, PREFETCH_MAX_BYTES)
 
 
 def run(ctx, weight: torch.Tensor, x, rows: int, out_dtype: torch.dtype, buffer: str, swiglu: bool,
@@ -116,7 +97,6 @@ def run(ctx, weight: torch.Tensor, x, rows: int, out_dtype: torch.dtype, buffer:
         epi, n_out = EPI_STORE, n
         out = ctx.ws.get(buffer, (rows, n), out_dtype)
     from . import gemm
-    pf_ptr, pf_bytes = _next_weights(ctx, weight)
     _check(lib().llm_gemv_fused(
         weight.data_ptr(), n, k, rows, pro, epi, xt.data_ptr(), x_stride, _ptr(norm_w), norm_code, eps,
         _ptr(row_index), out.data_ptr(), DT_BF16 if out.dtype == torch.bfloat16 else DT_F32, out.stride(0), n_out,
@@ -126,6 +106,6 @@ def run(ctx, weight: torch.Tensor, x, rows: int, out_dtype: torch.dtype, buffer:
         cache.head_dim if cache else 0, _ptr(positions), _ptr(row_seq), _ptr(inv_freq), q_heads, write_cache,
         _ptr(sq_in), sq_items, _ptr(pre_x), pre_x.stride(0) if pre_x is not None else 0, _ptr(pre_w),
         (DT_BF16 if pre_w.dtype == torch.bfloat16 else DT_F32) if pre_w is not None else DT_F32, _ptr(pre_sq),
-        pf_ptr, pf_bytes, N_SMS, gemm.error_word(weight.device).data_ptr(), ctx.stream), "gemv_fused")
+        sm_count(), gemm.error_word(weight.device).data_ptr(), ctx.stream), "gemv_fused")
     ctx.prenormed = Prenormed(epilogue.then_norm, pre_x, pre_sq, -(-n // 16)) if pre_x is not None else None
     return None if epi in (EPI_ADD, EPI_ROPE) else Partials(out)

@@ -54,6 +54,19 @@ def _dev(*tensors: Optional[torch.Tensor]) -> None:
             raise KernelLaunchError("kernel arguments must be CUDA tensors; the engine has no CPU path")
 
 
+B200_SMS = 148     # what planning assumes where no device can be asked (host-only tests)
+_sm_count = None
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current CUDA device, asked once."""
+    global _sm_count
+    if _sm_count is None:
+        _sm_count = (torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+                     if torch.cuda.is_available() else B200_SMS)
+    return _sm_count
+
+
 def stream_handle() -> int:
     return torch.cuda.current_stream().cuda_stream
 

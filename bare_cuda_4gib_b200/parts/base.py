@@ -20,6 +20,9 @@ Families and the one method each must have besides `weight_specs` / `bind`:
 * feed_forward  `forward(ctx, h) -> Partials`, or None as for a mixer
 * block         `forward(ctx, call, residual, pending) -> Partials`: runs one layer; `pending` is
                 the previous layer's contribution that has not been added to the residual yet.
+                `parts()` lists its parts; `cache_demands()` -> [(KVCacheRequest or None,
+                StateRequest or None), ...], one pair per part that keeps something per request
+                (`call.caches[j]` / `call.states[j]` belong to pair j).
 * embedding     `forward(ctx) -> residual [tokens, hidden] float32`
 * head          `forward(ctx, normed) -> logits [rows, vocab] float32`
 
@@ -91,10 +94,22 @@ class Part:
 
 
 class CallContext:
-    """One run of a layer inside a step: its index in the run order, the cache it reads (and
-    whether it also writes it) and its per-request state."""
+    """One run of a layer inside a step: its index in the run order, the caches it reads (and
+    whether it also writes them) and its per-request states, one of each per demand the block
+    stated (`None` where a demand asked for none).  `cache` and `state` are the first ones: all a
+    block with a single mixer needs."""
 
-    __slots__ = ("index", "cache", "writes_cache", "state")
+    __slots__ = ("index", "caches", "writes_cache", "states")
 
-    def __init__(self, index, cache, writes_cache, state):
-        self.index, self.cache, self.writes_cache, self.state = index, cache, writes_cache, state
+    def __init__(self, index, caches, writes_cache, states):
+        if not isinstance(caches, (list, tuple)):
+            caches, states = [caches], [states]
+        self.index, self.caches, self.writes_cache, self.states = index, list(caches), writes_cache, list(states)
+
+    @property
+    def cache(self):
+        return self.caches[0] if self.caches else None
+
+    @property
+    def state(self):
+        return self.states[0] if self.states else None

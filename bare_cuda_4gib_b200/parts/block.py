@@ -23,6 +23,10 @@ class PreNormBlock:
     def parts(self):
         return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
 
+    def cache_demands(self):
+        """What this layer keeps per request: its mixer's paged cache and state."""
+        return [(self.mixer.cache_request(), self.mixer.state_request())]
+
     def forward(self, ctx, call, residual, pending):
         n = ctx.n_tokens
         ctx.residual = residual      # a part may add its contribution here itself and return None

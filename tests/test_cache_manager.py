@@ -84,16 +84,16 @@ def test_groups_by_need_and_borrowed_caches():
                CacheDemand(KVCacheRequest(2, 16)), CacheDemand(KVCacheRequest(2, 16), cache_from=0),
                CacheDemand(None, StateRequest((4, 3)))]
     m = CacheManager(demands, page_tokens=8, max_seqs=2, max_tokens=64, num_pages=10, allocate=True, device="cpu")
-    assert len(m.groups) == 2 and m.groups[0].members == [0, 2] and m.groups[1].members == [1]
-    assert m.cache_group[3] == m.cache_group[0] and 4 not in m.cache_group
+    assert len(m.groups) == 2 and m.groups[0].members == [(0, 0), (2, 0)] and m.groups[1].members == [(1, 0)]
+    assert m.group_of(3) == m.group_of(0) and m.group_of(4) is None
     assert m.groups[0].page_stride == 2 * (2 * 2 * 8 * 16)
     with pytest.raises(CacheError, match="earlier run"):
         CacheManager([CacheDemand(KVCacheRequest(1, 16), cache_from=0)], page_tokens=8, max_seqs=1, max_tokens=8)
     # state slots: written by a request, zero for the next one that takes the slot
     s = m.acquire_slot()
-    m.states[4][s].fill_(5.0)
+    m.state_of(4)[s].fill_(5.0)
     m.release_slot(s)
-    assert m.acquire_slot() == s and float(m.states[4][s].abs().sum()) == 0.0
+    assert m.acquire_slot() == s and float(m.state_of(4)[s].abs().sum()) == 0.0
 
 
 def test_window_gives_pages_back_as_it_moves():

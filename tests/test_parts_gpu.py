@@ -134,7 +134,7 @@ def test_layer_named_twice_and_borrowed_cache(dtype):
     model, cfg = _llama("A", dtype, mutate)
     assert len(model.cache_demands()) == 4
     runner, cache = _runner(model, 16, 96)
-    assert len(cache.groups) == 1 and cache.groups[0].members == [0, 1, 2]     # the fourth run owns no cache
+    assert len(cache.groups) == 1 and cache.groups[0].members == [(0, 0), (1, 0), (2, 0)]     # the fourth run owns no cache
     plain = pl.read_model_folder(H.model_folder("A"))
     plain.order = order
     rng = random.Random(4)
@@ -239,7 +239,7 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
     demands = model.cache_demands()
     assert demands[0].kv is None and demands[0].state is not None and demands[1].kv is not None
     runner, cache = _runner(model, 16, 64)
-    assert 0 in cache.states and len(cache.groups) == 1 and cache.groups[0].members == [1]
+    assert cache.state_of(0) is not None and len(cache.groups) == 1 and cache.groups[0].members == [(1, 0)]
 
     # the same model, plainly: layer 0 with the moving average, layer 1 as the plain Llama layer
     t64 = {k: v.double().cpu() for k, v in tensors.items()}
