@@ -25,7 +25,7 @@ from ..cache.manager import CacheManager
 from ..errors import EngineError
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import DeviceSampler
-from .model import load_model
+from .model import load_model, random_model
 from .scheduler import (FINISH_CANCELLED, FINISH_ERROR, Request, Scheduler, SchedulerStats, TokenEvent)
 from .step import StepEntry, StepRunner
 
@@ -76,10 +76,17 @@ class LLMEngine:
     def __init__(self, model_path, max_tokens: int = 1024, max_seqs: int = 8, kv_pages: int = 0,
                  dtype: str = "bfloat16", page_tokens: int = 64, max_step_tokens: Optional[int] = None,
                  policy: str = "reserve", device: str = "cuda", use_fast_gemm: bool = True,
-                 use_fast_attention: bool = True, use_cuda_graphs: bool = True):
+                 use_fast_attention: bool = True, use_cuda_graphs: bool = True, random=None):
+        """`random=(config, seed)`: no folder is read; the model of that typed configuration gets
+        seeded random weights generated on the device (the values `write_random_model` would have
+        written with that seed from this device), and `model_path` may be None."""
         if not torch.cuda.is_available():
             raise EngineError("no CUDA device: the engine has no CPU path")
-        self.model, self.config = load_model(model_path, dtype, device)
+        if random is not None:
+            self.config = random[0]
+            self.model = random_model(random[0], int(random[1]), dtype, device)
+        else:
+            self.model, self.config = load_model(model_path, dtype, device)
         if max_tokens > self.model.spec.max_positions:
             raise EngineError(f"max_tokens {max_tokens} exceeds the model's {self.model.spec.max_positions} positions")
         if max_seqs <= 0:

@@ -20,7 +20,7 @@ from ..errors import ConfigError
 from ..parts.base import Part
 from ..parts.registry import build_part, lookup
 from ..parts.spec import ModelSpec, WeightSpec
-from ..weights.loader import load_weights
+from ..weights.loader import load_weights, random_weights
 
 RUN_DTYPES = {"float32": torch.float32, "fp32": torch.float32, "bfloat16": torch.bfloat16, "bf16": torch.bfloat16}
 
@@ -77,6 +77,16 @@ class Model:
                 for call in self.order]
 
     # ------------------------------------------------------------------ weights
+    def adjacent_weights(self) -> List[List[str]]:
+        """File names of tensors that some part multiplies as one matrix, in stacking order."""
+        out = []
+        for part in self.all_parts():
+            specs = part.weight_specs()
+            for group in part.adjacent_weights():
+                if all(local in specs for local in group):
+                    out.append([specs[local].name for local in group])
+        return out
+
     def bind(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype, device) -> None:
         """`tensors` by file name (see `expected_weights`)."""
         self.dtype, self.device = dtype, torch.device(device)
@@ -157,6 +167,21 @@ def load_model_with_spec(folder, spec: ModelSpec, dtype="bfloat16", device="cuda
     from a registered architecture)."""
     expected, model = expected_weights(spec)
     dt = run_dtype(dtype)
-    tensors = load_weights(folder, expected, spec.aliases, spec.ignorable, dt, torch.device(device))
+    tensors = load_weights(folder, expected, spec.aliases, spec.ignorable, dt, torch.device(device),
+                           model.adjacent_weights())
+    model.bind(tensors, dt, device)
+    return model
+
+
+def random_model(config, seed: int, dtype="bfloat16", device="cuda", stored: torch.dtype = torch.bfloat16) -> Model:
+    """The model `load_model` would return for the folder that `write_random_model(folder, config,
+    seed)` writes, with the weights generated straight on the device and no file in between."""
+    from .. import models  # noqa: F401  (registers the architectures)
+
+    arch = resolve_architecture(config.to_dict())
+    spec = arch.build_spec(config)
+    expected, model = expected_weights(spec)
+    dt = run_dtype(dtype)
+    tensors = random_weights(expected, spec.aliases, seed, dt, torch.device(device), model.adjacent_weights(), stored)
     model.bind(tensors, dt, device)
     return model

@@ -47,7 +47,8 @@ def llama_spec(cfg: LlamaConfig) -> ModelSpec:
         head=PartSpec("linear", sizes, {"weight": embed_name if tied else "lm_head.weight"}),
         # a checkpoint without lm_head.weight shares the embedding table
         aliases={} if tied else {"lm_head.weight": embed_name},
-        ignorable=("lm_head.weight",) if tied else (),
+        # buffers that older exports store beside the parameters, and the head of a tied model
+        ignorable=("*.rotary_emb.inv_freq",) + (("lm_head.weight",) if tied else ()),
     )
 
 

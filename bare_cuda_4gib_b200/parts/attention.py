@@ -22,6 +22,7 @@ from ..kernels import lib as K
 from .base import KVCacheRequest, Part
 from .linear import Linear
 from .registry import build_part, register_mixer
+from ..weights.loader import fused_rows
 
 
 @register_mixer("attention")
@@ -45,6 +46,9 @@ class Attention(Part):
         return {"q": ((qd, self.hidden), "matrix"), "k": ((kvd, self.hidden), "matrix"),
                 "v": ((kvd, self.hidden), "matrix"), "o": ((self.hidden, qd), "matrix")}
 
+    def adjacent_weights(self):
+        return [("q", "k", "v")]
+
     def cache_request(self):
         return KVCacheRequest(self.kv_heads, self.head_dim, self.window)
 
@@ -53,9 +57,7 @@ class Attention(Part):
 
     def prepare(self, dtype, device) -> None:
         t = self.tensors
-        parts = [t.pop("q"), t.pop("k"), t.pop("v")]
-        widest = torch.float32 if any(w.dtype == torch.float32 for w in parts) else parts[0].dtype
-        self.qkv = Linear(torch.cat([w.to(widest) for w in parts], dim=0), "qkv")
+        self.qkv = Linear(fused_rows([t.pop("q"), t.pop("k"), t.pop("v")]), "qkv")
         self.o = Linear(t.pop("o"), "o")
         self.qkv.prepare(dtype)
         self.o.prepare(dtype)

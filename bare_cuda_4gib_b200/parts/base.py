@@ -78,6 +78,12 @@ class Part:
             out[local] = WeightSpec(self.spec.weights[local], tuple(shape), init)
         return out
 
+    def adjacent_weights(self) -> List[Tuple[str, ...]]:
+        """Groups of local tensor names that this part multiplies as one matrix, rows stacked in
+        this order: the loader places such tensors back to back, so that `weights.fused_rows` of
+        them is a view and not a copy."""
+        return []
+
     def bind(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype) -> None:
         """Receives the loaded tensors by local name; `dtype` is the step's activation type."""
         self.tensors = dict(tensors)

@@ -14,6 +14,7 @@ from ..kernels import lib as K
 from .base import Part
 from .linear import Linear
 from .registry import register_feed_forward
+from ..weights.loader import fused_rows
 
 
 @register_feed_forward("swiglu")
@@ -22,11 +23,12 @@ class SwiGLUFeedForward(Part):
         h, i = int(self.params["hidden"]), int(self.params["intermediate"])
         return {"gate": ((i, h), "matrix"), "up": ((i, h), "matrix"), "down": ((h, i), "matrix")}
 
+    def adjacent_weights(self):
+        return [("gate", "up")]
+
     def prepare(self, dtype, device) -> None:
         t = self.tensors
-        parts = [t.pop("gate"), t.pop("up")]
-        widest = torch.float32 if any(w.dtype == torch.float32 for w in parts) else parts[0].dtype
-        self.gate_up = Linear(torch.cat([w.to(widest) for w in parts], dim=0), "gate_up")
+        self.gate_up = Linear(fused_rows([t.pop("gate"), t.pop("up")]), "gate_up")
         self.down = Linear(t.pop("down"), "down")
         self.gate_up.prepare(dtype)
         self.down.prepare(dtype)

@@ -17,7 +17,7 @@ from typing import Dict
 import torch
 
 from ..parts.spec import WeightSpec
-from .loader import WEIGHT_FILE
+from .checkpoint import WEIGHT_FILE
 from .safetensors_io import write_safetensors
 
 MATRIX_STD = 0.02
@@ -31,15 +31,22 @@ def _generator(seed: int, name: str, device) -> torch.Generator:
     return g
 
 
+def random_tensor(spec: WeightSpec, seed: int, name: str, dtype: torch.dtype, device) -> torch.Tensor:
+    g = _generator(seed, name, device)
+    x = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
+    x = 1.0 + NORM_STD * x if spec.init == "norm" else MATRIX_STD * x
+    return x.to(dtype)
+
+
 def random_tensors(expected: Dict[str, WeightSpec], seed: int, dtype: torch.dtype = torch.bfloat16,
                    device="cpu") -> Dict[str, torch.Tensor]:
-    out = {}
-    for name, spec in sorted(expected.items()):
-        g = _generator(seed, name, device)
-        x = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
-        x = 1.0 + NORM_STD * x if spec.init == "norm" else MATRIX_STD * x
-        out[name] = x.to(dtype)
-    return out
+    return {name: random_tensor(spec, seed, name, dtype, device) for name, spec in sorted(expected.items())}
+
+
+def fill_random(dest: torch.Tensor, spec: WeightSpec, seed: int, name: str, stored: torch.dtype) -> None:
+    """Writes into `dest` what a folder written with this seed and stored type would load as
+    (generated on dest's device, rounded to the stored type first)."""
+    dest.copy_(random_tensor(spec, seed, name, stored, dest.device))
 
 
 def write_random_model(folder, config, seed: int, dtype: torch.dtype = torch.bfloat16, device="cpu") -> pathlib.Path:

@@ -42,7 +42,7 @@ class SafetensorsFile:
     def __init__(self, path):
         self.path = pathlib.Path(path)
         try:
-            self._file = open(self.path, "rb")
+            self._file = open(self.path, "rb", buffering=0)
         except OSError as e:
             raise WeightError(f"cannot open {self.path}: {e}") from e
         size = self.path.stat().st_size
@@ -52,8 +52,16 @@ class SafetensorsFile:
         (n,) = struct.unpack("<Q", head)
         if n <= 0 or 8 + n > size:
             raise WeightError(f"{self.path}: header length {n} exceeds the file ({size} bytes)")
+        def no_duplicates(pairs):
+            seen = {}
+            for key, value in pairs:
+                if key in seen:
+                    raise WeightError(f"{self.path}: tensor '{key}' is listed twice in the header")
+                seen[key] = value
+            return seen
+
         try:
-            header = json.loads(self._file.read(n).decode("utf-8"))
+            header = json.loads(self._file.read(n).decode("utf-8"), object_pairs_hook=no_duplicates)
         except (UnicodeDecodeError, json.JSONDecodeError) as e:
             raise WeightError(f"{self.path}: header is not valid JSON: {e}") from e
         if not isinstance(header, dict):
@@ -86,6 +94,21 @@ class SafetensorsFile:
         raw = np.frombuffer(self._map, dtype=np.uint8, count=e.end - e.begin,
                             offset=self.data_start + e.begin)
         return torch.from_numpy(raw.copy()).view(e.dtype).reshape(e.shape)
+
+    def read_into(self, name: str, out: np.ndarray, begin: int = 0) -> None:
+        """Reads `out.nbytes` bytes of the tensor's data, from byte `begin` of it, straight into
+        `out` (a contiguous uint8 array, for instance a view of pinned memory): no copy in between."""
+        e = self.entries[name]
+        if begin < 0 or begin + out.nbytes > e.end - e.begin:
+            raise WeightError(f"{self.path}: read of {out.nbytes} bytes at {begin} exceeds tensor '{name}'")
+        self._file.seek(self.data_start + e.begin + begin)
+        view = memoryview(out).cast("B")
+        got = 0
+        while got < out.nbytes:
+            n = self._file.readinto(view[got:])
+            if not n:
+                raise WeightError(f"{self.path}: file ended inside tensor '{name}'")
+            got += n
 
     def close(self) -> None:
         if self._map is not None:

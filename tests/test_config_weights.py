@@ -171,3 +171,131 @@ def test_random_weights_are_seeded_and_shaped():
         n = f3.tensor("model.norm.weight")
         assert abs(float(n.mean()) - 1.0) < 0.01 and float(n.std()) < 0.02
     assert json.loads((a1 / "config.json").read_text())["architectures"] == ["LlamaForCausalLM"]
+
+
+def _as_shards(src, dst, n_shards=3, index_extra=None, drop=None):
+    """Rewrites the single-file model folder `src` as `n_shards` shards plus an index in `dst`."""
+    from bare_cuda_4gib_b200.weights import SafetensorsFile, write_safetensors
+    with SafetensorsFile(src / "model.safetensors") as f:
+        tensors = {n: f.tensor(n) for n in f.entries}
+    names = sorted(tensors)
+    weight_map = {}
+    for i in range(n_shards):
+        shard = f"model-{i + 1:05d}-of-{n_shards:05d}.safetensors"
+        mine = {n: tensors[n] for n in names[i::n_shards]}
+        for n in mine:
+            weight_map[n] = shard
+        if drop != shard:
+            write_safetensors(dst / shard, mine)
+    weight_map.update(index_extra or {})
+    (dst / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": weight_map}))
+    (dst / "config.json").write_text((src / "config.json").read_text())
+    return tensors, weight_map
+
+
+def test_sharded_checkpoint_loads_bit_equal_to_the_single_file(tmp_path):
+    from bare_cuda_4gib_b200.engine.model import load_model
+    src = H.model_folder("B")
+    _as_shards(src, tmp_path, 3)
+    one, _ = load_model(src, "bfloat16", "cpu")
+    many, _ = load_model(tmp_path, "bfloat16", "cpu")
+    a = {id(p): p for p in one.all_parts()}
+    for p1, p2 in zip(one.all_parts(), many.all_parts()):
+        for name in p1.tensors:
+            assert torch.equal(p1.tensors[name], p2.tensors[name]), name
+    for b1, b2 in zip(one.blocks, many.blocks):
+        assert torch.equal(b1.mixer.qkv.weight, b2.mixer.qkv.weight) and torch.equal(b1.ffn.gate_up.weight, b2.ffn.gate_up.weight)
+
+
+def test_shard_problems_are_part_of_the_one_error(tmp_path):
+    from bare_cuda_4gib_b200.engine.model import load_model
+    from bare_cuda_4gib_b200.errors import WeightError
+    from bare_cuda_4gib_b200.weights import write_safetensors
+    src = H.model_folder("A")
+    missing_shard = "model-00002-of-00003.safetensors"
+    tensors, weight_map = _as_shards(src, tmp_path, 3, drop=missing_shard,
+                                     index_extra={"model.layers.9.ghost.weight": "model-00001-of-00003.safetensors"})
+    # a tensor that two shards hold
+    twice = next(n for n, s in weight_map.items() if s == "model-00001-of-00003.safetensors" and "ghost" not in n)
+    third = {n: tensors[n] for n, s in weight_map.items() if s == "model-00003-of-00003.safetensors"}
+    third[twice] = tensors[twice]
+    write_safetensors(tmp_path / "model-00003-of-00003.safetensors", third)
+    with pytest.raises(WeightError) as e:
+        load_model(tmp_path, "float32", "cpu")
+    text = str(e.value)
+    assert text.count("do not match the model") == 1
+    assert missing_shard in text and "cannot open" in text                         # the missing shard file
+    assert "ghost" in text and "does not hold it" in text                          # listed in the index, absent from its shard
+    assert f"'{twice}' is held by 2 shards" in text                                # present in two shards
+    assert "missing tensors" in text                                               # what the lost shard held
+    (tmp_path / "model.safetensors.index.json").write_text("{}")
+    with pytest.raises(WeightError, match="not a usable shard index"):
+        load_model(tmp_path, "float32", "cpu")
+
+
+def test_duplicate_name_in_a_header_is_refused(tmp_path):
+    from bare_cuda_4gib_b200.errors import WeightError
+    from bare_cuda_4gib_b200.weights import SafetensorsFile
+    header = ('{"t":{"dtype":"F32","shape":[2],"data_offsets":[0,8]},'
+              '"t":{"dtype":"F32","shape":[2],"data_offsets":[8,16]}}').encode()
+    bad = tmp_path / "model.safetensors"
+    bad.write_bytes(len(header).to_bytes(8, "little") + header + b"\0" * 16)
+    with pytest.raises(WeightError, match="listed twice"):
+        SafetensorsFile(bad)
+
+
+def test_weights_lie_in_one_arena_and_fused_matrices_are_views():
+    """Every tensor at a 1,024-byte offset of one allocation; [Wq; Wk; Wv] and [Wgate; Wup] back to
+    back, so the fused matrices are views; known non-parameter buffers are ignored."""
+    from bare_cuda_4gib_b200.engine.model import load_model
+    from bare_cuda_4gib_b200.weights.loader import ARENA_ALIGN
+    model, _ = load_model(H.model_folder("A"), "bfloat16", "cpu")
+    storages = set()
+    for part in model.all_parts():
+        for t in part.tensors.values():
+            storages.add(t.untyped_storage().data_ptr())
+    for block in model.blocks:
+        for lin in (block.mixer.qkv, block.mixer.o, block.ffn.gate_up, block.ffn.down):
+            storages.add(lin.weight.untyped_storage().data_ptr())
+            assert (lin.weight.data_ptr() - lin.weight.untyped_storage().data_ptr()) % ARENA_ALIGN == 0
+        assert block.mixer.qkv.weight.shape == (4 * 16 + 2 * 2 * 16, 64)
+    assert len(storages) == 1
+
+
+def test_rotary_buffers_of_old_exports_are_ignored(tmp_path):
+    from bare_cuda_4gib_b200.engine.model import load_model
+    from bare_cuda_4gib_b200.weights import SafetensorsFile, write_safetensors
+    src = H.model_folder("A")
+    with SafetensorsFile(src / "model.safetensors") as f:
+        tensors = {n: f.tensor(n) for n in f.entries}
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    (tmp_path / "config.json").write_text((src / "config.json").read_text())
+    write_safetensors(tmp_path / "model.safetensors", tensors)
+    load_model(tmp_path, "float32", "cpu")
+
+
+def test_random_model_without_a_file_equals_the_written_folder():
+    from bare_cuda_4gib_b200.engine.model import load_model, random_model
+    from bare_cuda_4gib_b200.config import LlamaConfig
+    for name, cfg in (("A", H.TINY_A), ("B", H.TINY_B)):
+        for dtype in ("bfloat16", "float32"):
+            a, _ = load_model(H.model_folder(name, 5), dtype, "cpu")
+            b = random_model(LlamaConfig.from_dict(cfg), 5, dtype, "cpu")
+            for p1, p2 in zip(a.all_parts(), b.all_parts()):
+                for n in p1.tensors:
+                    assert p1.tensors[n].dtype == p2.tensors[n].dtype and torch.equal(p1.tensors[n], p2.tensors[n]), n
+            assert torch.equal(a.blocks[0].mixer.qkv.weight, b.blocks[0].mixer.qkv.weight)
+
+
+def test_large_tensor_goes_through_the_staging_buffer_in_pieces(tmp_path, monkeypatch):
+    from bare_cuda_4gib_b200.weights import loader, write_safetensors
+    from bare_cuda_4gib_b200.parts.spec import WeightSpec
+    monkeypatch.setattr(loader, "STAGING_BYTES", 4096)
+    t = {"w": torch.randn(300, 77).to(torch.float16), "i": torch.arange(5000, dtype=torch.int64),
+         "f": torch.randn(3000)}
+    write_safetensors(tmp_path / "model.safetensors", t)
+    expected = {n: WeightSpec(n, tuple(x.shape)) for n, x in t.items()}
+    got = loader.load_weights(tmp_path, expected, {}, (), torch.bfloat16, "cpu")
+    assert got["w"].dtype == torch.bfloat16 and torch.equal(got["w"], t["w"].to(torch.bfloat16))
+    assert got["i"].dtype == torch.int32 and torch.equal(got["i"], t["i"].to(torch.int32))
+    assert got["f"].dtype == torch.float32 and torch.equal(got["f"], t["f"])
