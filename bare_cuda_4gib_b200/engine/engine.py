@@ -111,7 +111,8 @@ class LLMEngine:
                                  use_fast_attention=use_fast_attention, use_cuda_graphs=use_cuda_graphs)
         self.executor = ModelExecutor(self.runner)
         self.policy = policy
-        self.scheduler = Scheduler(self.cache, self.executor, max_step_tokens=self.max_step_tokens, policy=policy)
+        self.scheduler = Scheduler(self.cache, self.executor, max_step_tokens=self.max_step_tokens, policy=policy,
+                                   vocab_size=self.model.spec.vocab_size)
 
     # sizes, as the reference's model summary line reports them (bench/src/main.cc:83-88)
     @property

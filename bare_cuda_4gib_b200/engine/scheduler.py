@@ -129,10 +129,14 @@ class Scheduler:
     """Not thread-safe; one thread calls everything.  `executor.run(entries, params, rngs)` must
     return one sampled token per wanted row (see `engine.ModelExecutor`)."""
 
-    def __init__(self, cache: CacheManager, executor, *, max_step_tokens: int, policy: str = "reserve"):
+    def __init__(self, cache: CacheManager, executor, *, max_step_tokens: int, policy: str = "reserve",
+                 vocab_size: int = 0):
+        """`vocab_size` (when known): a prompt with an id outside it is refused at submission, not by
+        the step function in the middle of a batch that other requests share."""
         if policy not in ("reserve", "on_demand"):
             raise EngineError(f"unknown page policy '{policy}' (reserve or on_demand)")
         self.cache, self.executor, self.policy = cache, executor, policy
+        self.vocab_size = int(vocab_size)
         self.limits = EngineLimits(cache.max_tokens, cache.max_seqs,
                                    min((g.num_pages for g in cache.groups), default=0), int(max_step_tokens))
         self.waiting: Deque[_Live] = deque()
@@ -161,6 +165,9 @@ class Scheduler:
             return "max_new_tokens must be positive"
         if n > self.limits.max_tokens:
             return f"prompt has {n} tokens, the engine holds {self.limits.max_tokens} per sequence"
+        if self.vocab_size and not (0 <= min(request.prompt) and max(request.prompt) < self.vocab_size):
+            bad = next(t for t in request.prompt if not (0 <= t < self.vocab_size))
+            return f"token id {bad} is outside the vocabulary (0..{self.vocab_size - 1})"
         for gi, pages in enumerate(self.pages_needed(n, request.max_new_tokens)):
             total = self.cache.groups[gi].num_pages
             if pages > total:

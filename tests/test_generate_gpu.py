@@ -97,8 +97,10 @@ def test_async_engine_surface():
     try:
         assert engine.vocab_size == 256 and engine.max_seqs == 2 and engine.healthy
         assert engine.submit(1, [], 4)[0] == "invalid"
-        assert engine.submit(1, [1, 2, 3], 4) == ("ok", "")
-        assert engine.submit(1, [1, 2, 3], 4)[0] in ("invalid", "ok")   # duplicate while live is invalid
+        assert engine.submit(1, [1, 2, 3], 40) == ("ok", "")
+        status, message = engine.submit(1, [1, 2, 3], 4)       # 40 steps cannot have run yet: the id is live
+        assert status == "invalid" and "already live" in message
+        assert engine.submit(3, [1, 999], 4)[0] == "invalid"   # an id outside the vocabulary of 256
         assert engine.submit(2, [4, 5], 3, temperature=-1.0)[0] == "invalid"
         events = []
         for _ in range(200):
