@@ -567,6 +567,13 @@ extern "C" int llm_attention_mma_static_scratch(const void* q, void* out, void* 
   cudaError_t e = cudaGetDevice(&device);
   if (e != cudaSuccess) return 1000 + (int)e;
   if (device < 0 || device >= MAX_DEVICES) return ERR_BAD_SIZE;
+  // the array's address belongs to the current device: a stream of another device must not get it
+  int stream_device = device;
+  if (cudaStreamGetDevice(stream, &stream_device) == cudaSuccess) {
+    if (stream_device != device) return LLM_ERR_STATIC_SCRATCH_WRONG_DEVICE;
+  } else {
+    (void)cudaGetLastError();     // the runtime cannot tell (a capturing stream, say): the caller's word stands
+  }
   if (!g_static_scratch_address[device]) {
     float* address = nullptr;
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&address), g_static_scratch);
@@ -576,4 +583,10 @@ extern "C" int llm_attention_mma_static_scratch(const void* q, void* out, void* 
   return llm_attention_mma(q, out, k_base, v_base, block_table, page_stride, table_stride, page_tokens, kv_heads,
                            head_dim, seq_q_start, seq_q_len, seq_kv_len, tile_seq, tile_index, n_tiles,
                            rows_per_tile, n_splits, g_static_scratch_address[device], q_heads, scale, window, stream);
+}
+
+extern "C" float* llm_attention_static_scratch_address(void) {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= MAX_DEVICES) return nullptr;
+  return g_static_scratch_address[device];
 }

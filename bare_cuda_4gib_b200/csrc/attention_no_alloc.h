@@ -30,10 +30,25 @@
 //     call before (each split writes its whole partial output and its log-sum-exp before it counts
 //     itself done).
 //
+//   * After a call that did not run to its end (a CUDA error in its stream, a launch that was
+//     aborted) those counters may be left non-zero, and every later split call would then merge a
+//     tile too early.  After any CUDA error, clear the first 4096 words yourself before the next
+//     split call: cudaMemsetAsync on the address that llm_attention_static_scratch_address()
+//     returns (it is known once one call on this device has succeeded; a call with n_splits == 1
+//     is enough).
+//
 // Set-up.  The first call on each device looks up the array's device address
 // (cudaGetSymbolAddress, with that device current) and remembers it; this makes the first call
 // slower and is ordinary host-side CUDA runtime work, so make that first call before any stream
-// capture begins.  The function never calls cudaMalloc, cudaFree or any allocating library routine;
+// capture begins.  The address is looked up for the device that is CURRENT on the calling thread
+// (cudaGetDevice), so `stream` must be a stream of that device: a stream of another device would
+// hand the kernel an address that means nothing there (where the runtime can tell which device a
+// stream belongs to, such a call is refused with LLM_ERR_STATIC_SCRATCH_WRONG_DEVICE and nothing
+// is launched).  The remembered addresses are plain host variables: if several host threads may
+// make the first call on a device at the same time, make one call on that device first from one
+// thread (the look-up itself is idempotent, but the C++ memory model promises nothing for the race).
+//
+// The function never calls cudaMalloc, cudaFree or any allocating library routine;
 // inputs, outputs and the step's index arrays are the caller's, exactly as for llm_attention_mma.
 //
 // Arguments and return value are those of llm_attention_mma without the `scratch` pointer:
@@ -45,6 +60,7 @@
 
 #define LLM_ATTENTION_STATIC_SCRATCH_FLOATS (1 << 20)
 #define LLM_ERR_STATIC_SCRATCH_TOO_SMALL 4
+#define LLM_ERR_STATIC_SCRATCH_WRONG_DEVICE 5
 
 #ifdef __cplusplus
 extern "C" {
@@ -56,6 +72,10 @@ int llm_attention_mma_static_scratch(const void* q, void* out, void* k_base, voi
                                      const int32_t* seq_q_len, const int32_t* seq_kv_len, const int32_t* tile_seq,
                                      const int32_t* tile_index, int n_tiles, int rows_per_tile, int n_splits,
                                      int q_heads, float scale, int window, cudaStream_t stream);
+
+// The array's address on the current device (null before the first call on it, or on an error):
+// only for clearing the counters after a failed call, as described above.
+float* llm_attention_static_scratch_address(void);
 
 #ifdef __cplusplus
 }

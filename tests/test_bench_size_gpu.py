@@ -1,0 +1,163 @@
+"""Parity at the sizes the benchmark times: the TinyLlama-1.1B preset with all 22 layers and its
+vocabulary of 32,000, and a two-layer model of the same widths at a context of 2,048 positions,
+each against the plain implementation in float32 and bfloat16 and in every way of cutting the work
+(cuongvng/bare-cuda-4gib checks its whole model the same way: engine/tests/test_forward.cu:42-46
+compares logits, then greedy ids; engine/tests/test_kv_cache.cu:163-220 decodes 200 steps from the
+cache against the whole-sequence reference)."""
+
+import functools
+import random
+
+import pytest
+import torch
+
+import helpers as H
+import plain_llama as pl
+
+pytestmark = pytest.mark.gpu
+
+
+@functools.lru_cache(maxsize=None)
+def _tinyllama_22_layers():
+    from bare_cuda_4gib_b200.models.presets import preset_config
+    from bare_cuda_4gib_b200.weights import write_random_model
+
+    cfg = preset_config("tinyllama")
+    assert cfg.num_hidden_layers == 22 and cfg.vocab_size == 32000
+    folder = H.tmp_root() / "tinyllama-22-layers"
+    write_random_model(folder, cfg, 5, torch.bfloat16, "cuda")
+    return folder, cfg
+
+
+@functools.lru_cache(maxsize=None)
+def _two_layers_peaked(scale: float = 2.0):
+    """Two layers of the TinyLlama widths whose query and key projections are scaled up, so that
+    attention is peaked: with N(0, 0.02) weights every key weighs about 1/context and a lost or
+    stale key would move the logits by less than the bfloat16 tolerance."""
+    from bare_cuda_4gib_b200.models.presets import preset_config
+    from bare_cuda_4gib_b200.weights import SafetensorsFile, write_random_model, write_safetensors
+
+    cfg = preset_config("tinyllama", num_hidden_layers=2, vocab_size=2003)
+    folder = H.tmp_root() / "tinyllama-2-layers-peaked"
+    write_random_model(folder, cfg, 9, torch.bfloat16, "cuda")
+    with SafetensorsFile(folder / "model.safetensors") as f:
+        tensors = {n: f.tensor(n) for n in f.entries}
+    for name in tensors:
+        if name.endswith("q_proj.weight") or name.endswith("k_proj.weight"):
+            tensors[name] = (tensors[name].float() * scale).to(torch.bfloat16)
+    write_safetensors(folder / "model.safetensors", tensors)
+    return folder, cfg
+
+
+def _check(folder, requests, got, dtype):
+    worst = H.check_against_plain(folder, requests, got, dtype, expect_all=False)
+    return worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_tinyllama_all_22_layers_in_every_cutting(dtype):
+    folder, cfg = _tinyllama_22_layers()
+    rng = random.Random(41)
+    a, b = H.random_ids(rng, 128, cfg.vocab_size), H.random_ids(rng, 70, cfg.vocab_size)
+    requests = {"a": a, "b": b}
+    replay = H.Replayer(folder, dtype, 64, 4 * 128, max_live=4, shuffle_seed=5)
+    worst = {}
+    # whole
+    got = replay.run(H.trace_whole(requests))
+    worst["whole"] = _check(folder, requests, got, dtype)
+    # most in one step, the last 32 one by one
+    got = replay.run(H.trace_decode_tail(requests, 32))
+    worst["tail"] = _check(folder, requests, got, dtype)
+    # portions of changing size, down to two tokens
+    got = replay.run(H.trace_portions(requests, random.Random(2)))
+    worst["portions"] = _check(folder, requests, got, dtype)
+    # mixed: portions of one beside decoded tokens of the other
+    got = replay.run(H.trace_mixed(requests, random.Random(3), live=2, page=64))
+    worst["mixed"] = _check(folder, requests, got, dtype)
+    assert replay.cache.pages_in_use() == [0]
+    print(f"tinyllama 22 layers {dtype}: worst row errors {worst}")
+    # greedy ids after the logits, as the reference's whole-model test does
+    plain = H.plain_model(folder)
+    want = pl.greedy_decode(plain, a[:40], 8)
+    from bare_cuda_4gib_b200.engine.step import StepEntry
+    slot = replay.cache.acquire_slot()
+    ids, out = list(a[:40]), []
+    logits = replay.runner.step([StepEntry(slot, ids, [len(ids) - 1])])
+    for _ in range(8):
+        out.append(int(torch.argmax(logits[0])))
+        logits = replay.runner.step([StepEntry(slot, [out[-1]], [0])])
+    replay.cache.release_slot(slot)
+    if dtype == "float32":
+        assert out == want
+    else:   # a bfloat16 near-tie may pick the runner-up: follow the engine's own ids and judge each pick
+        ids = list(a[:40])
+        for t in out:
+            row = pl.forward_logits(plain, ids)[-1]
+            best = int(torch.argmax(row))
+            assert t == best or float(row[best] - row[t]) <= H.TOLERANCE[dtype] * float(row.abs().max())
+            ids.append(t)
+
+
+def _long_trace(ids_a, ids_b):
+    """a: 1,500 tokens in one step, then portions 300 / 2 / 130 / 36 / 48 up to 2,016, then 32 single
+    tokens at positions 2,016..2,047; b (a second request) joins with small portions and single
+    tokens beside a's decoded tokens."""
+    steps, n = [], 0
+
+    def add(entries, end=()):
+        nonlocal n
+        steps.append({"step": n, "entries": entries, "end": list(end)})
+        n += 1
+
+    add([{"id": "a", "tokens": ids_a[:1500], "want": [0, 700, 1499]}])
+    p = 1500
+    for size in (300, 2, 130, 36, 48):
+        add([{"id": "a", "tokens": ids_a[p: p + size], "want": [0, size - 1]}])
+        p += size
+    assert p == 2016
+    q, portions = 0, [3, 1, 1, 40, 1, 2, 1, 1, 17, 1]
+    while p < len(ids_a):
+        entries = [{"id": "a", "tokens": [ids_a[p]], "want": [0]}]
+        p += 1
+        if q < len(ids_b):
+            size = min(portions[(p - 2016) % len(portions)], len(ids_b) - q)
+            entries.append({"id": "b", "tokens": ids_b[q: q + size], "want": [size - 1]})
+            q += size
+        add(entries)
+    steps[-1]["end"] = ["a", "b"]
+    return steps
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_context_2048_whole_portions_and_decoded_tail(dtype):
+    folder, cfg = _two_layers_peaked()
+    rng = random.Random(77)
+    a, b = H.random_ids(rng, 2048, cfg.vocab_size), H.random_ids(rng, 100, cfg.vocab_size)
+    # one step of 2,048 rows; logits wanted at a few places only
+    whole = [{"step": 0, "entries": [{"id": "a", "tokens": a, "want": [0, 1, 511, 512, 1023, 1500, 2046, 2047]}], "end": ["a"]}]
+    replay = H.Replayer(folder, dtype, 64, 2048 + 128, max_live=2, shuffle_seed=4)
+    got = replay.run(whole)
+    worst_whole = _check(folder, {"a": a}, got, dtype)
+    steps = _long_trace(a, b)
+    got = replay.run(steps)
+    assert sum(1 for (r, p) in got if r == "a" and p >= 2016) == 32
+    worst_cut = _check(folder, {"a": a, "b": b}, got, dtype)
+    assert replay.cache.pages_in_use() == [0]
+    print(f"context 2048 {dtype}: whole {worst_whole:.3e}, cut {worst_cut:.3e}")
+
+
+def test_peaked_attention_makes_a_lost_key_visible():
+    """The premise of the model above: hiding only the oldest key from the last position of a
+    2,048-token context (a window of 2,047 in the plain implementation) moves that position's
+    logits by more than the bfloat16 tolerance, so the tests above would see a lost key."""
+    import copy
+    folder, cfg = _two_layers_peaked()
+    rng = random.Random(77)
+    a = H.random_ids(rng, 2048, cfg.vocab_size)
+    full = H.plain_logits(folder, a)[-1]
+    plain = copy.copy(H.plain_model(folder))
+    plain.layers = [copy.copy(layer) for layer in plain.layers]
+    for layer in plain.layers:
+        layer.window = 2047
+    without_oldest = pl.forward_logits(plain, a)[-1]
+    assert H.row_error(without_oldest, full) > H.TOLERANCE["bfloat16"]

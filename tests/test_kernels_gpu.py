@@ -312,10 +312,13 @@ def test_gemm_tcgen05_swiglu(m, inter, k):
 
 # ------------------------------------------------------------------------------ tensor-core attention
 
-def _attention_case(seqs, heads, kv_heads, d, page, window, seed, far_key=False, drop_passed=False):
+def _attention_case(seqs, heads, kv_heads, d, page, window, seed, far_key=False, drop_passed=False,
+                    poison_tail=True):
     """seqs: [(q_len, kv_len)].  Fills a scrambled paged cache, runs the attention the launcher picks
     and the dense reference.  `drop_passed` (with a window): pages that every query of the step has
-    passed are taken out of the block table and filled with NaN, as the cache manager gives them back."""
+    passed are taken out of the block table and filled with NaN, as the cache manager gives them back.
+    `poison_tail`: positions at and beyond a request's length in its last page hold NaN, as a page
+    may that an earlier, longer request left behind."""
     from bare_cuda_4gib_b200.kernels import attention as fast
     from bare_cuda_4gib_b200.kernels.lib import CacheView
 
@@ -346,6 +349,8 @@ def _attention_case(seqs, heads, kv_heads, d, page, window, seed, far_key=False,
             lo, hi = b * page, min(kv_len, (b + 1) * page)
             sv[pg, 0, :, : hi - lo] = k[lo:hi].transpose(0, 1)
             sv[pg, 1, :, : hi - lo] = v[lo:hi].transpose(0, 1)
+            if poison_tail and hi - lo < page:
+                sv[pg, :, :, hi - lo:] = float("nan")
         if drop_passed and window > 0:
             passed = max(0, kv_len - q_len - window + 1) // page      # blocks wholly below the first query's window
             for b in range(passed):
@@ -377,12 +382,17 @@ def _attention_case(seqs, heads, kv_heads, d, page, window, seed, far_key=False,
     gemm.check_errors()
     want = torch.zeros(n, heads, d, dtype=torch.float64, device=DEV)
     for s, (q_len, kv_len) in enumerate(seqs):
-        for i in range(q_len):
-            pos = kv_len - q_len + i
-            lo = max(0, pos - window + 1) if window > 0 else 0
-            for h in range(heads):
-                sc = (ks[s][lo: pos + 1, h // g].double() @ q[starts[s] + i, h].double()) * scale
-                want[starts[s] + i, h] = torch.softmax(sc, 0) @ vs[s][lo: pos + 1, h // g].double()
+        pos = torch.arange(kv_len - q_len, kv_len, device=DEV)[:, None]
+        key = torch.arange(kv_len, device=DEV)[None, :]
+        hidden = key > pos
+        if window > 0:
+            hidden = hidden | (key < pos - window + 1)
+        for kvh in range(kv_heads):          # one key/value head at a time keeps the score matrix small
+            qs = q[starts[s]: starts[s] + q_len, kvh * g: (kvh + 1) * g].double()            # [q, g, d]
+            sc = torch.einsum("qgd,kd->gqk", qs, ks[s][:, kvh].double()) * scale
+            sc = sc.masked_fill(hidden[None], float("-inf"))
+            want[starts[s]: starts[s] + q_len, kvh * g: (kvh + 1) * g] = \
+                torch.einsum("gqk,kd->qgd", torch.softmax(sc, -1), vs[s][:, kvh].double())
     return out.view(n, heads, d), want, ctx
 
 
@@ -415,6 +425,31 @@ def test_attention_mma_window_and_far_key():
         _close(got, want, 2 ** -7, 4e-3)
     # one early key dominates every query: the output must be that key's value row
     got, want, _ = _attention_case([(1, 900), (33, 500)], 8, 2, 64, 64, 0, seed=2, far_key=True)
+    _close(got, want, 2 ** -7, 4e-3)
+
+
+@pytest.mark.parametrize("d,heads,kv_heads", [(64, 8, 2), (128, 4, 2)])
+@pytest.mark.parametrize("page", [16, 64])
+def test_attention_tcgen05_long_contexts_random_data(d, heads, kv_heads, page):
+    """Random queries, keys and values at the lengths the benchmark runs: a whole 2,048-token
+    prompt, portions after long cached prefixes and a single row beside them.  The kernel's ring of
+    key/value stages and its two P buffers wrap many times here, and every key carries weight, so
+    a stale stage or a missed key shows in the values."""
+    from bare_cuda_4gib_b200.kernels import attention as fast
+    seqs = [(2048, 2048), (300, 1500), (5, 1900), (1, 1000), (130, 641)]
+    got, want, ctx = _attention_case(seqs, heads, kv_heads, d, page, 0, seed=d + page)
+    plan = fast.plan_for(d, heads, kv_heads)
+    assert plan.tc is not None and any(v[3] == plan.prefill_rows for k, v in ctx.extras.items())   # the tcgen05 kernel ran
+    _close(got, want, 2 ** -7, 4e-3)
+
+
+@pytest.mark.parametrize("d,heads,kv_heads,page", [(64, 32, 4, 64), (128, 8, 8, 16), (64, 6, 2, 32)])
+def test_attention_decode_long_contexts_random_data(d, heads, kv_heads, page):
+    """The cluster decode kernel over contexts of up to 2,048 keys of random data, requests of very
+    different lengths in one step, with NaN behind each request's last key."""
+    seqs = [(1, 2048), (1, 1), (1, 63), (1, 64), (1, 65), (1, 1337), (2, 2000), (1, 511)]
+    got, want, ctx = _attention_case(seqs, heads, kv_heads, d, page, 0, seed=3 * d + page)
+    assert any(v[5] > 0 for k, v in ctx.extras.items())       # the cluster decode kernel ran
     _close(got, want, 2 ** -7, 4e-3)
 
 

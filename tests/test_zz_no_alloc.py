@@ -3,9 +3,9 @@
 Some users of the library cannot allocate where attention runs (their program has given all GPU
 memory to an allocator of its own, or a cudaMalloc would stall their latency-critical loop), so
 `llm_attention_mma_static_scratch` keeps its scratch in a fixed array inside the library.  This
-test checks that it computes what the ordinary entry point computes, on two calls in a row (the
-second call finds the array full of the first call's data), and that it refuses a size that its
-array cannot hold.  It is collected last so that a run which stops at the first failure has
+test checks that it computes what the ordinary entry point computes - and what dense float64
+arithmetic over the same keys and values gives - on two calls in a row (the second call finds the
+array full of the first call's data), and that it refuses a size that its array cannot hold.  It is collected last so that a run which stops at the first failure has
 already run every other test; it does not depend on them.
 """
 
@@ -34,6 +34,7 @@ def _library(head_dim):
     lib.llm_attention_mma_static_scratch.restype = c_int
     lib.llm_attention_scratch_floats.argtypes = [I, I, I, I]
     lib.llm_attention_scratch_floats.restype = c_longlong
+    lib.llm_attention_static_scratch_address.restype = c_void_p
     return lib
 
 
@@ -56,6 +57,21 @@ def _decode_case(seed, kv_lens, heads, kv_heads, d, page):
     return dict(q=torch.randn(n, heads * d, device=DEV).to(torch.bfloat16), storage=storage, table=table,
                 elems=elems, q_start=i32(list(range(n))), q_len=i32([1] * n), kv_len=i32(kv_lens),
                 tile_seq=i32(list(range(n))), tile_index=i32([0] * n), n=n)
+
+
+def _dense(case, kv_lens, heads, kv_heads, d, page):
+    """The same attention as float64 matrix arithmetic over the gathered keys and values."""
+    g = heads // kv_heads
+    sv = case["storage"].view(-1, 2, kv_heads, page, d)
+    out = torch.zeros(case["n"], heads, d, dtype=torch.float64, device=DEV)
+    for s, kv in enumerate(kv_lens):
+        pages = case["table"][s, : -(-kv // page)].long()
+        k = sv[pages, 0].permute(1, 0, 2, 3).reshape(kv_heads, -1, d)[:, :kv].double()      # [kv_heads, kv, d]
+        v = sv[pages, 1].permute(1, 0, 2, 3).reshape(kv_heads, -1, d)[:, :kv].double()
+        q = case["q"][s].view(kv_heads, g, d).double()
+        p = torch.softmax(torch.einsum("hgd,hkd->hgk", q, k) / math.sqrt(d), -1)
+        out[s] = torch.einsum("hgk,hkd->hgd", p, v).reshape(heads, d)
+    return out.view(case["n"], heads * d)
 
 
 def _call(lib, case, heads, kv_heads, d, page, n_splits, static, scratch=None):
@@ -89,6 +105,12 @@ def test_static_scratch_entry_point_matches_the_ordinary_one_twice():
         # same kernels, same order of sums: the tolerance of the attention kernel tests is ample
         diff = (got.double() - want.double()).abs()
         assert bool((diff <= 4e-3 + 2 ** -7 * want.double().abs()).all()), float(diff.max())
+        # ... and against dense float64 arithmetic, which shares nothing with either entry point
+        dense = _dense(case, kv_lens, heads, kv_heads, d, page)
+        diff = (got.double() - dense).abs()
+        assert bool((diff <= 4e-3 + 2 ** -7 * dense.abs()).all()), float(diff.max())
+    address = lib.llm_attention_static_scratch_address()
+    assert address                                         # known after the calls above
 
 
 def test_static_scratch_refuses_what_its_array_cannot_hold():
