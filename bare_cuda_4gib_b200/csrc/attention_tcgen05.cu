@@ -2,28 +2,35 @@
 // of attention are tcgen05.mma with their accumulators in tensor memory.  It covers the prefill
 // shape of csrc/attention_mma.cu (same arguments, same packing of the query heads that share a
 // key/value head into the rows of a tile) for head sizes 64 and 128; the decode shape stays with
-// the mma.sync kernel.  As there, nothing of cuongvng/bare-cuda-4gib's [heads, T, keys] score
+// the cluster decode kernel.  As there, nothing of cuongvng/bare-cuda-4gib's [heads, T, keys] score
 // buffer exists (engine/kernels/attention_qk.cu:49-68, softmax.cu:28-42, attention_av.cu:24-44).
 //
-// One thread block = 128 packed rows of one request and one key/value head.  Keys are visited in
-// blocks of 128 positions:
-//   loader warp    one thread copies the block's keys and values from the request's pages into
-//                  128-byte-swizzled shared memory with TMA (one tensor map over the cache group's
-//                  whole pool, a box per page piece; four stages, two for head size 128);
-//   MMA thread     S = Q K^T (M 128, N 128, K head size) into tensor memory columns [0, 128);
-//   softmax warps  first stage Q with cp.async (all 256 threads, a few chunks each).  Then
-//                  two groups of four warps; group g takes the key blocks j with j % 2 == g and
-//                  keeps a running softmax of its own.  One thread per row: read the row of S from
-//                  tensor memory, scale, mask, running maximum and sum in float32 (base 2), write
-//                  P as bfloat16 into swizzled shared memory (the A operand of the second product);
-//   MMA thread     O_block = P V (M 128, N 64 per 64 value columns, K 128) into tensor memory;
+// One thread block = 256 packed rows of one request and one key/value head: two tiles of 128 rows
+// that see (almost) the same keys, so every key and value block is brought into shared memory once
+// for both.  Keys are visited in blocks of 128 positions:
+//   loader warp    copies the blocks' keys and values from the request's pages into 128-byte-
+//                  swizzled shared memory with TMA (one tensor map over the cache group's whole
+//                  pool, a box per page piece).  Key tiles and value tiles go through ONE ring of
+//                  slots in the order K(0) V(0) K(1) V(1) ..., each slot given back by the commit of
+//                  the last product that reads it (8 slots at head size 64, 3 at 128);
+//   MMA thread     S_g = Q_g K^T (M 128, N 128, K head size) into tile g's S columns of tensor memory;
+//   softmax warps  two groups of four warps; group g owns tile g and sees every key block of it.
+//                  First it stages Q_g with cp.async.  Then, one thread per row: read the row of S
+//                  from tensor memory, scale, mask, running maximum and sum in float32 (base 2, kept
+//                  in several independent partial maxima and sums so that no long dependent chain
+//                  forms), write P as bfloat16 into swizzled shared memory (the A operand of the
+//                  second product);
+//   MMA thread     O_block = P_g V (M 128, N 64 per 64 value columns, K 128) into tensor memory;
 //                  V stays as it lies in the cache ([key][channel]) and is described to the MMA as
 //                  an MN-major operand;
-//   softmax warps  O = O * correction + O_block, with O in registers, one block of the group late,
-//                  so nobody waits for the tensor core; at the end the two groups' (maximum, sum,
-//                  O) are merged through shared memory.
-// S, P and O_block exist once per group: while one group exponentiates (the special-function
-// units bound this kernel), the other reads its maxima or adds its O_block.
+//   softmax warps  O = O * correction + O_block, with O in registers, one block late, so nobody
+//                  waits for the tensor core; at the end every thread divides its row by its sum and
+//                  stores it: no merge between threads.
+// While one group exponentiates (the special-function units bound this kernel), the other reads
+// its maxima or adds its O_block, and the MMA thread serves whichever group is ready next.
+// A request's last page may hold, behind its last key, what an earlier request left there: masked
+// scores never see it, but 0 x NaN would reach O through P V, so the loader clears those value rows
+// in shared memory before the last block's P V may run.
 // Every mbarrier wait is bounded: on a timeout the thread sets the error word, all roles leave
 // their loops, tensor memory is released and the block returns.
 
@@ -41,13 +48,15 @@ namespace {
 constexpr int D = HEAD_DIM;
 static_assert(D == 64 || D == 128, "the tcgen05 attention kernel is built for head sizes 64 and 128");
 constexpr int KA = D / 64;       // 64-wide sub-tiles ("atoms") along the head dimension
-constexpr int BM = 128;          // packed rows per block
+constexpr int BM = 128;          // packed rows per tile (one softmax group)
+constexpr int TILES = 2;         // tiles per block
+constexpr int BLOCK_ROWS = TILES * BM;
 constexpr int BN = 128;          // keys per block
-constexpr int STAGES = D == 64 ? 4 : 2;   // key/value blocks in flight (what shared memory allows)
 constexpr int SUB = 128 * 128;   // bytes of a [128 rows x 64 bf16] swizzled sub-tile
-constexpr int Q_BYTES = KA * SUB;
-constexpr int KV_BYTES = 2 * KA * SUB;   // keys then values of one stage
-constexpr int P_BYTES = 2 * SUB;         // [128 rows x 128 keys] as two sub-tiles; two such buffers
+constexpr int Q_BYTES = KA * SUB;        // one tile's queries
+constexpr int TILE_BYTES = KA * SUB;     // one key tile or one value tile
+constexpr int P_BYTES = 2 * SUB;         // [128 rows x 128 keys] as two sub-tiles; one such buffer per group
+constexpr int SLOTS = D == 64 ? 8 : 3;   // key and value tiles in flight (what shared memory allows)
 constexpr int SOFTMAX_THREADS = 256, LOADER_THREADS = 32;
 constexpr int MMA_WARP = SOFTMAX_THREADS / 32;
 constexpr int NUM_THREADS = SOFTMAX_THREADS + 32 + LOADER_THREADS;   // warps 0-7 softmax, 8 MMA, 9 loader
@@ -55,8 +64,7 @@ constexpr int TMEM_COLS = 512;
 constexpr int O_COL = 256;       // first tensor-memory column of the P V results (S buffers at 0 and 128)
 constexpr int GROUP_THREADS = 128;
 constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;
-constexpr size_t SMEM_BYTES = Q_BYTES + STAGES * KV_BYTES + 2 * P_BYTES + 192;   // 17 barriers + 2 words
-static_assert((size_t)STAGES * KV_BYTES + 2 * P_BYTES >= (size_t)2 * 128 * (D + 2) * 4, "the merge area reuses the stages");
+constexpr size_t SMEM_BYTES = TILES * Q_BYTES + SLOTS * TILE_BYTES + TILES * P_BYTES + 256;   // 2 * SLOTS + 13 barriers, 2 words
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -187,21 +195,20 @@ constexpr int ERR_LOADER = 11, ERR_MMA = 12, ERR_SOFTMAX = 13, ERR_LAYOUT = 14;
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs a) {
   extern __shared__ __align__(1024) uint8_t smem[];   // swizzled tiles need 1024-byte alignment (checked below)
-  uint8_t* q_smem = smem;
-  uint8_t* kv_smem = q_smem + Q_BYTES;              // [STAGES][keys: KA sub-tiles | values: KA sub-tiles]
-  uint8_t* p_smem = kv_smem + STAGES * KV_BYTES;    // [2][two sub-tiles of 64 keys]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + 2 * P_BYTES);
-  uint64_t* q_full = bars;                // softmax threads -> MMA: Q staged
-  uint64_t* kv_full = bars + 1;           // [STAGES] loaders -> MMA
-  uint64_t* kv_empty = kv_full + STAGES;  // [STAGES] MMA (commit) -> loaders
-  uint64_t* s_full = kv_empty + STAGES;   // [2] MMA (commit) -> softmax, per S buffer
-  uint64_t* p_full = s_full + 2;          // [2] softmax -> MMA: P written and S consumed, per buffer
-  uint64_t* o_full = p_full + 2;          // [2] MMA (commit) -> softmax, per group
-  uint64_t* o_empty = o_full + 2;         // [2] softmax -> MMA: O_block consumed, per group
-  uint64_t* s_free = o_empty + 2;         // [2] softmax -> MMA: the group holds its S values in registers
-  uint64_t* done_bar = s_free + 2;        // softmax <-> softmax: both groups finished their blocks
-  uint64_t* merge_bar = done_bar + 1;     // softmax <-> softmax: both groups wrote their state
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(merge_bar + 1);
+  uint8_t* q_smem = smem;                              // [TILES][KA sub-tiles]
+  uint8_t* ring = q_smem + TILES * Q_BYTES;            // [SLOTS][KA sub-tiles]: key and value tiles in turn
+  uint8_t* p_smem = ring + SLOTS * TILE_BYTES;         // [TILES][two sub-tiles of 64 keys]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + TILES * P_BYTES);
+  uint64_t* tile_full = bars;               // [SLOTS] loader -> MMA: the slot's tile has landed
+  uint64_t* tile_empty = tile_full + SLOTS; // [SLOTS] MMA (commit) -> loader
+  uint64_t* q_full = tile_empty + SLOTS;    // [2] softmax group -> MMA: Q_g staged
+  uint64_t* s_full = q_full + 2;            // [2] MMA (commit) -> softmax, per group
+  uint64_t* p_full = s_full + 2;            // [2] softmax -> MMA: P written, per group
+  uint64_t* o_full = p_full + 2;            // [2] MMA (commit) -> softmax, per group
+  uint64_t* o_empty = o_full + 2;           // [2] softmax -> MMA: O_block consumed, per group
+  uint64_t* s_free = o_empty + 2;           // [2] softmax -> MMA: the group holds its S values in registers
+  uint64_t* v_clean = s_free + 2;           // loader -> MMA: the last value tile holds no stale rows
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(v_clean + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   pdl_launch_dependents();
@@ -217,41 +224,53 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
   // the most keys), then of the tile before it, ... so the longest blocks of the whole grid start first
   const int tile = gridDim.y - 1 - blockIdx.y, kvh = blockIdx.x;
   const int seq = a.tile_seq[tile];
-  int n_kb = 0, kb_lo = 0;
   int q_start = 0, q_len = 0, kv_len = 0, row0 = 0, n_rows = 0, pos0 = 0, group = 1;
-  int tile_min_pos = 0, tile_max_pos = 0;
+  // per group (tile of 128 rows): its key blocks [g_lo, g_hi) and the positions of its first and last row
+  int g_lo[TILES] = {0, 0}, g_hi[TILES] = {0, 0}, g_min_pos[TILES] = {0, 0}, g_max_pos[TILES] = {0, 0};
+  int kb_lo = 0, n_kb = 0;   // the union of the two ranges: what the loader brings
   if (seq >= 0) {
     group = a.q_heads / a.cache.kv_heads;
     q_start = a.seq_q_start[seq];
     q_len = a.seq_q_len[seq];
     kv_len = a.seq_kv_len[seq];
-    row0 = a.tile_index[tile] * BM;
+    row0 = a.tile_index[tile] * BLOCK_ROWS;
     n_rows = q_len * group;
     pos0 = kv_len - q_len;
-    const int last_token = min(q_len - 1, (row0 + BM - 1) / group), first_token = row0 / group;
-    tile_min_pos = pos0 + first_token;
-    tile_max_pos = pos0 + last_token;
-    const int lo_key = a.window > 0 ? max(0, tile_min_pos - a.window + 1) : 0;
-    kb_lo = lo_key / BN;
-    n_kb = tile_max_pos / BN - kb_lo + 1;
+    int lo_all = 1 << 30, hi_all = 0;
+#pragma unroll
+    for (int g = 0; g < TILES; ++g) {
+      const int first_row = row0 + g * BM;
+      if (first_row >= n_rows) continue;
+      const int first_token = first_row / group, last_token = min(q_len - 1, (first_row + BM - 1) / group);
+      g_min_pos[g] = pos0 + first_token;
+      g_max_pos[g] = pos0 + last_token;
+      const int lo_key = a.window > 0 ? max(0, g_min_pos[g] - a.window + 1) : 0;
+      g_lo[g] = lo_key / BN;
+      g_hi[g] = g_max_pos[g] / BN + 1;
+      lo_all = min(lo_all, g_lo[g]);
+      hi_all = max(hi_all, g_hi[g]);
+    }
+    if (hi_all > 0) kb_lo = lo_all, n_kb = hi_all - lo_all;
   }
+  // the key block that holds the request's last key, if positions behind that key share it
+  const int stale_block = (seq >= 0 && kv_len % BN != 0) ? (kv_len - 1) / BN : -1;
+  const bool clean_needed = stale_block >= kb_lo && stale_block < kb_lo + n_kb;
 
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&pool_map)) : "memory");
-    mbar_init(q_full, SOFTMAX_THREADS);
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+    for (int s = 0; s < SLOTS; ++s) {
+      mbar_init(&tile_full[s], 1);
+      mbar_init(&tile_empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
+      mbar_init(&q_full[b], GROUP_THREADS);
       mbar_init(&s_full[b], 1);
       mbar_init(&p_full[b], GROUP_THREADS);
       mbar_init(&o_full[b], 1);
       mbar_init(&o_empty[b], GROUP_THREADS);
       mbar_init(&s_free[b], GROUP_THREADS);
     }
-    mbar_init(done_bar, SOFTMAX_THREADS);
-    mbar_init(merge_bar, SOFTMAX_THREADS);
+    mbar_init(v_clean, LOADER_THREADS);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -267,125 +286,152 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
   const uint32_t tmem_base = *tmem_slot;
   if (warp > MMA_WARP) {
     // ------------------------------------------------------------------ loader warp
-    // Keys and values: one TMA box per piece of a page (a page holds box_rows or more positions
-    // of a key block).  A piece whose page is not held (given back by a window) is filled with
-    // zeros by the warp instead; its keys are masked, but stale shared memory must not reach P V.
+    // Tile n of the ring is the keys (n even) or the values (n odd) of key block n / 2: one TMA box
+    // per piece of a page (a page holds box_rows or more positions of a key block).  A piece whose
+    // page is not held (given back by a window), or that lies wholly behind the request's last key,
+    // is filled with zeros by the warp instead; its keys are masked, but stale shared memory must not
+    // reach P V.
     const int page_tokens = a.cache.page_tokens;
     const int32_t* table_row = a.cache.block_table + (long long)max(seq, 0) * a.cache.table_stride;
-    const int pieces = BN / a.box_rows;   // at most 16: lane p looks piece p up, lane 0 issues the copies
+    const int pieces = BN / a.box_rows;   // at most 16: lane p looks piece p up, lanes 0 and 1 issue the copies
+    const uint32_t piece_mask = (pieces < 32) ? ((1u << pieces) - 1u) : 0xffffffffu;
     const int page_shift = (page_tokens & (page_tokens - 1)) == 0 ? __ffs(page_tokens) - 1 : -1;
-    auto issue_block = [&](int j) {
-      const int s = j % STAGES;
-      const uint32_t k_base = smem_u32(kv_smem) + s * KV_BYTES, v_base = k_base + KA * SUB;
-      const int key0 = (kb_lo + j) * BN;
-      // lane p: the pool row of piece p's first position, or -1 if its page is not held
-      long long my_row = -1;
-      if (lane < pieces) {
-        const int key = key0 + lane * a.box_rows;
-        if (key < kv_len) {
-          const int block = page_shift >= 0 ? key >> page_shift : key / page_tokens;
-          const int in_page = page_shift >= 0 ? key & (page_tokens - 1) : key % page_tokens;
-          const int page = __ldg(table_row + block);
-          if (page >= 0) my_row = (long long)page * a.page_rows + (long long)kvh * page_tokens + in_page;
-        }
+    long long my_row = -1;     // lane p: the pool row (without the cache's K or V offset) of piece p, or -1
+    auto look_up = [&](int jj) {
+      const int key = (kb_lo + jj) * BN + lane * a.box_rows;
+      my_row = -1;
+      if (lane < pieces && key < kv_len) {
+        const int block = page_shift >= 0 ? key >> page_shift : key / page_tokens;
+        const int in_page = page_shift >= 0 ? key & (page_tokens - 1) : key % page_tokens;
+        const int page = __ldg(table_row + block);
+        if (page >= 0) my_row = (long long)page * a.page_rows + (long long)kvh * page_tokens + in_page;
       }
-      const uint32_t held = __ballot_sync(0xffffffffu, my_row >= 0) & ((pieces < 32) ? ((1u << pieces) - 1u) : 0xffffffffu);
-      const uint32_t missing = ~held & ((pieces < 32) ? ((1u << pieces) - 1u) : 0xffffffffu);
+    };
+    auto issue_tile = [&](int n) {
+      const int slot = n % SLOTS;
+      const uint32_t base = smem_u32(ring) + slot * TILE_BYTES;
+      const bool values = n & 1;
+      if (!values) look_up(n >> 1);    // the value tile that follows uses the same rows
+      const uint32_t held = __ballot_sync(0xffffffffu, my_row >= 0) & piece_mask;
+      const uint32_t missing = ~held & piece_mask;
       if (missing) {   // rare: zero the pieces without a page, and make the stores visible to the MMA
         for (int piece = 0; piece < pieces; ++piece) {
           if (!((missing >> piece) & 1u)) continue;
           for (int at = 0; at < KA; ++at)
-            for (int i = lane; i < a.box_rows * 8; i += 32) {
-              const uint32_t off = at * SUB + piece * a.box_rows * 128 + i * 16;
-              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(k_base + off), "r"(0) : "memory");
-              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(v_base + off), "r"(0) : "memory");
-            }
+            for (int i = lane; i < a.box_rows * 8; i += 32)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(base + at * SUB + piece * a.box_rows * 128 + i * 16), "r"(0) : "memory");
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
       }
-      if (lane == 0) mbar_expect_tx(&kv_full[s], (uint32_t)__popc(held) * 2u * KA * a.box_rows * 128u);   // also the one arrival
+      if (lane == 0) mbar_expect_tx(&tile_full[slot], (uint32_t)__popc(held) * KA * a.box_rows * 128u);   // also the one arrival
       __syncwarp();
-      // lane 0 issues the key copies, lane 1 the value copies: issuing is what takes the time
-      for (int piece = 0; piece < pieces; ++piece) {
+      const long long row0_of_cache = values ? a.v_row0 : a.k_row0;
+      for (int piece = 0; piece < pieces; ++piece) {     // lanes 0 and 1 take the pieces in turn: issuing is what takes the time
         const long long row = __shfl_sync(0xffffffffu, my_row, piece);
-        if (lane > 1 || row < 0) continue;
-        const uint32_t base = lane == 0 ? k_base : v_base;
-        const long long row0_of_cache = lane == 0 ? a.k_row0 : a.v_row0;
+        if (lane != (piece & 1) || row < 0) continue;
         for (int at = 0; at < KA; ++at)
-          tma_load_2d(base + at * SUB + piece * a.box_rows * 128, &pool_map, &kv_full[s], at * 64, (int)(row + row0_of_cache));
+          tma_load_2d(base + at * SUB + piece * a.box_rows * 128, &pool_map, &tile_full[slot], at * 64, (int)(row + row0_of_cache));
       }
     };
-    // Block j + 1 is requested as soon as its stage is free (the MMA thread frees it with P V of
-    // block j - 1, which it issues after S of block j).
     bool ok = true;
-    if (n_kb > 0) issue_block(0);
-    for (int j = 0; j + 1 < n_kb && ok; ++j) {
-      const int s1 = (j + 1) % STAGES;
-      const uint32_t use = (uint32_t)((j + 1) / STAGES);   // how often the stage was filled before
-      if (use > 0 && !mbar_wait(&kv_empty[s1], (use - 1) & 1, abort_flag)) {
-        if (lane == 0) {
-          *abort_flag = 1;
-          atomicCAS(a.error_word, 0, ERR_LOADER);
-        }
+    const int n_tiles = 2 * n_kb;
+    for (int n = 0; n < n_tiles && ok; ++n) {
+      const uint32_t use = (uint32_t)(n / SLOTS);   // how often the slot was filled before
+      if (use > 0 && !mbar_wait(&tile_empty[n % SLOTS], (use - 1) & 1, abort_flag)) {
         ok = false;
         break;
       }
-      issue_block(j + 1);
+      issue_tile(n);
     }
+    if (ok && clean_needed) {
+      // the value tile of the block with the request's last key: once it has landed, clear the rows
+      // behind that key (whole pieces behind it were never copied and are zero already)
+      const int n = 2 * (stale_block - kb_lo) + 1, slot = n % SLOTS;
+      ok = mbar_wait(&tile_full[slot], (n / SLOTS) & 1, abort_flag);
+      if (ok) {
+        const int first_stale = kv_len - stale_block * BN;           // 1 .. BN - 1
+        const int piece_end = min(BN, (first_stale + a.box_rows - 1) / a.box_rows * a.box_rows);
+        const uint32_t base = smem_u32(ring) + slot * TILE_BYTES;
+        for (int at = 0; at < KA; ++at)
+          for (int i = lane; i < (piece_end - first_stale) * 8; i += 32)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(base + at * SUB + first_stale * 128 + i * 16), "r"(0) : "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      }
+    }
+    if (!ok && lane == 0) {
+      *abort_flag = 1;
+      atomicCAS(a.error_word, 0, ERR_LOADER);
+    }
+    mbar_arrive(v_clean);      // in every case: the MMA thread must not wait in vain
   } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && n_kb > 0) {
       constexpr uint32_t idesc_s = instr_desc(BM, BN, 0);
       constexpr uint32_t idesc_o = instr_desc(BM, 64, 1);
-      const uint32_t q_addr = smem_u32(q_smem);
-      // S(j) = Q K(j)^T into the S buffer of block j's group
-      auto issue_s = [&](int j) -> bool {
-        const int s = j % STAGES, b = j & 1;
-        if (!mbar_wait(&kv_full[s], (j / STAGES) & 1, abort_flag)) return false;
+      // which group reads key block jj (of the union) last: its product gives the tile's slot back
+      auto active = [&](int g, int jj) { return kb_lo + jj >= g_lo[g] && kb_lo + jj < g_hi[g]; };
+      auto last_user = [&](int g, int jj) { return g == 1 || !active(1, jj); };
+      // S_g = Q_g K(jj)^T into group g's S buffer
+      auto issue_s = [&](int g, int jj) -> bool {
+        const int n = 2 * jj, slot = n % SLOTS;
+        if (!mbar_wait(&tile_full[slot], (n / SLOTS) & 1, abort_flag)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t k_addr = smem_u32(kv_smem) + s * KV_BYTES;
+        const uint32_t k_addr = smem_u32(ring) + slot * TILE_BYTES, q_addr = smem_u32(q_smem) + g * Q_BYTES;
 #pragma unroll
         for (int at = 0; at < KA; ++at)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_bf16(tmem_base + b * BN, smem_desc_sw128(q_addr + at * SUB) + 2 * k,
+            umma_bf16(tmem_base + g * BN, smem_desc_sw128(q_addr + at * SUB) + 2 * k,
                       smem_desc_sw128(k_addr + at * SUB) + 2 * k, idesc_s, (at > 0 || k > 0) ? 1u : 0u);
-        umma_commit(&s_full[b]);
+        umma_commit(&s_full[g]);
+        if (last_user(g, jj)) umma_commit(&tile_empty[slot]);
         return true;
       };
-      // O_block(j) = P(j) V(j) into the group's O_block, once the group has read its O_block(j - 2)
-      auto issue_pv = [&](int j) -> bool {
-        const int s = j % STAGES, b = j & 1;
-        if (j > 1 && !mbar_wait(&o_empty[b], ((j >> 1) - 1) & 1, abort_flag)) return false;
+      // O_block = P_g V(jj) into the group's O_block, once the group has read the one before (i: the
+      // group's own count of blocks)
+      auto issue_pv = [&](int g, int jj, int i) -> bool {
+        const int n = 2 * jj + 1, slot = n % SLOTS;
+        if (i > 0 && !mbar_wait(&o_empty[g], (i - 1) & 1, abort_flag)) return false;
+        if (!mbar_wait(&tile_full[slot], (n / SLOTS) & 1, abort_flag)) return false;
+        if (kb_lo + jj == stale_block && !mbar_wait(v_clean, 0, abort_flag)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t v_addr = smem_u32(kv_smem) + s * KV_BYTES + KA * SUB, p_addr = smem_u32(p_smem) + b * P_BYTES;
+        const uint32_t v_addr = smem_u32(ring) + slot * TILE_BYTES, p_addr = smem_u32(p_smem) + g * P_BYTES;
 #pragma unroll
         for (int vt = 0; vt < KA; ++vt)
 #pragma unroll
           for (int kk = 0; kk < BN / 16; ++kk)
-            umma_bf16(tmem_base + O_COL + b * D + vt * 64, smem_desc_sw128(p_addr + (kk >> 2) * SUB) + 2 * (kk & 3),
+            umma_bf16(tmem_base + O_COL + g * D + vt * 64, smem_desc_sw128(p_addr + (kk >> 2) * SUB) + 2 * (kk & 3),
                       smem_desc_sw128(v_addr + vt * SUB) + (uint64_t)(kk * 2048 >> 4), idesc_o, kk > 0 ? 1u : 0u);
-        umma_commit(&o_full[b]);
-        umma_commit(&kv_empty[s]);
+        umma_commit(&o_full[g]);
+        if (last_user(g, jj)) umma_commit(&tile_empty[slot]);
         return true;
       };
-      // Both groups get their first S at once.  A group reports when it holds S(j) in registers:
-      // its next S is issued then, while it still exponentiates; P V follows when it reports P(j).
-      // With two stages only, S(j + 2) needs the stage that P V of block j frees, so it comes after.
-      bool ok = mbar_wait(q_full, 0, abort_flag);
-      if (ok) ok = issue_s(0);
-      if (ok && n_kb > 1) ok = issue_s(1);
-      for (int j = 0; j < n_kb && ok; ++j) {
-        if (STAGES >= 3) {
-          ok = mbar_wait(&s_free[j & 1], (j >> 1) & 1, abort_flag);
-          if (ok && j + 2 < n_kb) ok = issue_s(j + 2);
-          if (ok) ok = mbar_wait(&p_full[j & 1], (j >> 1) & 1, abort_flag);
-          if (ok) ok = issue_pv(j);
-        } else {
-          ok = mbar_wait(&p_full[j & 1], (j >> 1) & 1, abort_flag);
-          if (ok) ok = issue_pv(j);
-          if (ok && j + 2 < n_kb) ok = issue_s(j + 2);
+      // Each group gets its first S at once.  A group reports when it holds S of a block in registers:
+      // its next S is issued then, while it still exponentiates; P V follows when it reports P.
+      bool ok = true;
+      bool started[TILES] = {false, false};
+#pragma unroll
+      for (int g = 0; g < TILES; ++g)
+        if (ok && g_hi[g] > g_lo[g] && g_lo[g] == kb_lo) {
+          ok = mbar_wait(&q_full[g], 0, abort_flag);
+          if (ok) ok = issue_s(g, 0);
+          started[g] = true;
+        }
+      for (int jj = 0; jj < n_kb && ok; ++jj) {
+#pragma unroll
+        for (int g = 0; g < TILES; ++g) {
+          if (!ok || !active(g, jj)) continue;
+          const int i = kb_lo + jj - g_lo[g];
+          if (!started[g]) {      // a group whose window starts a block later than the other's
+            ok = mbar_wait(&q_full[g], 0, abort_flag);
+            if (ok) ok = issue_s(g, jj);
+            started[g] = true;
+          }
+          if (ok) ok = mbar_wait(&s_free[g], i & 1, abort_flag);
+          if (ok && active(g, jj + 1)) ok = issue_s(g, jj + 1);
+          if (ok) ok = mbar_wait(&p_full[g], i & 1, abort_flag);
+          if (ok) ok = issue_pv(g, jj, i);
         }
       }
       if (!ok) {
@@ -398,36 +444,39 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax: two groups, one thread per row
-    // Q: 128 rows x D in 16-byte chunks, staged by all softmax threads (a few chunks each, so one
-    // round of global latency; one warp alone took most of a short block's time over it); rows past
-    // the request's packed rows are zero
-    for (int i = threadIdx.x; i < BM * (D / 8); i += SOFTMAX_THREADS) {
+    // ------------------------------------------------------------------ softmax: group g owns tile g, one thread per row
+    const int quad = warp & 3, g = warp >> 2;        // tensor-memory lanes 32 * quad ..
+    const int gt = threadIdx.x & (GROUP_THREADS - 1);
+    const int tile_row0 = row0 + g * BM;
+    // Q_g: 128 rows x D in 16-byte chunks, staged by the group's threads (a few chunks each, so one
+    // round of global latency); rows past the request's packed rows are zero
+    for (int i = gt; i < BM * (D / 8); i += GROUP_THREADS) {
       const int qr = i / (D / 8), c = i % (D / 8);
-      const int QR = row0 + qr;
+      const int QR = tile_row0 + qr;
       const bool valid = seq >= 0 && QR < n_rows;
       const int token = valid ? QR / group : 0, head = valid ? kvh * group + QR % group : 0;
       const __nv_bfloat16* src = a.q + ((long long)(q_start + token) * a.q_heads + head) * D + c * 8;
-      cp_async16(smem_u32(q_smem) + (c >> 3) * SUB + swizzled(qr, c & 7), src, valid);
+      cp_async16(smem_u32(q_smem) + g * Q_BYTES + (c >> 3) * SUB + swizzled(qr, c & 7), src, valid);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    mbar_arrive(q_full);
-    const int quad = warp & 3, g = warp >> 2;        // tensor-memory lanes 32 * quad ..; group g takes blocks j % 2 == g
+    mbar_arrive(&q_full[g]);
     const int r = quad * 32 + lane;                  // row of the tile = tensor-memory lane
-    const int R = row0 + r;
+    const int R = tile_row0 + r;
     const bool row_valid = seq >= 0 && R < n_rows;
     const int row_pos = row_valid ? pos0 + R / group : -1;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
     const uint32_t s_addr = lane_addr + g * BN, o_addr = lane_addr + O_COL + g * D;
+    const int my_lo = g_lo[g], my_n = g_hi[g] - g_lo[g];
+    const int tile_min_pos = g_min_pos[g], tile_max_pos = g_max_pos[g];
     float m = -INFINITY, l = 0.0f, corr_prev = 1.0f;
     float o[D];
 #pragma unroll
     for (int i = 0; i < D; ++i) o[i] = 0.0f;
-    // O = O * corr + O_block(j), once the MMA thread reports the group's O_block(j)
-    auto add_block = [&](int j, float corr) -> bool {
-      if (!mbar_wait(&o_full[g], (j >> 1) & 1, abort_flag) || *abort_flag) return false;
+    // O = O * corr + O_block(i), once the MMA thread reports the group's O_block(i)
+    auto add_block = [&](int i, float corr) -> bool {
+      if (!mbar_wait(&o_full[g], i & 1, abort_flag) || *abort_flag) return false;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
       for (int c0 = 0; c0 < D; c0 += 64) {
@@ -436,66 +485,70 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
         tmem_load32_nowait(o_addr + c0 + 32, v + 32);
         tmem_wait_loads();
 #pragma unroll
-        for (int i = 0; i < 64; ++i) o[c0 + i] = o[c0 + i] * corr + __uint_as_float(v[i]);
+        for (int k = 0; k < 64; ++k) o[c0 + k] = o[c0 + k] * corr + __uint_as_float(v[k]);
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       mbar_arrive(&o_empty[g]);
       return true;
     };
     bool ok = true;
-    int last = -1;
-    for (int j = g; j < n_kb && ok; j += 2) {
-      const int key0 = (kb_lo + j) * BN;
-      ok = mbar_wait(&s_full[g], (j >> 1) & 1, abort_flag) && !*abort_flag;
+    for (int i = 0; i < my_n && ok; ++i) {
+      const int key0 = (my_lo + i) * BN;
+      ok = mbar_wait(&s_full[g], i & 1, abort_flag) && !*abort_flag;
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const bool all_visible = key0 + BN - 1 <= tile_min_pos && (a.window <= 0 || key0 > tile_max_pos - a.window);
-      // pass 1: the row's maximum
-      float mx = -INFINITY;
+      // pass 1: the row's maximum, in four independent partial maxima
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         uint32_t v[64];
         tmem_load32_nowait(s_addr + h * 64, v);
         tmem_load32_nowait(s_addr + h * 64 + 32, v + 32);
         tmem_wait_loads();
-        if (all_visible) {
+        if (!all_visible) {
 #pragma unroll
-          for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 64; ++i) {
-            const int key = key0 + h * 64 + i;
+          for (int k = 0; k < 64; ++k) {
+            const int key = key0 + h * 64 + k;
             const bool visible = key <= row_pos && (a.window <= 0 || key > row_pos - a.window);
-            if (visible) mx = fmaxf(mx, __uint_as_float(v[i]));
+            if (!visible) v[k] = 0xff800000u;   // -inf
           }
         }
+#pragma unroll
+        for (int k = 0; k < 64; k += 8) {
+          mx0 = fmaxf(mx0, fmaxf(__uint_as_float(v[k]), __uint_as_float(v[k + 1])));
+          mx1 = fmaxf(mx1, fmaxf(__uint_as_float(v[k + 2]), __uint_as_float(v[k + 3])));
+          mx2 = fmaxf(mx2, fmaxf(__uint_as_float(v[k + 4]), __uint_as_float(v[k + 5])));
+          mx3 = fmaxf(mx3, fmaxf(__uint_as_float(v[k + 6]), __uint_as_float(v[k + 7])));
+        }
       }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       const float m_new = fmaxf(m, mx * a.scale_log2);       // scale > 0: the maximum commutes with it
       const float m_use = m_new == -INFINITY ? 0.0f : m_new;
       const float corr = fast_exp2(m - m_use);                 // m = -inf gives 0
       m = m_new;
-      l *= corr;
-      // pass 2: probabilities into shared memory as the A operand of P V (two sub-tiles of 64 keys)
+      // pass 2: probabilities into shared memory as the A operand of P V (two sub-tiles of 64 keys);
+      // the row's sum in four independent partial sums
+      float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         uint32_t v[64];
         tmem_load32_nowait(s_addr + h * 64, v);
         tmem_load32_nowait(s_addr + h * 64 + 32, v + 32);
         tmem_wait_loads();
-        if (h == 1) {   // the last read of S(j): the MMA thread may overwrite the buffer with S(j + 2)
+        if (h == 1) {   // the last read of S(i): the MMA thread may overwrite the buffer with S(i + 1)
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           mbar_arrive(&s_free[g]);
         }
-        // P(j) goes where P(j - 2) lay: the product that read it must be complete (its commit on
-        // o_full says so; O_block itself is added later, after P(j) is handed over).  Without this wait
-        // only the length of pass 1 kept the two apart.
-        if (h == 0 && last >= 0 && !mbar_wait(&o_full[g], (last >> 1) & 1, abort_flag)) ok = false;
+        // P(i) goes where P(i - 1) lay: the product that read it must be complete (its commit on
+        // o_full says so; O_block itself is added later, after P(i) is handed over)
+        if (h == 0 && i > 0 && !mbar_wait(&o_full[g], (i - 1) & 1, abort_flag)) ok = false;
         if (!all_visible) {
 #pragma unroll
-          for (int i = 0; i < 64; ++i) {
-            const int key = key0 + h * 64 + i;
+          for (int k = 0; k < 64; ++k) {
+            const int key = key0 + h * 64 + k;
             const bool visible = key <= row_pos && (a.window <= 0 || key > row_pos - a.window);
-            if (!visible) v[i] = 0xff800000u;   // -inf: probability 0
+            if (!visible) v[k] = 0xff800000u;   // -inf: probability 0
           }
         }
         uint8_t* p_tile = p_smem + g * P_BYTES + h * SUB;
@@ -506,60 +559,37 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
           for (int e = 0; e < 4; ++e) {
             const float p0 = fast_exp2(fmaf(__uint_as_float(v[ch * 8 + 2 * e]), a.scale_log2, -m_use));
             const float p1 = fast_exp2(fmaf(__uint_as_float(v[ch * 8 + 2 * e + 1]), a.scale_log2, -m_use));
-            l += p0 + p1;
+            if (e == 0) l0 += p0 + p1;
+            else if (e == 1) l1 += p0 + p1;
+            else if (e == 2) l2 += p0 + p1;
+            else l3 += p0 + p1;
             packed[e] = pack_bf16(p0, p1);
           }
           *reinterpret_cast<uint4*>(p_tile + swizzled(r, ch)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
         }
       }
+      l = l * corr + ((l0 + l1) + (l2 + l3));
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(&p_full[g]);
-      if (last >= 0) ok = add_block(last, corr_prev);   // the group's block before, whose P V ran meanwhile
+      if (i > 0) ok = ok && add_block(i - 1, corr_prev);   // the block before, whose P V ran meanwhile
       corr_prev = corr;
-      last = j;
     }
-    if (ok && last >= 0) ok = add_block(last, corr_prev);
+    if (ok && my_n > 0) ok = add_block(my_n - 1, corr_prev);
     if (!ok) {
       *abort_flag = 1;
       atomicCAS(a.error_word, 0, ERR_SOFTMAX);
     }
-    // ---- merge the two groups.  First everybody must be done with the stages (the MMAs that read
-    // them have all completed once both groups have added their last O_block), then each thread
-    // parks O of its row there as float4 units (unit i of row r in slot i ^ (r % units), so that the
-    // threads of a warp, who write the same unit of 32 rows, hit different banks) and (maximum, sum)
-    // behind them.  Then the threads take the units in order: a warp reads consecutive slots of a few
-    // rows and writes 256 contiguous bytes of the output (heads that share a key/value head lie side
-    // by side in a token's output row, as their rows do in the tile).
-    constexpr int UNITS = D / 4;                         // float4 units per row
-    float4* park = reinterpret_cast<float4*>(kv_smem);   // [2 groups][128 rows][UNITS]
-    float2* park_ml = reinterpret_cast<float2*>(park + 2 * 128 * UNITS);   // [2 groups][128 rows]
-    mbar_arrive(done_bar);
-    if (ok) ok = mbar_wait(done_bar, 0, abort_flag);
-    float4* mine = park + ((size_t)g * 128 + r) * UNITS;
+    // ---- every thread finishes its own row: O / l, rounded to bfloat16, 16 bytes at a time.  Heads
+    // that share a key/value head lie side by side in a token's output row, as their rows do in the tile.
+    if (ok && row_valid) {
+      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+      const int token = R / group, head = kvh * group + R % group;
+      uint4* dst = reinterpret_cast<uint4*>(a.out + ((long long)(q_start + token) * a.q_heads + head) * D);
 #pragma unroll
-    for (int i = 0; i < UNITS; ++i) mine[i ^ (r & (UNITS - 1))] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
-    park_ml[g * 128 + r] = make_float2(m, l);
-    mbar_arrive(merge_bar);
-    if (ok) ok = mbar_wait(merge_bar, 0, abort_flag);
-    if (ok && seq >= 0) {
-#pragma unroll
-      for (int q = threadIdx.x; q < BM * UNITS; q += SOFTMAX_THREADS) {
-        const int rr = q / UNITS, i = q % UNITS;
-        const int RR = row0 + rr;
-        if (RR >= n_rows) continue;
-        const float2 ml0 = park_ml[rr], ml1 = park_ml[128 + rr];
-        const float mm = fmaxf(ml0.x, ml1.x);
-        const float f0 = ml0.x == -INFINITY ? 0.0f : fast_exp2(ml0.x - mm), f1 = ml1.x == -INFINITY ? 0.0f : fast_exp2(ml1.x - mm);
-        const float total = ml0.y * f0 + ml1.y * f1;
-        const float inv = total > 0.0f ? 1.0f / total : 0.0f;
-        const float4 x0 = park[(size_t)rr * UNITS + (i ^ (rr & (UNITS - 1)))];
-        const float4 x1 = park[((size_t)128 + rr) * UNITS + (i ^ (rr & (UNITS - 1)))];
-        const int token = RR / group, head = kvh * group + RR % group;
-        uint2* dst = reinterpret_cast<uint2*>(a.out + ((long long)(q_start + token) * a.q_heads + head) * D + i * 4);
-        *dst = make_uint2(pack_bf16((x0.x * f0 + x1.x * f1) * inv, (x0.y * f0 + x1.y * f1) * inv),
-                          pack_bf16((x0.z * f0 + x1.z * f1) * inv, (x0.w * f0 + x1.w * f1) * inv));
-      }
+      for (int c = 0; c < D / 8; ++c)
+        dst[c] = make_uint4(pack_bf16(o[8 * c] * inv, o[8 * c + 1] * inv), pack_bf16(o[8 * c + 2] * inv, o[8 * c + 3] * inv),
+                            pack_bf16(o[8 * c + 4] * inv, o[8 * c + 5] * inv), pack_bf16(o[8 * c + 6] * inv, o[8 * c + 7] * inv));
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -605,12 +635,12 @@ extern "C" int llm_attention_tc_pool_map(void* map_out, const void* base, long l
 }
 
 extern "C" int llm_attention_tc_head_dim() { return D; }
-extern "C" int llm_attention_tc_rows() { return BM; }
+extern "C" int llm_attention_tc_rows() { return BLOCK_ROWS; }
 
 // Same arguments as llm_attention_mma without splits and scratch, plus the pool's tensor map
 // (llm_attention_tc_pool_map over `pool_base`, which k_base and v_base lie in, with boxes of
-// `box_rows` rows: a multiple of 8 that divides both 128 and the page size).  Every tile has 128
-// packed rows.
+// `box_rows` rows: a multiple of 8 that divides both 128 and the page size).  Every tile has 256
+// packed rows (llm_attention_tc_rows).
 extern "C" int llm_attention_tcgen05(const void* pool_map, const void* pool_base, int box_rows, const void* q, void* out,
                                      void* k_base, void* v_base, const int32_t* block_table,
                                      long long page_stride, int table_stride, int page_tokens, int kv_heads,

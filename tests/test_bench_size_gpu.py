@@ -29,24 +29,53 @@ def _tinyllama_22_layers():
     return folder, cfg
 
 
+PLANTED_TOKEN = 7      # the token id whose key, at position 0, every query of layer 0 looks at
+
+
 @functools.lru_cache(maxsize=None)
-def _two_layers_peaked(scale: float = 2.0):
-    """Two layers of the TinyLlama widths whose query and key projections are scaled up, so that
-    attention is peaked: with N(0, 0.02) weights every key weighs about 1/context and a lost or
-    stale key would move the logits by less than the bfloat16 tolerance."""
+def _two_layers_planted():
+    """Two layers of the TinyLlama widths in which one far key decides the logits.  With N(0, 0.02)
+    weights attention is near uniform, a key weighs about 1 / context, and a lost or stale key would
+    move the logits by less than the bfloat16 tolerance.  So layer 0 is given one score that stands
+    out: every token's embedding carries 1.0 in channel 0, only token PLANTED_TOKEN carries 1.0 in
+    channel 1, every head's query reads channel 0 into its feature 31 and every head's key reads
+    channel 1 into that feature (the feature with the slowest rotation: 0.27 rad over 2,048
+    positions).  A request that starts with PLANTED_TOKEN then has a score of about 30 on its first
+    key from every later position, and the attention output - one value row instead of the mean of
+    thousands - dominates the residual stream."""
     from bare_cuda_4gib_b200.models.presets import preset_config
     from bare_cuda_4gib_b200.weights import SafetensorsFile, write_random_model, write_safetensors
 
     cfg = preset_config("tinyllama", num_hidden_layers=2, vocab_size=2003)
-    folder = H.tmp_root() / "tinyllama-2-layers-peaked"
+    folder = H.tmp_root() / "tinyllama-2-layers-planted"
     write_random_model(folder, cfg, 9, torch.bfloat16, "cuda")
     with SafetensorsFile(folder / "model.safetensors") as f:
-        tensors = {n: f.tensor(n) for n in f.entries}
-    for name in tensors:
-        if name.endswith("q_proj.weight") or name.endswith("k_proj.weight"):
-            tensors[name] = (tensors[name].float() * scale).to(torch.bfloat16)
+        tensors = {n: f.tensor(n).clone() for n in f.entries}
+    d, feature = cfg.head_dim, cfg.head_dim // 2 - 1
+    embed = tensors["model.embed_tokens.weight"].float()
+    embed[:, 0] = 1.0
+    embed[:, 1] = 0.0
+    embed[PLANTED_TOKEN, 1] = 1.0
+    tensors["model.embed_tokens.weight"] = embed.to(torch.bfloat16)
+    wq = tensors["model.layers.0.self_attn.q_proj.weight"].float()
+    wk = tensors["model.layers.0.self_attn.k_proj.weight"].float()
+    for h in range(cfg.num_attention_heads):
+        wq[h * d + feature] = 0.0
+        wq[h * d + feature, 0] = 0.18
+    for h in range(cfg.num_key_value_heads):
+        wk[h * d + feature] = 0.0
+        wk[h * d + feature, 1] = 1.5
+    tensors["model.layers.0.self_attn.q_proj.weight"] = wq.to(torch.bfloat16)
+    tensors["model.layers.0.self_attn.k_proj.weight"] = wk.to(torch.bfloat16)
     write_safetensors(folder / "model.safetensors", tensors)
     return folder, cfg
+
+
+def _ids(rng, n, vocab, planted_first):
+    ids = [t if t != PLANTED_TOKEN else PLANTED_TOKEN + 1 for t in H.random_ids(rng, n, vocab)]
+    if planted_first:
+        ids[0] = PLANTED_TOKEN
+    return ids
 
 
 def _check(folder, requests, got, dtype):
@@ -130,9 +159,9 @@ def _long_trace(ids_a, ids_b):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_context_2048_whole_portions_and_decoded_tail(dtype):
-    folder, cfg = _two_layers_peaked()
+    folder, cfg = _two_layers_planted()
     rng = random.Random(77)
-    a, b = H.random_ids(rng, 2048, cfg.vocab_size), H.random_ids(rng, 100, cfg.vocab_size)
+    a, b = _ids(rng, 2048, cfg.vocab_size, True), _ids(rng, 100, cfg.vocab_size, False)
     # one step of 2,048 rows; logits wanted at a few places only
     whole = [{"step": 0, "entries": [{"id": "a", "tokens": a, "want": [0, 1, 511, 512, 1023, 1500, 2046, 2047]}], "end": ["a"]}]
     replay = H.Replayer(folder, dtype, 64, 2048 + 128, max_live=2, shuffle_seed=4)
@@ -146,18 +175,18 @@ def test_context_2048_whole_portions_and_decoded_tail(dtype):
     print(f"context 2048 {dtype}: whole {worst_whole:.3e}, cut {worst_cut:.3e}")
 
 
-def test_peaked_attention_makes_a_lost_key_visible():
+def test_planted_key_makes_a_lost_key_visible():
     """The premise of the model above: hiding only the oldest key from the last position of a
     2,048-token context (a window of 2,047 in the plain implementation) moves that position's
-    logits by more than the bfloat16 tolerance, so the tests above would see a lost key."""
+    logits by far more than the bfloat16 tolerance, so the test above would see a lost far key."""
     import copy
-    folder, cfg = _two_layers_peaked()
+    folder, cfg = _two_layers_planted()
     rng = random.Random(77)
-    a = H.random_ids(rng, 2048, cfg.vocab_size)
+    a = _ids(rng, 2048, cfg.vocab_size, True)
     full = H.plain_logits(folder, a)[-1]
     plain = copy.copy(H.plain_model(folder))
     plain.layers = [copy.copy(layer) for layer in plain.layers]
     for layer in plain.layers:
         layer.window = 2047
     without_oldest = pl.forward_logits(plain, a)[-1]
-    assert H.row_error(without_oldest, full) > H.TOLERANCE["bfloat16"]
+    assert H.row_error(without_oldest, full) > 10 * H.TOLERANCE["bfloat16"]

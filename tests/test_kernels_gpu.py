@@ -638,3 +638,4 @@ def test_gemv_fused_add_then_prenormed_input(tokens, hidden, inter):
     # without the request nothing is left
     gemv.run(ctx, w_down, act, tokens, torch.float32, "out", False, K.AddTo(residual))
     assert ctx.prenormed is None
+

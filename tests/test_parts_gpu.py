@@ -237,7 +237,7 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
     model.bind(tensors, torch.float32, "cuda")
     assert not model.graph_safe
     demands = model.cache_demands()
-    assert demands[0].kv is None and demands[0].state is not None and demands[1].kv is not None
+    assert demands[0][0].kv is None and demands[0][0].state is not None and demands[1][0].kv is not None
     runner, cache = _runner(model, 16, 64)
     assert cache.state_of(0) is not None and len(cache.groups) == 1 and cache.groups[0].members == [(1, 0)]
 
