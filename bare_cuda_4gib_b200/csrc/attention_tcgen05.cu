@@ -63,6 +63,7 @@ constexpr int NUM_THREADS = SOFTMAX_THREADS + 32 + LOADER_THREADS;   // warps 0-
 constexpr int TMEM_COLS = 512;
 constexpr int O_COL = 256;       // first tensor-memory column of the P V results (S buffers at 0 and 128)
 constexpr int GROUP_THREADS = 128;
+constexpr int S_PIECE = 64;      // columns of S a softmax thread holds in registers at a time (BN: the whole row, read once)
 constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;
 constexpr size_t SMEM_BYTES = TILES * Q_BYTES + SLOTS * TILE_BYTES + TILES * P_BYTES + 256;   // 2 * SLOTS + 13 barriers, 2 words
 
@@ -160,6 +161,17 @@ __device__ __forceinline__ void tmem_load32_nowait(uint32_t taddr, uint32_t* r) 
       : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_wait_loads() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_store32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_stores() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -205,8 +217,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
   uint64_t* s_full = q_full + 2;            // [2] MMA (commit) -> softmax, per group
   uint64_t* p_full = s_full + 2;            // [2] softmax -> MMA: P written, per group
   uint64_t* o_full = p_full + 2;            // [2] MMA (commit) -> softmax, per group
-  uint64_t* o_empty = o_full + 2;           // [2] softmax -> MMA: O_block consumed, per group
-  uint64_t* s_free = o_empty + 2;           // [2] softmax -> MMA: the group holds its S values in registers
+  uint64_t* s_free = o_full + 2;            // [2] softmax -> MMA: the group holds its S values in registers
   uint64_t* v_clean = s_free + 2;           // loader -> MMA: the last value tile holds no stale rows
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(v_clean + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -267,7 +278,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
       mbar_init(&s_full[b], 1);
       mbar_init(&p_full[b], GROUP_THREADS);
       mbar_init(&o_full[b], 1);
-      mbar_init(&o_empty[b], GROUP_THREADS);
       mbar_init(&s_free[b], GROUP_THREADS);
     }
     mbar_init(v_clean, LOADER_THREADS);
@@ -369,13 +379,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
     if (lane == 0 && n_kb > 0) {
       constexpr uint32_t idesc_s = instr_desc(BM, BN, 0);
       constexpr uint32_t idesc_o = instr_desc(BM, 64, 1);
-      // which group reads key block jj (of the union) last: its product gives the tile's slot back
       auto active = [&](int g, int jj) { return kb_lo + jj >= g_lo[g] && kb_lo + jj < g_hi[g]; };
-      auto last_user = [&](int g, int jj) { return g == 1 || !active(1, jj); };
-      // S_g = Q_g K(jj)^T into group g's S buffer
-      auto issue_s = [&](int g, int jj) -> bool {
-        const int n = 2 * jj, slot = n % SLOTS;
-        if (!mbar_wait(&tile_full[slot], (n / SLOTS) & 1, abort_flag)) return false;
+      // S_g = Q_g K(jj)^T into group g's S buffer; `last`: no product after this one reads the key tile
+      auto issue_s = [&](int g, int jj, bool last) {
+        const int slot = (2 * jj) % SLOTS;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t k_addr = smem_u32(ring) + slot * TILE_BYTES, q_addr = smem_u32(q_smem) + g * Q_BYTES;
 #pragma unroll
@@ -385,16 +392,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
             umma_bf16(tmem_base + g * BN, smem_desc_sw128(q_addr + at * SUB) + 2 * k,
                       smem_desc_sw128(k_addr + at * SUB) + 2 * k, idesc_s, (at > 0 || k > 0) ? 1u : 0u);
         umma_commit(&s_full[g]);
-        if (last_user(g, jj)) umma_commit(&tile_empty[slot]);
-        return true;
+        if (last) umma_commit(&tile_empty[slot]);
       };
-      // O_block = P_g V(jj) into the group's O_block, once the group has read the one before (i: the
-      // group's own count of blocks)
-      auto issue_pv = [&](int g, int jj, int i) -> bool {
-        const int n = 2 * jj + 1, slot = n % SLOTS;
-        if (i > 0 && !mbar_wait(&o_empty[g], (i - 1) & 1, abort_flag)) return false;
-        if (!mbar_wait(&tile_full[slot], (n / SLOTS) & 1, abort_flag)) return false;
-        if (kb_lo + jj == stale_block && !mbar_wait(v_clean, 0, abort_flag)) return false;
+      // O_g (+)= P_g V(jj): the group's O accumulates in tensor memory over its key blocks (`first`: overwrite)
+      auto issue_pv = [&](int g, int jj, bool last, bool first) {
+        const int slot = (2 * jj + 1) % SLOTS;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t v_addr = smem_u32(ring) + slot * TILE_BYTES, p_addr = smem_u32(p_smem) + g * P_BYTES;
 #pragma unroll
@@ -402,36 +404,50 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
 #pragma unroll
           for (int kk = 0; kk < BN / 16; ++kk)
             umma_bf16(tmem_base + O_COL + g * D + vt * 64, smem_desc_sw128(p_addr + (kk >> 2) * SUB) + 2 * (kk & 3),
-                      smem_desc_sw128(v_addr + vt * SUB) + (uint64_t)(kk * 2048 >> 4), idesc_o, kk > 0 ? 1u : 0u);
+                      smem_desc_sw128(v_addr + vt * SUB) + (uint64_t)(kk * 2048 >> 4), idesc_o, (kk > 0 || !first) ? 1u : 0u);
         umma_commit(&o_full[g]);
-        if (last_user(g, jj)) umma_commit(&tile_empty[slot]);
-        return true;
+        if (last) umma_commit(&tile_empty[slot]);
       };
-      // Each group gets its first S at once.  A group reports when it holds S of a block in registers:
-      // its next S is issued then, while it still exponentiates; P V follows when it reports P.
+      // The two groups are served as they come: a group's next S as soon as it reports that it holds the
+      // S before it in registers (and the key tile has landed), its P V as soon as it reports P (and has
+      // read the O_block before).  Nothing is waited for while the other group could be served.
       bool ok = true;
-      bool started[TILES] = {false, false};
-#pragma unroll
-      for (int g = 0; g < TILES; ++g)
-        if (ok && g_hi[g] > g_lo[g] && g_lo[g] == kb_lo) {
-          ok = mbar_wait(&q_full[g], 0, abort_flag);
-          if (ok) ok = issue_s(g, 0);
-          started[g] = true;
-        }
-      for (int jj = 0; jj < n_kb && ok; ++jj) {
+      int s_next[TILES] = {0, 0}, pv_next[TILES] = {0, 0};      // per group: its next block to issue S / P V for
+      const int n_g[TILES] = {g_hi[0] - g_lo[0], g_hi[1] - g_lo[1]};
+      auto landed = [&](int n) { return mbar_try_wait(&tile_full[n % SLOTS], (n / SLOTS) & 1); };
+      unsigned long long idle_since = 0;
+      unsigned idle_spins = 0;
+      while (ok && (pv_next[0] < n_g[0] || pv_next[1] < n_g[1])) {
+        bool progress = false;
 #pragma unroll
         for (int g = 0; g < TILES; ++g) {
-          if (!ok || !active(g, jj)) continue;
-          const int i = kb_lo + jj - g_lo[g];
-          if (!started[g]) {      // a group whose window starts a block later than the other's
-            ok = mbar_wait(&q_full[g], 0, abort_flag);
-            if (ok) ok = issue_s(g, jj);
-            started[g] = true;
+          const int o = 1 - g;
+          if (s_next[g] < n_g[g]) {
+            const int i = s_next[g], jj = g_lo[g] + i - kb_lo;
+            if ((i == 0 ? mbar_try_wait(&q_full[g], 0) : mbar_try_wait(&s_free[g], (i - 1) & 1)) && landed(2 * jj)) {
+              // the other group is done with K(jj) if it never reads it or has issued its S for it already
+              const bool last = !active(o, jj) || s_next[o] > kb_lo + jj - g_lo[o];
+              issue_s(g, jj, last);
+              s_next[g] = i + 1;
+              progress = true;
+            }
           }
-          if (ok) ok = mbar_wait(&s_free[g], i & 1, abort_flag);
-          if (ok && active(g, jj + 1)) ok = issue_s(g, jj + 1);
-          if (ok) ok = mbar_wait(&p_full[g], i & 1, abort_flag);
-          if (ok) ok = issue_pv(g, jj, i);
+          if (pv_next[g] < s_next[g]) {
+            const int i = pv_next[g], jj = g_lo[g] + i - kb_lo;
+            if (mbar_try_wait(&p_full[g], i & 1) && landed(2 * jj + 1) &&
+                (kb_lo + jj != stale_block || mbar_try_wait(v_clean, 0))) {
+              const bool last = !active(o, jj) || pv_next[o] > kb_lo + jj - g_lo[o];
+              issue_pv(g, jj, last, i == 0);
+              pv_next[g] = i + 1;
+              progress = true;
+            }
+          }
+        }
+        if (progress) {
+          idle_spins = 0;
+        } else if ((++idle_spins & 63u) == 0u) {
+          if (idle_spins == 64u) idle_since = global_timer();
+          if (*abort_flag || global_timer() - idle_since > WAIT_LIMIT_NS) ok = false;
         }
       }
       if (!ok) {
@@ -470,126 +486,145 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
     const uint32_t s_addr = lane_addr + g * BN, o_addr = lane_addr + O_COL + g * D;
     const int my_lo = g_lo[g], my_n = g_hi[g] - g_lo[g];
     const int tile_min_pos = g_min_pos[g], tile_max_pos = g_max_pos[g];
-    float m = -INFINITY, l = 0.0f, corr_prev = 1.0f;
-    float o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.0f;
-    // O = O * corr + O_block(i), once the MMA thread reports the group's O_block(i)
-    auto add_block = [&](int i, float corr) -> bool {
-      if (!mbar_wait(&o_full[g], i & 1, abort_flag) || *abort_flag) return false;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 64) {
-        uint32_t v[64];
-        tmem_load32_nowait(o_addr + c0, v);
-        tmem_load32_nowait(o_addr + c0 + 32, v + 32);
-        tmem_wait_loads();
-#pragma unroll
-        for (int k = 0; k < 64; ++k) o[c0 + k] = o[c0 + k] * corr + __uint_as_float(v[k]);
-      }
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(&o_empty[g]);
-      return true;
-    };
+    // Running softmax of the row.  `m` is the maximum the exponentials are taken against; it follows the
+    // true maximum only when that has grown by more than RESCALE_STEP (in base-2 units), so that O, which
+    // accumulates in tensor memory over all key blocks, has to be rescaled rarely: with a stale maximum
+    // the probabilities reach at most 2^RESCALE_STEP, and since sum and O are taken against the same `m`
+    // their quotient is exact either way.
+    constexpr float RESCALE_STEP = 8.0f;
+    float m = -INFINITY, l = 0.0f;
+    // this row of the group's P tile (swizzled: chunk c of row r lies at c ^ (r % 8) inside the row's 128 bytes)
+    const uint32_t p_row = smem_u32(p_smem) + g * P_BYTES + (r >> 3) * 1024 + (r & 7) * 128, p_xor = (uint32_t)(r & 7) << 4;
     bool ok = true;
-    for (int i = 0; i < my_n && ok; ++i) {
+    for (int i = 0; i < my_n; ++i) {
       const int key0 = (my_lo + i) * BN;
       ok = mbar_wait(&s_full[g], i & 1, abort_flag) && !*abort_flag;
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const bool all_visible = key0 + BN - 1 <= tile_min_pos && (a.window <= 0 || key0 > tile_max_pos - a.window);
-      // pass 1: the row's maximum, in four independent partial maxima
+      // S is read in pieces of S_PIECE columns: once for the row's maximum and, unless the whole row is
+      // kept in registers meanwhile (S_PIECE == BN), once more for the probabilities
+      uint32_t v[S_PIECE];
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      auto load_piece = [&](int h) {
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t v[64];
-        tmem_load32_nowait(s_addr + h * 64, v);
-        tmem_load32_nowait(s_addr + h * 64 + 32, v + 32);
+        for (int c = 0; c < S_PIECE; c += 32) tmem_load32_nowait(s_addr + h * S_PIECE + c, v + c);
         tmem_wait_loads();
         if (!all_visible) {
 #pragma unroll
-          for (int k = 0; k < 64; ++k) {
-            const int key = key0 + h * 64 + k;
+          for (int k = 0; k < S_PIECE; ++k) {
+            const int key = key0 + h * S_PIECE + k;
             const bool visible = key <= row_pos && (a.window <= 0 || key > row_pos - a.window);
-            if (!visible) v[k] = 0xff800000u;   // -inf
+            if (!visible) v[k] = 0xff800000u;   // -inf: probability 0
           }
         }
+      };
 #pragma unroll
-        for (int k = 0; k < 64; k += 8) {
+      for (int h = 0; h < BN / S_PIECE; ++h) {
+        load_piece(h);
+#pragma unroll
+        for (int k = 0; k < S_PIECE; k += 8) {   // four independent partial maxima
           mx0 = fmaxf(mx0, fmaxf(__uint_as_float(v[k]), __uint_as_float(v[k + 1])));
           mx1 = fmaxf(mx1, fmaxf(__uint_as_float(v[k + 2]), __uint_as_float(v[k + 3])));
           mx2 = fmaxf(mx2, fmaxf(__uint_as_float(v[k + 4]), __uint_as_float(v[k + 5])));
           mx3 = fmaxf(mx3, fmaxf(__uint_as_float(v[k + 6]), __uint_as_float(v[k + 7])));
         }
       }
-      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      const float m_new = fmaxf(m, mx * a.scale_log2);       // scale > 0: the maximum commutes with it
-      const float m_use = m_new == -INFINITY ? 0.0f : m_new;
-      const float corr = fast_exp2(m - m_use);                 // m = -inf gives 0
-      m = m_new;
-      // pass 2: probabilities into shared memory as the A operand of P V (two sub-tiles of 64 keys);
-      // the row's sum in four independent partial sums
+      if (S_PIECE == BN) {     // the row is in registers: the MMA thread may write S(i + 1) over it
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        mbar_arrive(&s_free[g]);
+      }
+      const float m_new = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * a.scale_log2);   // scale > 0: the maximum commutes with it
+      // tensor-memory loads and stores are warp-wide: the warp moves its maxima together, as soon as one of
+      // its rows has outgrown its own by the step (a row that has not may follow the true maximum just as well)
+      const bool move = __any_sync(0xffffffffu, m_new > m + RESCALE_STEP);
+      // P(i) goes where P(i - 1) lay, and O may only be touched between two products: the product
+      // before must be complete (its commit on o_full says so)
+      if (i > 0 && !mbar_wait(&o_full[g], (i - 1) & 1, abort_flag)) {
+        ok = false;
+        break;
+      }
+      if (move) {
+        const float corr = fast_exp2(m - (m_new == -INFINITY ? 0.0f : m_new));   // m = -inf gives 0
+        m = m_new;
+        l *= corr;
+        if (i > 0) {     // O = O * corr in tensor memory (the first product overwrites O, nothing to scale yet)
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t t[32];
+            tmem_load32_nowait(o_addr + c0, t);
+            tmem_wait_loads();
+#pragma unroll
+            for (int k = 0; k < 32; ++k) t[k] = __float_as_uint(__uint_as_float(t[k]) * corr);
+            tmem_store32(o_addr + c0, t);
+          }
+          tmem_wait_stores();
+        }
+      }
+      const float m_use = m == -INFINITY ? 0.0f : m;
+      // probabilities into shared memory as the A operand of P V (two sub-tiles of 64 keys); the row's
+      // sum in four independent partial sums
       float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t v[64];
-        tmem_load32_nowait(s_addr + h * 64, v);
-        tmem_load32_nowait(s_addr + h * 64 + 32, v + 32);
-        tmem_wait_loads();
-        if (h == 1) {   // the last read of S(i): the MMA thread may overwrite the buffer with S(i + 1)
-          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-          mbar_arrive(&s_free[g]);
-        }
-        // P(i) goes where P(i - 1) lay: the product that read it must be complete (its commit on
-        // o_full says so; O_block itself is added later, after P(i) is handed over)
-        if (h == 0 && i > 0 && !mbar_wait(&o_full[g], (i - 1) & 1, abort_flag)) ok = false;
-        if (!all_visible) {
-#pragma unroll
-          for (int k = 0; k < 64; ++k) {
-            const int key = key0 + h * 64 + k;
-            const bool visible = key <= row_pos && (a.window <= 0 || key > row_pos - a.window);
-            if (!visible) v[k] = 0xff800000u;   // -inf: probability 0
+      for (int h = 0; h < BN / S_PIECE; ++h) {
+        if (S_PIECE < BN) {
+          load_piece(h);
+          if (h == BN / S_PIECE - 1) {   // the last read of S(i): the MMA thread may overwrite the buffer with S(i + 1)
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(&s_free[g]);
           }
         }
-        uint8_t* p_tile = p_smem + g * P_BYTES + h * SUB;
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
+        for (int c = 0; c < S_PIECE / 8; ++c) {
+          const int chunk = h * (S_PIECE / 8) + c;       // 16-byte chunk of the row's 128 keys: sub-tile chunk / 8
           uint32_t packed[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(v[ch * 8 + 2 * e]), a.scale_log2, -m_use));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(v[ch * 8 + 2 * e + 1]), a.scale_log2, -m_use));
+            const float p0 = fast_exp2(fmaf(__uint_as_float(v[c * 8 + 2 * e]), a.scale_log2, -m_use));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(v[c * 8 + 2 * e + 1]), a.scale_log2, -m_use));
             if (e == 0) l0 += p0 + p1;
             else if (e == 1) l1 += p0 + p1;
             else if (e == 2) l2 += p0 + p1;
             else l3 += p0 + p1;
             packed[e] = pack_bf16(p0, p1);
           }
-          *reinterpret_cast<uint4*>(p_tile + swizzled(r, ch)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + (chunk >> 3) * SUB + (((chunk & 7) << 4) ^ p_xor)),
+                       "r"(packed[0]), "r"(packed[1]), "r"(packed[2]), "r"(packed[3]) : "memory");
         }
       }
-      l = l * corr + ((l0 + l1) + (l2 + l3));
+      l += (l0 + l1) + (l2 + l3);
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(&p_full[g]);
-      if (i > 0) ok = ok && add_block(i - 1, corr_prev);   // the block before, whose P V ran meanwhile
-      corr_prev = corr;
     }
-    if (ok && my_n > 0) ok = add_block(my_n - 1, corr_prev);
+    if (ok && my_n > 0) ok = mbar_wait(&o_full[g], (my_n - 1) & 1, abort_flag) && !*abort_flag;
     if (!ok) {
       *abort_flag = 1;
       atomicCAS(a.error_word, 0, ERR_SOFTMAX);
     }
-    // ---- every thread finishes its own row: O / l, rounded to bfloat16, 16 bytes at a time.  Heads
-    // that share a key/value head lie side by side in a token's output row, as their rows do in the tile.
-    if (ok && row_valid) {
+    // ---- every thread finishes its own row: O / l out of tensor memory, rounded to bfloat16, 64 bytes
+    // at a time.  Heads that share a key/value head lie side by side in a token's output row, as their
+    // rows do in the tile.  (The loads are warp-wide, so rows without an output still take part.)
+    if (ok && my_n > 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-      const int token = R / group, head = kvh * group + R % group;
+      const int token = row_valid ? R / group : 0, head = row_valid ? kvh * group + R % group : 0;
       uint4* dst = reinterpret_cast<uint4*>(a.out + ((long long)(q_start + token) * a.q_heads + head) * D);
 #pragma unroll
-      for (int c = 0; c < D / 8; ++c)
-        dst[c] = make_uint4(pack_bf16(o[8 * c] * inv, o[8 * c + 1] * inv), pack_bf16(o[8 * c + 2] * inv, o[8 * c + 3] * inv),
-                            pack_bf16(o[8 * c + 4] * inv, o[8 * c + 5] * inv), pack_bf16(o[8 * c + 6] * inv, o[8 * c + 7] * inv));
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t t[32];
+        tmem_load32_nowait(o_addr + c0, t);
+        tmem_wait_loads();
+        if (row_valid) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            dst[c0 / 8 + c] = make_uint4(pack_bf16(__uint_as_float(t[8 * c]) * inv, __uint_as_float(t[8 * c + 1]) * inv),
+                                         pack_bf16(__uint_as_float(t[8 * c + 2]) * inv, __uint_as_float(t[8 * c + 3]) * inv),
+                                         pack_bf16(__uint_as_float(t[8 * c + 4]) * inv, __uint_as_float(t[8 * c + 5]) * inv),
+                                         pack_bf16(__uint_as_float(t[8 * c + 6]) * inv, __uint_as_float(t[8 * c + 7]) * inv));
+        }
+      }
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

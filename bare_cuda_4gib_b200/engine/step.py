@@ -14,6 +14,7 @@ from that block, so a step of the same padded shape can be replayed as a CUDA gr
 
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -360,9 +361,19 @@ class StepRunner:
             return self._forward(c)               # first time: run directly (also sizes the workspace)
         graph = torch.cuda.CUDAGraph()
         before = K.LAUNCHES[0]
-        with torch.cuda.graph(graph):
-            c.stream = torch.cuda.current_stream().cuda_stream
-            logits = self._forward(c)
+        # Destroying a CUDA graph is not permitted while a stream captures, and Python's collector
+        # may do just that to the graphs of an engine that was dropped earlier: collect now, and keep
+        # the collector off until the capture has ended.
+        gc.collect()
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                c.stream = torch.cuda.current_stream().cuda_stream
+                logits = self._forward(c)
+        finally:
+            if collecting:
+                gc.enable()
         launched = K.LAUNCHES[0] - before
         K.LAUNCHES[0] = before
         c.stream = torch.cuda.current_stream().cuda_stream
