@@ -81,16 +81,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Waits for the phase with the given parity; gives up after WAIT_LIMIT_NS or when another role
+// Waits for the phase with the given parity; gives up after limit_ns or when another role
 // has already given up.  Returns false on giving up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long start = global_timer();
   for (unsigned spins = 0;; ++spins) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spins & 63u) == 63u) {
       if (*abort_flag) return false;
-      if (global_timer() - start > WAIT_LIMIT_NS) return false;
+      if (global_timer() - start > limit_ns) return false;
     }
   }
 }
@@ -154,13 +155,22 @@ struct Geometry {
   int stages;
   int tmem_cols;    // power of two >= bn * a_tiles, at least 32
   uint32_t idesc;
+  unsigned long long wait_ns;   // how long a role waits on an mbarrier before it gives up
+  int drop_k_block;             // tests only (llm_gemm_test_hooks): this k block's barrier is armed, its copies are left out
 };
 
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int MAX_STAGES = 8;
 
+// Set by llm_gemm_test_hooks: the wait limit of the launches that follow, and a k block whose copies
+// the producer of the non-persistent kernel leaves out, so that a test can watch a bounded wait run out.
+static unsigned long long g_wait_ns = WAIT_LIMIT_NS;
+static int g_drop_k_block = -1;
+
 static Geometry make_geometry(int bn, int mode, int orient, int blocks_per_sm) {
   Geometry g;
+  g.wait_ns = g_wait_ns;
+  g.drop_k_block = g_drop_k_block;
   g.bn = bn;
   g.a_tiles = 1;
   g.b_bytes = bn * BK * 2;
@@ -208,6 +218,7 @@ gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_
   auto issue_weights = [&](int i, int s, int which) {   // which: 0 = arm + first tile, 1 = second tile, 2 = both
     uint8_t* stage = smem + s * geo.stage_bytes;
     if (which != 1) mbar_expect_tx(&full_bar[s], geo.stage_bytes);
+    if (i == geo.drop_k_block) return;   // a test's way to leave a barrier waiting (never set otherwise)
     const int k0 = (kb_begin + i) * BK;
     if (ORIENT == 0) {
       if (which != 1) tma_load_2d(stage, &map_w, &full_bar[s], k0, f0);   // MODE 1: map_w's box has 64 rows
@@ -220,6 +231,7 @@ gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_
     }
   };
   auto issue_activations = [&](int i, int s) {
+    if (i == geo.drop_k_block) return;
     uint8_t* stage = smem + s * geo.stage_bytes;
     const int k0 = (kb_begin + i) * BK;
     if (ORIENT == 0) tma_load_2d(stage + geo.a_tiles * A_BYTES, &map_a, &full_bar[s], k0, t0);
@@ -266,7 +278,7 @@ gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_
       int s = n_early == geo.stages ? 0 : n_early;
       uint32_t phase = n_early == geo.stages ? 1 : 0;
       for (int i = n_early; i < n_kb; ++i) {
-        if (!mbar_wait(&empty_bar[s], phase ^ 1, abort_flag)) {
+        if (!mbar_wait(&empty_bar[s], phase ^ 1, abort_flag, geo.wait_ns)) {
           *abort_flag = 1;
           atomicCAS(error_word, 0, ERR_TIMEOUT_PRODUCER);
           break;
@@ -281,7 +293,7 @@ gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_
         for (int i = max(0, armed - geo.stages); i < armed; ++i) {
           const unsigned long long start = global_timer();
           while (!mbar_try_wait(&full_bar[i % geo.stages], (i / geo.stages) & 1) &&  // rare path
-                 global_timer() - start < WAIT_LIMIT_NS / 10) {
+                 global_timer() - start < geo.wait_ns / 10) {
           }
         }
       }
@@ -295,7 +307,7 @@ gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_
       uint32_t phase = 0;
       const uint32_t smem_base = smem_u32(smem);
       for (int i = 0; i < n_kb && ok; ++i) {
-        if (!mbar_wait(&full_bar[s], phase, abort_flag)) {
+        if (!mbar_wait(&full_bar[s], phase, abort_flag, geo.wait_ns)) {
           *abort_flag = 1;
           atomicCAS(error_word, 0, ERR_TIMEOUT_MMA);
           ok = false;
@@ -320,7 +332,7 @@ gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5)
     const int quad = warp & 3;  // tensor-memory lanes 32 * quad .. + 31 belong to this warp
-    bool ok = mbar_wait(tmem_full_bar, 0, abort_flag);
+    bool ok = mbar_wait(tmem_full_bar, 0, abort_flag, geo.wait_ns);
     if (!ok) {
       *abort_flag = 1;
       atomicCAS(error_word, 0, ERR_TIMEOUT_EPILOGUE);
@@ -543,7 +555,7 @@ gemm_tcgen05_persistent_kernel(const Geometry geo, const __grid_constant__ CUten
         const int f0 = (tile / t_tiles) * F_TILE, t0 = (tile % t_tiles) * BM;
         for (int i = 0; i < n_kb; ++i, ++q) {
           if ((q & 1) != turn) continue;
-          if (!mbar_wait(&empty_bar[s], phase ^ 1, abort_flag)) {
+          if (!mbar_wait(&empty_bar[s], phase ^ 1, abort_flag, geo.wait_ns)) {
             *abort_flag = 1;
             atomicCAS(error_word, 0, ERR_TIMEOUT_PRODUCER);
             ok = false;
@@ -570,7 +582,7 @@ gemm_tcgen05_persistent_kernel(const Geometry geo, const __grid_constant__ CUten
         for (int i = max(0, armed - geo.stages); i < armed; ++i) {
           const unsigned long long start = global_timer();
           while (!mbar_try_wait(&full_bar[i % geo.stages], (i / geo.stages) & 1) &&
-                 global_timer() - start < WAIT_LIMIT_NS / 10) {
+                 global_timer() - start < geo.wait_ns / 10) {
           }
         }
       }
@@ -584,7 +596,7 @@ gemm_tcgen05_persistent_kernel(const Geometry geo, const __grid_constant__ CUten
       bool ok = true;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++j) {
         const int buf = j & 1;
-        if (!mbar_wait(&acc_empty[buf], ((j >> 1) & 1) ^ 1, abort_flag)) {
+        if (!mbar_wait(&acc_empty[buf], ((j >> 1) & 1) ^ 1, abort_flag, geo.wait_ns)) {
           *abort_flag = 1;
           atomicCAS(error_word, 0, ERR_TIMEOUT_MMA);
           break;
@@ -592,7 +604,7 @@ gemm_tcgen05_persistent_kernel(const Geometry geo, const __grid_constant__ CUten
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t acc_addr = tmem_base + buf * ACC_COLS;
         for (int i = 0; i < n_kb; ++i) {
-          if (!mbar_wait(&full_bar[s], phase, abort_flag)) {
+          if (!mbar_wait(&full_bar[s], phase, abort_flag, geo.wait_ns)) {
             *abort_flag = 1;
             atomicCAS(error_word, 0, ERR_TIMEOUT_MMA);
             ok = false;
@@ -619,7 +631,7 @@ gemm_tcgen05_persistent_kernel(const Geometry geo, const __grid_constant__ CUten
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++j) {
       const int buf = j & 1;
       const int f0 = (tile / t_tiles) * F_TILE, t0 = (tile % t_tiles) * BM;
-      if (!mbar_wait(&acc_full[buf], (j >> 1) & 1, abort_flag) || *abort_flag) {
+      if (!mbar_wait(&acc_full[buf], (j >> 1) & 1, abort_flag, geo.wait_ns) || *abort_flag) {
         *abort_flag = 1;
         atomicCAS(error_word, 0, ERR_TIMEOUT_EPILOGUE);
         break;
@@ -791,6 +803,17 @@ extern "C" int llm_gemm_tensor_map(void* map_out, const void* base, long long ro
 // `accumulate` (orient 1, mode 0, float32 out, no split): out[t, f] += the product, which is how a
 // projection adds itself into the residual stream.
 // orient 0: bn tokens per tile; map_a's box must have bn rows, map_w's 128 (64 in mode 1).
+
+// For tests of the bounded waits: the launches that follow give up on an mbarrier after `wait_ns`
+// nanoseconds (0: the default of one second), and the producer of the non-persistent kernel arms
+// the barrier of k block `drop_k_block` of every tile without issuing its copies (-1: none), so the
+// MMA issuer's wait for it runs out: the kernel reports "MMA issuer" in the error word, releases its
+// tensor memory and returns.  Call with (0, -1) to put things back.
+extern "C" void llm_gemm_test_hooks(long long wait_ns, int drop_k_block) {
+  g_wait_ns = wait_ns > 0 ? (unsigned long long)wait_ns : WAIT_LIMIT_NS;
+  g_drop_k_block = drop_k_block;
+}
+
 // orient 1: bn weight rows per tile; map_a's box must have 128 rows, map_w's bn rows (bn / 2 in mode 1).
 extern "C" int llm_gemm_bf16(const void* map_w, const void* map_a, void* out, int out_dtype, int n_tokens,
                              int n_features, int K, long long ld_out, long long partial_stride, int splits,

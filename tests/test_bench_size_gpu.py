@@ -190,3 +190,29 @@ def test_planted_key_makes_a_lost_key_visible():
         layer.window = 2047
     without_oldest = pl.forward_logits(plain, a)[-1]
     assert H.row_error(without_oldest, full) > 10 * H.TOLERANCE["bfloat16"]
+
+
+def test_greedy_batch_on_the_planted_model_through_the_scheduler():
+    """Three requests of different lengths through the entry point in bfloat16: prompts in portions
+    under the step's token budget, then decode steps of three rows padded to four, captured as a
+    graph, with the scheduler a step ahead (token ids fed on the device).  Every request starts with
+    the planted token, so a request that lost its first key, or read another request's, would pick
+    other ids: each pick must be the plain implementation's, or within the bfloat16 tolerance of it."""
+    from bare_cuda_4gib_b200.engine.engine import LLMEngine
+
+    folder, cfg = _two_layers_planted()
+    rng = random.Random(5)
+    prompts = [_ids(rng, n, cfg.vocab_size, True) for n in (700, 300, 150)]
+    engine = LLMEngine(folder, max_tokens=1024, max_seqs=4, dtype="bfloat16", page_tokens=64)
+    got = engine.generate_batch(prompts, 12)
+    assert engine.scheduler.stats().as_dict()["kv_pages_used"] == 0
+    plain = H.plain_model(folder)
+    for prompt, ids in zip(prompts, got):
+        assert len(ids) == 12
+        seen = list(prompt)
+        for t in ids:
+            row = pl.forward_logits(plain, seen)[-1]
+            best = int(torch.argmax(row))
+            assert t == best or float(row[best] - row[t]) <= H.TOLERANCE["bfloat16"] * float(row.abs().max()), \
+                f"picked {t}, the plain implementation picks {best} at position {len(seen)}"
+            seen.append(t)

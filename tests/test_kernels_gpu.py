@@ -310,6 +310,42 @@ def test_gemm_tcgen05_swiglu(m, inter, k):
     _close(res.tensor, want, 2 ** -7, 1e-3)
 
 
+def test_a_bounded_wait_runs_out_and_the_kernel_returns():
+    """Every wait inside the pipelined kernels has a limit.  Here one is seen to run out: with the
+    test hooks of the GEMM library the producer arms one stage's barrier and issues no copy for it,
+    and the wait limit is 2 ms.  The MMA issuer must give up, say so in the error word, the kernel
+    must release its tensor memory and return on its own, and the next ordinary launch must be right."""
+    import time
+    from ctypes import c_int, c_longlong
+    from bare_cuda_4gib_b200.errors import KernelLaunchError
+    from bare_cuda_4gib_b200.kernels import gemm
+    torch.manual_seed(4)
+    m, n, k = 40, 256, 256                     # four k blocks, all in the ring at once: only the MMA issuer waits
+    ctx = _ctx()
+    a = ctx.ws.get("a", (m, k), torch.bfloat16)
+    a.copy_(torch.randn(m, k, device=DEV) * 0.5)
+    w = (torch.randn(n, k, device=DEV) * 0.2).to(torch.bfloat16)
+    plan = gemm.plan_for(w)
+    want = a.double() @ w.double().t()
+    gemm.check_errors()
+    hooks = gemm.lib().llm_gemm_test_hooks
+    hooks.argtypes, hooks.restype = [c_longlong, c_int], None
+    hooks(2_000_000, 2)
+    try:
+        started = time.time()
+        gemm.run(ctx, plan, a, m, torch.float32, "out", allow_partials=False, swiglu=False)
+        torch.cuda.synchronize()               # returns: nothing waits for ever
+        took = time.time() - started
+        with pytest.raises(KernelLaunchError, match="gemm MMA issuer"):
+            gemm.check_errors()
+    finally:
+        hooks(0, -1)
+    assert took < 1.0, f"the kernel took {took:.2f} s to give up"
+    res = gemm.run(ctx, plan, a, m, torch.float32, "out", allow_partials=False, swiglu=False)
+    gemm.check_errors()
+    _close(res.tensor, want, 1e-5, 2e-3)
+
+
 # ------------------------------------------------------------------------------ tensor-core attention
 
 def _attention_case(seqs, heads, kv_heads, d, page, window, seed, far_key=False, drop_passed=False,
