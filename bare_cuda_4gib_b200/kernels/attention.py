@@ -199,14 +199,15 @@ def step_tiles(ctx, plan: AttentionPlan):
     dec_splits = dec_slots = 0
     if use_decode:
         # The cluster decode kernel: up to 8 blocks of 4 warps share a tile, a warp keeps one key
-        # block in flight.  As many blocks per tile as still lets every block be resident at once
-        # (a block holds 4 key blocks in shared memory).  The number does not depend on the context
-        # length (a short context leaves some warps without a key block), so a captured graph of the
-        # step stays valid while the requests grow.
-        d = plan.head_dim       # shared memory of a block: alignment slack, 4 key blocks (K and V), Q, merge states, barriers
-        block_smem = 1024 + 4 * 2 * KEY_BLOCK * d * 2 + 16 * (d + 8) * 2 + 24 * (d + 4) * 4 + 128
-        resident = sm_count() * max(1, (227 * 1024) // block_smem)
-        dec_splits = max(1, min(8, resident // (n_tiles * plan.kv_heads)))
+        # block in flight.  Measured at a context of 2,048 (batches 8 to 64): the kernel is fastest
+        # with about two blocks per SM in all, and with a power of two of them per tile (batch 64:
+        # 26.7 us with one block per tile, 32 with two or four; batch 32: 13.4 us with two, 20.9 / 16.1 with
+        # one / four; batch 16: 8.5 us with four, 12.1 / 12.6 with two / eight).  The number does not depend
+        # on the context length (a short context leaves some warps without a key block), so a captured
+        # graph of the step stays valid while the requests grow.
+        dec_splits = 1
+        while dec_splits < 8 and n_tiles * plan.kv_heads * dec_splits * 2 <= 2 * sm_count():
+            dec_splits *= 2
         dec_slots = 1
         if os.environ.get("BARE_CUDA_B200_ATTN_SPLITS"):     # experiments only
             dec_splits = max(1, min(8, int(os.environ["BARE_CUDA_B200_ATTN_SPLITS"])))

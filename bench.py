@@ -191,6 +191,8 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-shapes", action="store_true", help="skip the Llama-2-7B / Llama-3-8B points")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--only", default="", choices=["", "prefill", "decode"],
+                    help="profiling aid: run just the prefill step or just the decode steps and print their time")
     args = ap.parse_args()
     args.repeats = max(1, args.repeats)
 
@@ -339,6 +341,13 @@ def main() -> int:
     max_batch = max(args.batch, 1 if args.no_points else 64)
     bench = Bench(args.preset, args.layers, max_batch)
     cfg = bench.cfg
+    if args.only:      # a short run for a profiler: one kind of step, nothing else
+        if args.only == "prefill":
+            r = bench.prefill(min(2048, context), args.repeats)
+        else:
+            r = bench.decode(args.batch, args.steps, warmup, args.repeats)
+        print(json.dumps({"only": args.only, "layers": bench.layers, "batch": args.batch, **r}))
+        return 0
     clocks = ClockSampler()
     clocks.start()
     main_run = bench.decode(args.batch, args.steps, warmup, args.repeats)
