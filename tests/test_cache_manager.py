@@ -151,3 +151,43 @@ def test_random_orders_of_requests(window):
     for s in list(live):
         m.release_slot(s)
     assert m.pages_in_use() == [0] and m.free_slots == 5
+
+
+def test_a_block_with_two_mixers_states_two_demands():
+    """A block defined here arranges an attention-like mixer beside a recurrent one: it states two
+    demands per run, the manager serves both, and a run that borrows another run's cache borrows
+    both - without a change to the generic model."""
+    import bare_cuda_4gib_b200.models  # noqa: F401
+    from bare_cuda_4gib_b200.config import LlamaConfig
+    from bare_cuda_4gib_b200.engine.model import Model
+    from bare_cuda_4gib_b200.models.llama import llama_spec
+    from bare_cuda_4gib_b200.parts import register_block
+    from bare_cuda_4gib_b200.parts.block import PreNormBlock
+    from bare_cuda_4gib_b200.parts.spec import LayerCall
+
+    @register_block("toy_two_mixers")
+    class TwoMixers(PreNormBlock):
+        def cache_demands(self):
+            return [(self.mixer.cache_request(), None),                       # the attention's pages
+                    (KVCacheRequest(1, 8, window=16), StateRequest((5,)))]    # a second mixer: a small windowed cache and state
+
+    cfg = LlamaConfig.from_dict(dict(architectures=["LlamaForCausalLM"], vocab_size=32, hidden_size=32, num_hidden_layers=2,
+                                     num_attention_heads=2, num_key_value_heads=1, head_dim=16, intermediate_size=48))
+    spec = llama_spec(cfg)
+    spec.layers[1].block = "toy_two_mixers"
+    spec.order = [LayerCall(0), LayerCall(1), LayerCall(1, cache_from=1)]
+    model = Model(spec)
+    demands = model.cache_demands()
+    assert [len(d) for d in demands] == [1, 2, 2] and demands[2][1].cache_from == 1
+    m = CacheManager(demands, page_tokens=8, max_seqs=2, max_tokens=32, allocate=True, device="cpu")
+    assert len(m.groups) == 2                                                  # attention pages; the windowed second cache
+    assert m.group_of(0) == (0, 0) and m.group_of(1) == (0, 1) and m.group_of(1, 1) == (1, 0)
+    assert m.group_of(2) == m.group_of(1) and m.group_of(2, 1) == m.group_of(1, 1)      # borrowed, both
+    assert m.state_of(1, 1).shape == (2 + 1, 5) and m.state_of(2, 1) is m.state_of(1, 1) and m.state_of(1, 0) is None
+    s = m.acquire_slot()
+    m.reserve(s, 20)
+    m.commit(s, 20)
+    m.check_consistency()
+    assert m.pages_in_use() == [3, 3]
+    m.release_slot(s)
+    assert m.pages_in_use() == [0, 0]

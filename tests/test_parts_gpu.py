@@ -401,3 +401,80 @@ def test_toy_position_encoding_and_routed_feed_forward_are_registered_built_and_
         assert H.row_error(got_a[p], want_a[p]) < 2e-5, p
     for p in range(18):
         assert H.row_error(got_b[p], want_b[p]) < 2e-5, p
+
+
+# ------------------------------------------------------------------------------ a graph-safe mixer with state, under padded decode steps
+
+
+def test_graph_safe_stateful_mixer_keeps_live_state_clean_when_a_decode_step_is_padded():
+    """A toy mixer whose state lives in the per-request slots and is updated on the device (so its
+    steps may be captured as CUDA graphs).  Three requests decode together; the step is padded to
+    four rows, captured on its second occurrence and replayed.  The idle row must update the spare
+    state row that no request owns: request 0 must get what it gets alone."""
+    from bare_cuda_4gib_b200.config import LlamaConfig
+    from bare_cuda_4gib_b200.engine.model import expected_weights
+    from bare_cuda_4gib_b200.engine.step import StepEntry
+    from bare_cuda_4gib_b200.kernels.lib import Partials
+    from bare_cuda_4gib_b200.models.llama import llama_spec
+    from bare_cuda_4gib_b200.parts import Part, PartSpec, StateRequest, register_mixer
+    from bare_cuda_4gib_b200.weights import random_tensors
+
+    @register_mixer("toy_running_mean_on_device")
+    class RunningMean(Part):
+        """state = decay * state + (1 - decay) * h, row by row in row order, with device-side indices
+        only: the host loop runs over the step's row count, which is part of a graph's key."""
+
+        def local_weights(self):
+            h = self.params["hidden"]
+            return {"out": ((h, h), "matrix")}
+
+        def cache_request(self):
+            return None
+
+        def state_request(self):
+            return StateRequest((self.params["hidden"],), torch.float32)
+
+        def forward(self, ctx, call, h):
+            decay = self.params["decay"]
+            out = ctx.ws.get("toy_out", (ctx.n_tokens, self.params["hidden"]), torch.float32)
+            slot_of_row = ctx.seq_slot.long()[ctx.row_seq[: ctx.n_tokens].long()]      # device indices
+            for r in range(ctx.n_tokens):
+                index = slot_of_row[r: r + 1]
+                state = call.state.index_select(0, index) * decay + h[r: r + 1].float() * (1.0 - decay)
+                call.state.index_copy_(0, index, state)
+                out[r: r + 1] = state @ self.tensors["out"].float().t()
+            return Partials(out)
+
+    cfg = LlamaConfig.from_dict(H.TINY_A)
+    spec = llama_spec(cfg)
+    decay = 0.5
+    spec.layers[0].mixer = PartSpec("toy_running_mean_on_device", {"hidden": cfg.hidden_size, "decay": decay},
+                                    {"out": "model.layers.0.toy.out.weight"})
+    expected, model = expected_weights(spec)
+    tensors = {k: v.to("cuda", torch.float32) for k, v in random_tensors(expected, seed=6).items()}
+    model.bind(tensors, torch.float32, "cuda")
+    assert model.graph_safe
+
+    def decode(batch_of, steps):
+        """Decodes `steps` fixed tokens for the given requests together; returns request 0's logits."""
+        runner, cache = _runner(model, 16, 64, max_live=4)
+        assert runner.use_cuda_graphs
+        slots = [cache.acquire_slot() for _ in batch_of]
+        assert slots[0] == 0
+        rows = []
+        for step in range(steps):
+            entries = [StepEntry(s, [(7 * i + 3 * step + 1) % cfg.vocab_size], [0]) for i, s in zip(batch_of, slots)]
+            rows.append(runner.step(entries)[0].float().cpu().clone())
+        captured = len(runner._graphs)
+        state0 = cache.state_of(0)[0].clone()
+        spare = cache.state_of(0)[cache.idle_slot].clone()
+        return torch.stack(rows), captured, state0, spare
+
+    alone, _, state_alone, spare_alone = decode([0], 6)
+    together, captured, state_together, spare_together = decode([0, 1, 2], 6)       # three rows, padded to four
+    assert captured >= 1                                      # the padded step ran as a captured graph
+    assert float(spare_alone.abs().sum()) == 0.0              # a batch of one is not padded
+    assert float(spare_together.abs().sum()) > 0.0            # the idle row did write: into the spare state row
+    assert torch.equal(state_alone, state_together)           # ... and nowhere else
+    for p in range(6):
+        assert H.row_error(together[p], alone[p]) < 2e-5, p
