@@ -185,6 +185,18 @@ static Geometry make_geometry(int bn, int mode, int orient, int blocks_per_sm) {
   return g;
 }
 
+// Streaming multiprocessors of the current device, asked once.
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n < 1)
+      n = 148;   // a B200
+  }
+  return n;
+}
+
 static size_t smem_bytes(const Geometry& g) { return (size_t)g.stages * g.stage_bytes + 1024 + 256; }
 
 template <int MODE, int ORIENT, int BLOCKS_PER_SM>
@@ -769,7 +781,7 @@ int launch_persistent(int bn, const CUtensorMap* map_w, const CUtensorMap* map_a
   const int f_tile = MODE == 1 ? bn / 2 : bn;
   const int f_tiles = (n_features + f_tile - 1) / f_tile, t_tiles = (n_tokens + BM - 1) / BM;
   const long long tiles = (long long)f_tiles * t_tiles;
-  const int grid = tiles < 148 ? (int)tiles : 148;
+  const int grid = tiles < sm_count() ? (int)tiles : sm_count();
   launch_kernel(kern, grid, NUM_THREADS, smem, stream, g, *map_w, *map_a, out, out_is_f32, n_tokens, n_features,
                 (K + BK - 1) / BK, ld_out, up_row_offset, f_tiles, t_tiles, error_word);
   return launch_status();
@@ -797,13 +809,6 @@ extern "C" int llm_gemm_tensor_map(void* map_out, const void* base, long long ro
   return r == CUDA_SUCCESS ? 0 : 2000 + (int)r;
 }
 
-// out[z][t, f] (z < splits) = partial sums of act[t, :] . w[f, :]; mode 1: silu(gate) * up with
-// w = [gate; up], the up rows starting at `up_row_offset` (splits must be 1 then).
-// `bn` is the N tile, a multiple of 16 up to 256 (of 32 for orient 1 with mode 1).
-// `accumulate` (orient 1, mode 0, float32 out, no split): out[t, f] += the product, which is how a
-// projection adds itself into the residual stream.
-// orient 0: bn tokens per tile; map_a's box must have bn rows, map_w's 128 (64 in mode 1).
-
 // For tests of the bounded waits: the launches that follow give up on an mbarrier after `wait_ns`
 // nanoseconds (0: the default of one second), and the producer of the non-persistent kernel arms
 // the barrier of k block `drop_k_block` of every tile without issuing its copies (-1: none), so the
@@ -814,6 +819,12 @@ extern "C" void llm_gemm_test_hooks(long long wait_ns, int drop_k_block) {
   g_drop_k_block = drop_k_block;
 }
 
+// out[z][t, f] (z < splits) = partial sums of act[t, :] . w[f, :]; mode 1: silu(gate) * up with
+// w = [gate; up], the up rows starting at `up_row_offset` (splits must be 1 then).
+// `bn` is the N tile, a multiple of 16 up to 256 (of 32 for orient 1 with mode 1).
+// `accumulate` (orient 1, mode 0, float32 out, no split): out[t, f] += the product, which is how a
+// projection adds itself into the residual stream.
+// orient 0: bn tokens per tile; map_a's box must have bn rows, map_w's 128 (64 in mode 1).
 // orient 1: bn weight rows per tile; map_a's box must have 128 rows, map_w's bn rows (bn / 2 in mode 1).
 extern "C" int llm_gemm_bf16(const void* map_w, const void* map_a, void* out, int out_dtype, int n_tokens,
                              int n_features, int K, long long ld_out, long long partial_stride, int splits,
@@ -837,13 +848,8 @@ extern "C" int llm_gemm_bf16(const void* map_w, const void* map_a, void* out, in
   const Geometry two = make_geometry(bn, mode, orient, 2);
   const long long f_tile = orient == 0 ? (mode == 1 ? BM / 2 : BM) : (mode == 1 ? bn / 2 : bn), t_tile = orient == 0 ? bn : BM;
   const long long tiles = ((n_features + f_tile - 1) / f_tile) * ((n_tokens + t_tile - 1) / t_tile) * splits;
-  const bool pair = tiles > 148 && two.tmem_cols <= 256 && two.stages >= ((orient == 1 && mode == 1) ? 2 : 3);
-  static int persistent_wish = -1;
-  if (persistent_wish < 0) {
-    const char* v = getenv("BARE_CUDA_B200_GEMM_PERSISTENT");
-    persistent_wish = (v && v[0] == '0') ? 0 : 1;
-  }
-  if (persistent_wish && orient == 1 && splits == 1 && tiles > 148 && bn >= 192) {
+  const bool pair = tiles > sm_count() && two.tmem_cols <= 256 && two.stages >= ((orient == 1 && mode == 1) ? 2 : 3);
+  if (orient == 1 && splits == 1 && tiles > sm_count() && bn >= 192) {
     // More tiles than SMs: one block per SM walks over them (see the persistent kernel).  Only for
     // wide tiles: a stage of a narrow tile is shorter on the tensor core than the one issuing
     // thread's round of waiting for it, issuing its instructions and committing, and then two

@@ -543,12 +543,7 @@ static bool plan_smem(int tokens, int k, int pro, size_t budget, int min_stages,
   if (tokens < 1 || tokens > 32 || k < 32 || k % 32) return false;
   const int nt = (tokens + 7) / 8;
   p.x_ld = k + ((k * 2) % 128 == 64 ? 0 : 32);
-  static int kc_wish = -1;
-  if (kc_wish < 0) {
-    const char* v = getenv("BARE_CUDA_B200_GEMV_KC");
-    kc_wish = v ? atoi(v) : 2048;
-    if (kc_wish < 32 || kc_wish % 32) kc_wish = 2048;
-  }
+  constexpr int kc_wish = 2048;   // the longest row piece of a stage: 4 KB per bulk copy (the copy unit's cost is per copy)
   const size_t fixed = (size_t)8 * nt * p.x_ld * 2 + (size_t)2 * WARPS * nt * 4 * 32 * 4 + SQ_SLOTS * 4 +
                        (pro == PRO_NORM ? (size_t)k * 4 : 0) + (2 * MAX_STAGES + 2) * 8 + 16;
   // the stage size: the longest piece of a row (k / n values, a multiple of 32, at most kc_wish)

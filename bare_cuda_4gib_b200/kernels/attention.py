@@ -86,7 +86,7 @@ class AttentionPlan:
         self.lib = lib(head_dim)
         self.prefill_rows = int(self.lib.llm_attention_prefill_rows())
         self.tc = None
-        if head_dim in TC_HEAD_DIMS and not os.environ.get("BARE_CUDA_B200_NO_TC_ATTENTION"):
+        if head_dim in TC_HEAD_DIMS:
             self.tc = tc_lib(head_dim)
             self.prefill_rows = int(self.tc.llm_attention_tc_rows())
         self.decode = None

@@ -21,7 +21,6 @@ PRO_BF16, PRO_NORM, PRO_PRENORMED = 0, 1, 2
 SQ_SLOTS = 32
 EPI_STORE, EPI_ADD, EPI_SWIGLU, EPI_ROPE = 0, 1, 2, 3
 MAX_TOKENS = int(os.environ.get("BARE_CUDA_B200_GEMV_MAX_TOKENS", "24"))     # measured: 24 rows still gain, 32 lose
-PRENORM = os.environ.get("BARE_CUDA_B200_GEMV_PRENORM", "1") not in ("0", "")
 _lib = None
 _smem: Dict[Tuple[int, int], int] = {}
 
@@ -84,7 +83,7 @@ def run(ctx, weight: torch.Tensor, x, rows: int, out_dtype: torch.dtype, buffer:
         out = ctx.ws.get(buffer, (rows, n_out), out_dtype)
     elif isinstance(epilogue, AddTo):
         epi, n_out, out = EPI_ADD, n, epilogue.residual
-        if epilogue.then_norm is not None and PRENORM:
+        if epilogue.then_norm is not None:
             pre_w = epilogue.then_norm.tensors["weight"]
             pre_x = ctx.ws.get("prenormed.x", (rows, n), torch.bfloat16, max_rows=MAX_TOKENS)
             pre_sq = ctx.ws.get("prenormed.sq", (-(-n // 16), SQ_SLOTS), torch.float32, max_rows=-(-n // 16))
