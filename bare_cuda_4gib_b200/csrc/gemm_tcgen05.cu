@@ -145,6 +145,207 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr));
 }
 
+// What the epilogue of the tokens-on-rows orientation may do beyond storing the product.
+struct RowsExtra {
+  // The input was prepared for a norm whose factor is one number per row (see AddTo / Prenormed in
+  // the launcher): it is bfloat16(residual * norm weight), and the factor rsqrt(mean of squares +
+  // eps) is applied here to the float32 sums.  `sq_in` [sq_items][sq_stride]: parts of every
+  // input row's sum of squares, added in index order.  Null: the input is what it is.
+  const float* sq_in;
+  int sq_items;
+  long long sq_stride;
+  float norm_width, eps;
+  // With `out` the float32 residual stream (accumulate): besides residual += product the epilogue
+  // leaves what the next norm's product needs: pre_x = bfloat16(new residual * pre_w) and this
+  // tile's part of every row's sum of squares in pre_sq[feature tile][row].  Null: neither.
+  __nv_bfloat16* pre_x;
+  long long pre_x_stride;
+  const void* pre_w;
+  int pre_w_dtype;
+  float* pre_sq;
+  long long pre_sq_stride;
+};
+
+constexpr int STAGING_BYTES = 4 * 32 * 32 * 4;   // per epilogue warp 32 rows of 32 float32, for the adding epilogue
+
+// The factor of the norm that the input rows were prepared for (1 without one).
+__device__ __forceinline__ float row_scale(const RowsExtra& ex, int t, int n_tokens) {
+  if (!ex.sq_in || t >= n_tokens) return 1.0f;
+  float sq = 0.0f;
+  for (int i = 0; i < ex.sq_items; ++i) sq += ex.sq_in[(long long)i * ex.sq_stride + t];
+  return 1.0f / sqrtf(sq / ex.norm_width + ex.eps);
+}
+
+// Epilogue of one warp for a tile with tokens on the tensor-memory lanes (lane = token, column =
+// feature): the warp's 32 tokens start at `t_first`, the tile's features at f0.  `lane_base` is
+// the tensor-memory address of the warp's lanes at the accumulator's first column; `have_acc`
+// false means an empty K range (zeros).  MODE 1: gate in column c, up in column BN/2 + c.
+// `wait_acc()` waits until the accumulator is complete (false: the block has given up, nothing is
+// stored); what does not depend on the accumulator is requested from memory before it is called.
+template <int MODE, int DEPTH, typename Wait>
+__device__ __forceinline__ void epilogue_tokens_on_rows(uint32_t lane_base, int BN, int F_TILE, int f0, int f_tile_index,
+                                                        int t_first, int lane, bool have_acc, void* out, int out_is_f32,
+                                                        long long ld_out, int n_tokens, int n_features,
+                                                        const RowsExtra& ex, float* staging, Wait&& wait_acc) {
+  float* out_f32 = reinterpret_cast<float*>(out);
+  __nv_bfloat16* out_bf16 = reinterpret_cast<__nv_bfloat16*>(out);
+  if (MODE == 0 && out_is_f32 == 2 && ex.pre_x) {
+    // ---- residual += product, with the next norm prepared.  A thread owns a token's row of the
+    // accumulator, but rows of the residual stream lie far apart in memory, so the warp passes 32
+    // columns at a time through shared memory (16-byte chunks swizzled by row, free of bank
+    // conflicts both ways) and then walks over them four rows per instruction, each row's 128
+    // bytes read and written by eight neighbouring lanes.  The old residual values and the norm's
+    // weights of DEPTH such chunks are in registers at any time: the first ones are requested
+    // while the tensor core still works on the tile, and a chunk's registers are refilled for
+    // the chunk DEPTH further on as soon as it is done, so the memory's latency is not waited for.
+    const int sub = lane >> 3, ch = lane & 7;
+    float sq_acc[8];
+#pragma unroll
+    for (int it = 0; it < 8; ++it) sq_acc[it] = 0.0f;
+    float4 old[DEPTH][8], w[DEPTH];
+    bool f_ok[DEPTH];
+    auto fetch = [&](int d, int cc) {     // (d is a constant wherever this is called)
+      const int f = f0 + cc + ch * 4;
+      f_ok[d] = cc < F_TILE && f + 4 <= n_features && cc + ch * 4 < F_TILE;   // (a tile's width is a multiple of 16)
+      w[d] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (f_ok[d]) {
+        if (ex.pre_w_dtype == DT_BF16) {
+          const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(ex.pre_w) + f);
+          const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+          const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+          w[d] = make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+        } else {
+          w[d] = *reinterpret_cast<const float4*>(static_cast<const float*>(ex.pre_w) + f);
+        }
+      }
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int t = t_first + it * 4 + sub;
+        old[d][it] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (f_ok[d] && t < n_tokens) old[d][it] = *reinterpret_cast<const float4*>(out_f32 + (long long)t * ld_out + f);
+      }
+    };
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d) fetch(d, 32 * d);
+    if (!wait_acc()) return;
+#pragma unroll 1
+    for (int c0 = 0; c0 < F_TILE; c0 += 32 * DEPTH) {
+      if (f0 + c0 >= n_features) break;   // uniform across the block
+#pragma unroll
+      for (int d = 0; d < DEPTH; ++d) {
+        const int cc = c0 + 32 * d, f = f0 + cc + ch * 4;
+        if (cc < F_TILE && f0 + cc < n_features) {   // uniform across the warp
+          uint32_t v[32];
+          if (have_acc) {
+            tmem_load16(lane_base + cc, *reinterpret_cast<uint32_t(*)[16]>(&v[0]));
+            tmem_load16(lane_base + cc + 16, *reinterpret_cast<uint32_t(*)[16]>(&v[16]));
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0u;
+          }
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<uint4*>(staging + lane * 32 + ((c ^ (lane & 7)) << 2)) =
+                make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int row = it * 4 + sub, t = t_first + row;
+            if (!f_ok[d] || t >= n_tokens) continue;
+            const float4 a = *reinterpret_cast<const float4*>(staging + row * 32 + ((ch ^ (row & 7)) << 2));
+            const float4 o4 = old[d][it];
+            const float4 now = make_float4(o4.x + a.x, o4.y + a.y, o4.z + a.z, o4.w + a.w);
+            *reinterpret_cast<float4*>(out_f32 + (long long)t * ld_out + f) = now;
+            const __nv_bfloat162 p01 = __floats2bfloat162_rn(now.x * w[d].x, now.y * w[d].y);
+            const __nv_bfloat162 p23 = __floats2bfloat162_rn(now.z * w[d].z, now.w * w[d].w);
+            uint2 packed;
+            packed.x = *reinterpret_cast<const uint32_t*>(&p01);
+            packed.y = *reinterpret_cast<const uint32_t*>(&p23);
+            *reinterpret_cast<uint2*>(ex.pre_x + (long long)t * ex.pre_x_stride + f) = packed;
+            sq_acc[it] += now.x * now.x;
+            sq_acc[it] += now.y * now.y;
+            sq_acc[it] += now.z * now.z;
+            sq_acc[it] += now.w * now.w;
+          }
+          __syncwarp();   // the staging rows are about to be overwritten
+          fetch(d, cc + 32 * DEPTH);
+        }
+      }
+    }
+    // a row's eight lanes add up (in a fixed order), the first of them writes this tile's part
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      float part = sq_acc[it];
+      part += __shfl_xor_sync(0xffffffffu, part, 1);
+      part += __shfl_xor_sync(0xffffffffu, part, 2);
+      part += __shfl_xor_sync(0xffffffffu, part, 4);
+      const int t = t_first + it * 4 + sub;
+      if (ch == 0 && t < n_tokens) ex.pre_sq[(long long)f_tile_index * ex.pre_sq_stride + t] = part;
+    }
+    return;
+  }
+  const int t = t_first + lane;
+  const float rs = row_scale(ex, t, n_tokens);
+  if (!wait_acc()) return;
+  const bool vec_ok = out_is_f32 ? (ld_out % 4 == 0 && (reinterpret_cast<uintptr_t>(out_f32) & 15) == 0)
+                                 : (ld_out % 8 == 0 && (reinterpret_cast<uintptr_t>(out_bf16) & 15) == 0);
+#pragma unroll 1
+  for (int c0 = 0; c0 < F_TILE; c0 += 16) {
+    if (f0 + c0 >= n_features) break;  // uniform across the block
+    uint32_t g[16], u[16];
+    if (have_acc) {
+      tmem_load16(lane_base + c0, g);
+      if (MODE == 1) tmem_load16(lane_base + BN / 2 + c0, u);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) g[j] = u[j] = 0u;
+    }
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      v[j] = __uint_as_float(g[j]) * rs;
+      if (MODE == 1) v[j] = v[j] / (1.0f + expf(-v[j])) * (__uint_as_float(u[j]) * rs);
+    }
+    if (t >= n_tokens) continue;
+    const int f = f0 + c0;
+    const long long at = (long long)t * ld_out + f;
+    if (vec_ok && f + 16 <= n_features) {
+      if (out_is_f32) {
+        float4* dst = reinterpret_cast<float4*>(out_f32 + at);
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          float4 w4 = make_float4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
+          if (out_is_f32 == 2) {   // accumulate: the output is the float32 residual stream
+            const float4 old = dst[q4];
+            w4.x += old.x, w4.y += old.y, w4.z += old.z, w4.w += old.w;
+          }
+          dst[q4] = w4;
+        }
+      } else {
+        uint32_t pk[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+          pk[j] = *reinterpret_cast<uint32_t*>(&b);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(out_bf16 + at);
+        dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (f + j < n_features) {
+          if (out_is_f32) out_f32[at + j] = out_is_f32 == 2 ? out_f32[at + j] + v[j] : v[j];
+          else out_bf16[at + j] = __float2bfloat16_rn(v[j]);
+        }
+      }
+    }
+  }
+}
+
 // Sizes of a launch that depend on the N tile `bn` (a run-time value: any multiple of 16 up to
 // 256, so that the number of tiles can be matched to the number of SMs).
 struct Geometry {
@@ -204,7 +405,7 @@ __global__ void __launch_bounds__(NUM_THREADS, BLOCKS_PER_SM)
 gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                     void* __restrict__ out, int out_is_f32, int n_tokens, int n_features, int k_blocks,
                     int k_blocks_per_split, long long ld_out, long long partial_stride, int up_row_offset,
-                    int* __restrict__ error_word) {
+                    const RowsExtra ex, int* __restrict__ error_word) {
   const int BN = geo.bn;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -344,18 +545,27 @@ gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5)
     const int quad = warp & 3;  // tensor-memory lanes 32 * quad .. + 31 belong to this warp
-    bool ok = mbar_wait(tmem_full_bar, 0, abort_flag, geo.wait_ns);
-    if (!ok) {
-      *abort_flag = 1;
-      atomicCAS(error_word, 0, ERR_TIMEOUT_EPILOGUE);
-    }
-    asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps agree on whether to go on
-    ok = !*abort_flag;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
-      const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
-      float* out_f32 = reinterpret_cast<float*>(out) + (long long)blockIdx.z * partial_stride;
-      __nv_bfloat16* out_bf16 = reinterpret_cast<__nv_bfloat16*>(out) + (long long)blockIdx.z * partial_stride;
+    auto wait_acc = [&]() -> bool {
+      bool ok = mbar_wait(tmem_full_bar, 0, abort_flag, geo.wait_ns);
+      if (!ok) {
+        *abort_flag = 1;
+        atomicCAS(error_word, 0, ERR_TIMEOUT_EPILOGUE);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps agree on whether to go on
+      ok = !*abort_flag;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      return ok;
+    };
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+    float* out_f32 = reinterpret_cast<float*>(out) + (long long)blockIdx.z * partial_stride;
+    __nv_bfloat16* out_bf16 = reinterpret_cast<__nv_bfloat16*>(out) + (long long)blockIdx.z * partial_stride;
+    if (ORIENT == 1) {
+      // (the pipeline's stages are idle once the accumulator is complete: the adding epilogue passes its tiles through them)
+      epilogue_tokens_on_rows<MODE, BLOCKS_PER_SM == 1 ? 4 : 1>(
+          lane_base, BN, F_TILE, f0, blockIdx.x, t0 + quad * 32, lane, n_kb > 0,
+          out_is_f32 ? static_cast<void*>(out_f32) : static_cast<void*>(out_bf16), out_is_f32, ld_out, n_tokens, n_features,
+          ex, reinterpret_cast<float*>(smem) + quad * (32 * 32), wait_acc);
+    } else if (wait_acc()) {
       if (ORIENT == 0 && MODE == 1) {
         // lanes 0..63 hold gate, lanes 64..127 up, for the block's 64 output features: the up warps
         // park their values in shared memory (the pipeline stages are idle by now), [token][feature]
@@ -426,64 +636,6 @@ gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_
             }
           }
         }
-      } else {
-        const int t = t0 + quad * 32 + lane;
-        const bool vec_ok = out_is_f32 ? (ld_out % 4 == 0 && (reinterpret_cast<uintptr_t>(out_f32) & 15) == 0)
-                                       : (ld_out % 8 == 0 && (reinterpret_cast<uintptr_t>(out_bf16) & 15) == 0);
-#pragma unroll 1
-        for (int c0 = 0; c0 < F_TILE; c0 += 16) {
-          if (f0 + c0 >= n_features) break;  // uniform across the block
-          uint32_t g[16], u[16];
-          if (n_kb > 0) {
-            tmem_load16(lane_base + c0, g);
-            if (MODE == 1) tmem_load16(lane_base + BN / 2 + c0, u);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) g[j] = u[j] = 0u;
-          }
-          float v[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            v[j] = __uint_as_float(g[j]);
-            if (MODE == 1) v[j] = v[j] / (1.0f + expf(-v[j])) * __uint_as_float(u[j]);
-          }
-          if (t >= n_tokens) continue;
-          const int f = f0 + c0;
-          const long long at = (long long)t * ld_out + f;
-          if (vec_ok && f + 16 <= n_features) {
-            if (out_is_f32) {
-              float4* dst = reinterpret_cast<float4*>(out_f32 + at);
-#pragma unroll
-              for (int q4 = 0; q4 < 4; ++q4) {
-                float4 w4 = make_float4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
-                if (out_is_f32 == 2) {   // accumulate: the output is the float32 residual stream
-                  const float4 old = dst[q4];
-                  w4.x += old.x, w4.y += old.y, w4.z += old.z, w4.w += old.w;
-                }
-                dst[q4] = w4;
-              }
-            } else {
-              uint32_t pk[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                pk[j] = *reinterpret_cast<uint32_t*>(&b);
-              }
-              uint4* dst = reinterpret_cast<uint4*>(out_bf16 + at);
-              dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-              dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              if (f + j < n_features) {
-                if (out_is_f32) out_f32[at + j] = out_is_f32 == 2 ? out_f32[at + j] + v[j] : v[j];
-                else out_bf16[at + j] = __float2bfloat16_rn(v[j]);
-              }
-            }
-          }
-        }
       }
     }
   }
@@ -511,7 +663,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_persistent_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_w,
                                const __grid_constant__ CUtensorMap map_a, void* __restrict__ out, int out_is_f32,
                                int n_tokens, int n_features, int n_kb, long long ld_out, int up_row_offset,
-                               int f_tiles, int t_tiles, int* __restrict__ error_word) {
+                               int f_tiles, int t_tiles, const RowsExtra ex, int* __restrict__ error_word) {
   const int BN = geo.bn;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -643,72 +795,22 @@ gemm_tcgen05_persistent_kernel(const Geometry geo, const __grid_constant__ CUten
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++j) {
       const int buf = j & 1;
       const int f0 = (tile / t_tiles) * F_TILE, t0 = (tile % t_tiles) * BM;
-      if (!mbar_wait(&acc_full[buf], (j >> 1) & 1, abort_flag, geo.wait_ns) || *abort_flag) {
-        *abort_flag = 1;
-        atomicCAS(error_word, 0, ERR_TIMEOUT_EPILOGUE);
-        break;
-      }
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      bool ok = true;
+      auto wait_acc = [&]() -> bool {
+        if (!mbar_wait(&acc_full[buf], (j >> 1) & 1, abort_flag, geo.wait_ns) || *abort_flag) {
+          *abort_flag = 1;
+          atomicCAS(error_word, 0, ERR_TIMEOUT_EPILOGUE);
+          ok = false;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        return ok;
+      };
       const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * ACC_COLS;
-      float* out_f32 = reinterpret_cast<float*>(out);
-      __nv_bfloat16* out_bf16 = reinterpret_cast<__nv_bfloat16*>(out);
-      const int t = t0 + quad * 32 + lane;
-      const bool vec_ok = out_is_f32 ? (ld_out % 4 == 0 && (reinterpret_cast<uintptr_t>(out_f32) & 15) == 0)
-                                     : (ld_out % 8 == 0 && (reinterpret_cast<uintptr_t>(out_bf16) & 15) == 0);
-#pragma unroll 1
-      for (int c0 = 0; c0 < F_TILE; c0 += 16) {
-        if (f0 + c0 >= n_features) break;  // uniform across the block
-        uint32_t g[16], u[16];
-        if (n_kb > 0) {
-          tmem_load16(lane_base + c0, g);
-          if (MODE == 1) tmem_load16(lane_base + BN / 2 + c0, u);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        } else {
-#pragma unroll
-          for (int q = 0; q < 16; ++q) g[q] = u[q] = 0u;
-        }
-        float v[16];
-#pragma unroll
-        for (int q = 0; q < 16; ++q) {
-          v[q] = __uint_as_float(g[q]);
-          if (MODE == 1) v[q] = v[q] / (1.0f + expf(-v[q])) * __uint_as_float(u[q]);
-        }
-        if (t >= n_tokens) continue;
-        const int f = f0 + c0;
-        const long long at = (long long)t * ld_out + f;
-        if (vec_ok && f + 16 <= n_features) {
-          if (out_is_f32) {
-            float4* dst = reinterpret_cast<float4*>(out_f32 + at);
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              float4 w4 = make_float4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
-              if (out_is_f32 == 2) {   // accumulate: the output is the float32 residual stream
-                const float4 old = dst[q4];
-                w4.x += old.x, w4.y += old.y, w4.z += old.z, w4.w += old.w;
-              }
-              dst[q4] = w4;
-            }
-          } else {
-            uint32_t pk[8];
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * q], v[2 * q + 1]);
-              pk[q] = *reinterpret_cast<uint32_t*>(&b);
-            }
-            uint4* dst = reinterpret_cast<uint4*>(out_bf16 + at);
-            dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-          }
-        } else {
-#pragma unroll
-          for (int q = 0; q < 16; ++q) {
-            if (f + q < n_features) {
-              if (out_is_f32) out_f32[at + q] = out_is_f32 == 2 ? out_f32[at + q] + v[q] : v[q];
-              else out_bf16[at + q] = __float2bfloat16_rn(v[q]);
-            }
-          }
-        }
-      }
+      epilogue_tokens_on_rows<MODE, 2>(lane_base, BN, F_TILE, f0, tile / t_tiles, t0 + quad * 32, lane, n_kb > 0, out, out_is_f32,
+                                       ld_out, n_tokens, n_features, ex,
+                                       reinterpret_cast<float*>(smem + geo.stages * geo.stage_bytes + 256) + quad * (32 * 32),
+                                       wait_acc);
+      if (!ok) break;
       // this warp has read its lanes of the half out: the MMA warp may overwrite it
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
@@ -743,7 +845,7 @@ EncodeTiledFn encode_tiled_fn() {
 template <int MODE, int ORIENT, int BLOCKS_PER_SM>
 int launch(int bn, const CUtensorMap* map_w, const CUtensorMap* map_a, void* out, int out_is_f32, int n_tokens,
            int n_features, int K, long long ld_out, long long partial_stride, int splits, int up_row_offset,
-           int* error_word, cudaStream_t stream) {
+           const RowsExtra& ex, int* error_word, cudaStream_t stream) {
   const Geometry g = make_geometry(bn, MODE, ORIENT, BLOCKS_PER_SM);
   if (g.stages < 1 || g.tmem_cols * BLOCKS_PER_SM > 512) return ERR_BAD_SIZE;
   auto kern = gemm_tcgen05_kernel<MODE, ORIENT, BLOCKS_PER_SM>;
@@ -761,18 +863,19 @@ int launch(int bn, const CUtensorMap* map_w, const CUtensorMap* map_a, void* out
   dim3 grid((n_features + f_tile - 1) / f_tile, (n_tokens + t_tile - 1) / t_tile, splits);
   if (grid.y > 65535 || grid.z > 65535) return ERR_BAD_SIZE;
   launch_kernel(kern, grid, NUM_THREADS, smem, stream, g, *map_w, *map_a, out, out_is_f32, n_tokens, n_features,
-                k_blocks, per_split, ld_out, partial_stride, up_row_offset, error_word);
+                k_blocks, per_split, ld_out, partial_stride, up_row_offset, ex, error_word);
   return launch_status();
 }
 
 template <int MODE>
 int launch_persistent(int bn, const CUtensorMap* map_w, const CUtensorMap* map_a, void* out, int out_is_f32, int n_tokens,
-                      int n_features, int K, long long ld_out, int up_row_offset, int* error_word, cudaStream_t stream) {
+                      int n_features, int K, long long ld_out, int up_row_offset, const RowsExtra& ex, int* error_word,
+                      cudaStream_t stream) {
   const Geometry g = make_geometry(bn, MODE, 1, 1);
   if (g.stages < 2 || g.tmem_cols > ACC_COLS) return ERR_BAD_SIZE;
   auto kern = gemm_tcgen05_persistent_kernel<MODE>;
   static size_t configured = 0;
-  const size_t smem = smem_bytes(g);
+  const size_t smem = smem_bytes(g) + STAGING_BYTES;   // the adding epilogue's staging rows lie behind the barriers
   if (smem > configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return launch_status();
@@ -783,7 +886,7 @@ int launch_persistent(int bn, const CUtensorMap* map_w, const CUtensorMap* map_a
   const long long tiles = (long long)f_tiles * t_tiles;
   const int grid = tiles < sm_count() ? (int)tiles : sm_count();
   launch_kernel(kern, grid, NUM_THREADS, smem, stream, g, *map_w, *map_a, out, out_is_f32, n_tokens, n_features,
-                (K + BK - 1) / BK, ld_out, up_row_offset, f_tiles, t_tiles, error_word);
+                (K + BK - 1) / BK, ld_out, up_row_offset, f_tiles, t_tiles, ex, error_word);
   return launch_status();
 }
 
@@ -826,10 +929,17 @@ extern "C" void llm_gemm_test_hooks(long long wait_ns, int drop_k_block) {
 // projection adds itself into the residual stream.
 // orient 0: bn tokens per tile; map_a's box must have bn rows, map_w's 128 (64 in mode 1).
 // orient 1: bn weight rows per tile; map_a's box must have 128 rows, map_w's bn rows (bn / 2 in mode 1).
+// Orient 1 only, both optional (see RowsExtra):
+// `sq_in` [sq_items][sq_stride]: the activations are bfloat16(residual * norm weight) and the norm's
+// factor per row, 1 / sqrt(sum of the parts / norm_width + eps), is applied to the sums;
+// `pre_x` (with accumulate): the kernel also writes pre_x[t, f] = bfloat16(out[t, f] * pre_w[f]) and
+// pre_sq[feature tile][t] = that tile's part of the row's sum of squares (ceil(n_features / bn) tiles).
 extern "C" int llm_gemm_bf16(const void* map_w, const void* map_a, void* out, int out_dtype, int n_tokens,
                              int n_features, int K, long long ld_out, long long partial_stride, int splits,
-                             int bn, int mode, int orient, int up_row_offset, int accumulate, int* error_word,
-                             cudaStream_t stream) {
+                             int bn, int mode, int orient, int up_row_offset, int accumulate, const float* sq_in,
+                             int sq_items, long long sq_stride, float norm_width, float eps, void* pre_x,
+                             long long pre_x_stride, const void* pre_w, int pre_w_dtype, float* pre_sq,
+                             long long pre_sq_stride, int* error_word, cudaStream_t stream) {
   if (n_tokens <= 0 || n_features <= 0) return 0;
   if (K <= 0 || splits <= 0 || (mode == 1 && splits != 1)) return ERR_BAD_SIZE;
   if (splits > 1 && out_dtype != DT_F32) return ERR_BAD_DTYPE;
@@ -842,6 +952,20 @@ extern "C" int llm_gemm_bf16(const void* map_w, const void* map_a, void* out, in
   if (accumulate && (orient != 1 || mode != 0 || splits != 1 || out_dtype != DT_F32)) return ERR_BAD_SIZE;
   const int f32 = out_dtype == DT_F32 ? (accumulate ? 2 : 1) : 0;   // 2: out[t, f] += result
   if (bn < 16 || bn > 256 || bn % 16 || (mode == 1 && orient == 1 && bn % 32)) return ERR_BAD_SIZE;
+  RowsExtra ex = {};
+  if (sq_in) {
+    if (orient != 1 || sq_items < 1 || sq_stride < n_tokens || !(norm_width > 0.0f)) return ERR_BAD_SIZE;
+    ex.sq_in = sq_in, ex.sq_items = sq_items, ex.sq_stride = sq_stride, ex.norm_width = norm_width, ex.eps = eps;
+  }
+  if (pre_x) {
+    if (!accumulate || !pre_w || !pre_sq || pre_sq_stride < n_tokens || n_features % 4 || ld_out % 4 || pre_x_stride % 4)
+      return ERR_BAD_SIZE;
+    if ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(pre_w)) & 15 || reinterpret_cast<uintptr_t>(pre_x) & 7)
+      return ERR_BAD_ALIGN;
+    if (pre_w_dtype != DT_F32 && pre_w_dtype != DT_BF16) return ERR_BAD_DTYPE;
+    ex.pre_x = static_cast<__nv_bfloat16*>(pre_x), ex.pre_x_stride = pre_x_stride, ex.pre_w = pre_w;
+    ex.pre_w_dtype = pre_w_dtype, ex.pre_sq = pre_sq, ex.pre_sq_stride = pre_sq_stride;
+  }
   // Two thread blocks per SM let one block's epilogue overlap the other's main loop, at the price
   // of half the pipeline depth each: worth it only when there are more tiles than SMs and at
   // least three stages still fit (two for the SwiGLU tiles, whose long epilogue gains most).
@@ -854,15 +978,15 @@ extern "C" int llm_gemm_bf16(const void* map_w, const void* map_a, void* out, in
     // wide tiles: a stage of a narrow tile is shorter on the tensor core than the one issuing
     // thread's round of waiting for it, issuing its instructions and committing, and then two
     // blocks per SM with an issuing thread each are faster.
-    if (mode == 0) return launch_persistent<0>(bn, mw, ma, out, f32, n_tokens, n_features, K, ld_out, up_row_offset, error_word, stream);
-    return launch_persistent<1>(bn, mw, ma, out, f32, n_tokens, n_features, K, ld_out, up_row_offset, error_word, stream);
+    if (mode == 0) return launch_persistent<0>(bn, mw, ma, out, f32, n_tokens, n_features, K, ld_out, up_row_offset, ex, error_word, stream);
+    return launch_persistent<1>(bn, mw, ma, out, f32, n_tokens, n_features, K, ld_out, up_row_offset, ex, error_word, stream);
   }
 #define GEMM_CASE(MODE_, ORIENT_)                                                                            \
   if (mode == MODE_ && orient == ORIENT_)                                                                    \
     return pair ? launch<MODE_, ORIENT_, 2>(bn, mw, ma, out, f32, n_tokens, n_features, K, ld_out,           \
-                                            partial_stride, splits, up_row_offset, error_word, stream)      \
+                                            partial_stride, splits, up_row_offset, ex, error_word, stream)  \
                 : launch<MODE_, ORIENT_, 1>(bn, mw, ma, out, f32, n_tokens, n_features, K, ld_out,           \
-                                            partial_stride, splits, up_row_offset, error_word, stream)
+                                            partial_stride, splits, up_row_offset, ex, error_word, stream)
   GEMM_CASE(0, 0);
   GEMM_CASE(1, 0);
   GEMM_CASE(0, 1);

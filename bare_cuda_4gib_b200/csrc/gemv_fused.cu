@@ -73,8 +73,9 @@ struct GemvArgs {
   int norm_w_dtype;
   float eps;
   const int32_t* row_index; // PRO_NORM, PRO_PRENORMED: token i reads row row_index[i] (null: i)
-  const float* sq_in;       // PRO_PRENORMED: [sq_items][SQ_SLOTS] parts of the rows' sums of squares
+  const float* sq_in;       // PRO_PRENORMED: [sq_items][sq_stride] parts of the rows' sums of squares
   int sq_items;
+  long long sq_stride;
   // EPI_ADD, optional: what the next product's PRO_PRENORMED needs
   __nv_bfloat16* pre_x;     // [tokens, n_out] = bfloat16(new residual * pre_w)
   long long pre_x_stride;
@@ -336,7 +337,7 @@ __global__ void __launch_bounds__(THREADS, PRO == PRO_NORM ? 1 : 2) gemv_fused_k
       for (int tok = warp; tok < a.tokens; tok += WARPS) {
         const int src = a.row_index ? a.row_index[tok] : tok;
         float sq = 0.0f;
-        for (int i = lane; i < a.sq_items; i += 32) sq += a.sq_in[(size_t)i * SQ_SLOTS + src];
+        for (int i = lane; i < a.sq_items; i += 32) sq += a.sq_in[(long long)i * a.sq_stride + src];
         sq = warp_sum(sq);
         if (lane == 0) scale_s[tok] = 1.0f / sqrtf(sq / (float)a.k + a.eps);
       }
@@ -590,13 +591,13 @@ extern "C" int llm_gemv_fused(const void* w, int w_rows, int k, int tokens, int 
                               int up_offset, void* k_base, void* v_base, const int32_t* block_table,
                               long long page_stride, int table_stride, int page_tokens, int kv_heads, int head_dim,
                               const int32_t* positions, const int32_t* row_seq, const float* inv_freq, int q_heads,
-                              int write_cache, const float* sq_in, int sq_items, void* pre_x, long long pre_x_stride,
+                              int write_cache, const float* sq_in, int sq_items, long long sq_stride, void* pre_x, long long pre_x_stride,
                               const void* pre_w, int pre_w_dtype, float* pre_sq, int max_blocks, int* error_word, cudaStream_t stream) {
   SmemPlan plan;
   if (!plan_smem(tokens, k, pro, SMEM_BUDGET, 2, plan)) return ERR_BAD_SIZE;
   if (out_dtype != DT_F32 && out_dtype != DT_BF16) return ERR_BAD_DTYPE;
   if (epi == EPI_ADD && out_dtype != DT_F32) return ERR_BAD_DTYPE;
-  if (tokens > SQ_SLOTS || (pro == PRO_PRENORMED && (!sq_in || sq_items < 1)) || (pre_x && (epi != EPI_ADD || !pre_w || !pre_sq)))
+  if (tokens > SQ_SLOTS || (pro == PRO_PRENORMED && (!sq_in || sq_items < 1 || sq_stride < 1)) || (pre_x && (epi != EPI_ADD || !pre_w || !pre_sq)))
     return ERR_BAD_SIZE;
   const auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   if (!aligned16(w) || !aligned16(x) || (pro != PRO_NORM && x_stride % 8) || (pro == PRO_NORM && x_stride % 4) ||
@@ -610,7 +611,7 @@ extern "C" int llm_gemv_fused(const void* w, int w_rows, int k, int tokens, int 
   a.out = out, a.out_dtype = out_dtype, a.out_stride = out_stride, a.n_out = n_out, a.up_offset = up_offset;
   a.cache = PagedCache{k_base, v_base, block_table, page_stride, table_stride, page_tokens, kv_heads, head_dim};
   a.positions = positions, a.row_seq = row_seq, a.inv_freq = inv_freq, a.q_heads = q_heads, a.write_cache = write_cache;
-  a.sq_in = sq_in, a.sq_items = sq_items;
+  a.sq_in = sq_in, a.sq_items = sq_items, a.sq_stride = sq_stride;
   a.pre_x = static_cast<__nv_bfloat16*>(pre_x), a.pre_x_stride = pre_x_stride, a.pre_w = pre_w, a.pre_w_dtype = pre_w_dtype;
   a.pre_sq = pre_sq;
   if (epi == EPI_SWIGLU) {

@@ -5,14 +5,14 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_int, c_longlong, c_void_p
+from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Dict, Optional, Tuple
 
 import torch
 
 from ..errors import KernelLaunchError
 from . import build
-from .lib import DT_BF16, DT_F32, Partials, _check, sm_count
+from .lib import DT_BF16, DT_F32, AddTo, LazyNorm, Partials, Prenormed, _check, _ptr, sm_count
 
 BM, BK = 128, 64
 SPLIT_MAX_ROWS = 256          # steps with more rows never split K
@@ -24,10 +24,10 @@ def lib():
     global _lib
     if _lib is None:
         l = build.load_library("gemm_tcgen05.cu")
-        P, I, L = c_void_p, c_int, c_longlong
+        P, I, L, F = c_void_p, c_int, c_longlong, c_float
         l.llm_gemm_tensor_map.argtypes = [P, P, L, L, L, I]
         l.llm_gemm_tensor_map.restype = c_int
-        l.llm_gemm_bf16.argtypes = [P, P, P, I, I, I, I, L, L, I, I, I, I, I, I, P, P]
+        l.llm_gemm_bf16.argtypes = [P, P, P, I, I, I, I, L, L, I, I, I, I, I, I, P, I, L, F, F, P, L, P, I, P, L, P, P]
         l.llm_gemm_bf16.restype = c_int
         _lib = l
     return _lib
@@ -165,27 +165,71 @@ def feature_tile(rows: int, n_out: int, swiglu: bool) -> int:
     return best
 
 
-def run(ctx, plan: GemmPlan, a: torch.Tensor, rows: int, out_dtype: torch.dtype, buffer: str,
-        allow_partials: bool, swiglu: bool, add_to: Optional[torch.Tensor] = None) -> Optional[Partials]:
-    """`add_to` (a float32 [rows, n] matrix, the residual stream): where the kernel can, the product is
-    added into it and None comes back; otherwise the plain result comes back as without it."""
+NO_EXTRA = (0, 0, 0, 0.0, 0.0, 0, 0, 0, 0, 0, 0)     # no row factor on the way in, nothing prepared on the way out
+
+
+def takes_prenormed(rows: int, swiglu: bool) -> bool:
+    """Whether a step of `rows` rows runs in the orientation whose epilogue can apply a norm's
+    factor per row (tokens on the MMA rows), so that the product can take a `LazyNorm` that a
+    product before it prepared."""
+    return rows > (SWIGLU_TOKENS_ON_ROWS_ABOVE if swiglu else TOKENS_ON_ROWS_ABOVE)
+
+
+def run(ctx, plan: GemmPlan, a, rows: int, out_dtype: torch.dtype, buffer: str,
+        allow_partials: bool, swiglu: bool, epilogue=None) -> Optional[Partials]:
+    """`a`: a bfloat16 matrix, or a `LazyNorm` whose `prenormed` a product before this one left
+    (`takes_prenormed` steps only).  `epilogue`: with an `AddTo` whose norm can be prepared, a
+    many-token step adds the product into the float32 residual stream itself, leaves bfloat16(new
+    residual * that norm's weight) and the rows' sums of squares for the product that reads the
+    norm next (`ctx.prenormed`), and None comes back; otherwise the plain result comes back and the
+    epilogue stays the caller's."""
+    extra_in = NO_EXTRA[:5]
+    if isinstance(a, LazyNorm):
+        pre = a.prenormed
+        if pre is None or a.row_index is not None or not takes_prenormed(rows, swiglu):
+            a = a.materialize()
+        else:
+            extra_in = (pre.sq.data_ptr(), pre.items, pre.sq.stride(0), float(pre.x.shape[-1]), a.eps)
+            a = pre.x
+    ctx.prenormed = None
     if a.dtype != torch.bfloat16 or a.stride(-1) != 1 or a.shape[-1] != plan.k or a.data_ptr() % 16 or a.stride(0) % 8:
         raise KernelLaunchError(f"gemm_tcgen05: activations {tuple(a.shape)} {a.dtype} do not fit weight "
                                 f"[{plan.n}, {plan.k}]")
     err = error_word(a.device)
     l = lib()
     code = DT_BF16 if out_dtype == torch.bfloat16 else DT_F32
-    if rows > (SWIGLU_TOKENS_ON_ROWS_ABOVE if swiglu else TOKENS_ON_ROWS_ABOVE):
+    if takes_prenormed(rows, swiglu):
         n_out = plan.n // 2 if swiglu else plan.n
         bn = feature_tile(rows, n_out, swiglu)
-        fused_add = (add_to is not None and not swiglu and out_dtype == torch.float32 and add_to.dtype == torch.float32
-                     and add_to.shape[-1] == n_out and add_to.stride(-1) == 1)
-        out = add_to if fused_add else ctx.ws.get(buffer, (rows, n_out), out_dtype)
+        extra_out = NO_EXTRA[5:]
+        out, then = None, None
+        if (isinstance(epilogue, AddTo) and epilogue.then_norm is not None and not swiglu
+                and epilogue.residual.dtype == torch.float32 and epilogue.residual.shape[-1] == n_out
+                and epilogue.residual.stride(-1) == 1 and epilogue.residual.stride(0) % 4 == 0 and n_out % 4 == 0
+                and epilogue.residual.data_ptr() % 16 == 0):
+            then = epilogue.then_norm
+            pre_w = then.tensors["weight"]
+            if pre_w.is_cuda and pre_w.data_ptr() % 16 == 0 and pre_w.dtype in (torch.float32, torch.bfloat16):
+                out = epilogue.residual
+                f_tiles = -(-n_out // bn)
+                pre_x = ctx.ws.get("prenormed.rows.x", (rows, n_out), torch.bfloat16)
+                # one row of parts per feature tile (a tile is at least 64 wide), as long as the largest step
+                most_tiles = -(-n_out // 64)
+                pre_sq = ctx.ws.get("prenormed.rows.sq", (most_tiles, ctx.ws.max_rows), torch.float32, max_rows=most_tiles)
+                extra_out = (pre_x.data_ptr(), pre_x.stride(0), pre_w.data_ptr(),
+                             DT_BF16 if pre_w.dtype == torch.bfloat16 else DT_F32, pre_sq.data_ptr(), pre_sq.stride(0))
+        fused = out is not None
+        if not fused:
+            out = ctx.ws.get(buffer, (rows, n_out), out_dtype)
         _check(l.llm_gemm_bf16(ctypes.addressof(plan.weight_map(bn // 2 if swiglu else bn)),
-                               ctypes.addressof(plan.act_map(a, BM)), out.data_ptr(), code, rows, n_out, plan.k,
-                               out.stride(0), 0, 1, bn, 1 if swiglu else 0, 1, n_out if swiglu else 0,
-                               1 if fused_add else 0, err.data_ptr(), ctx.stream), "gemm_tcgen05 (tokens on rows)")
-        return None if fused_add else Partials(out)
+                               ctypes.addressof(plan.act_map(a, BM)), out.data_ptr(), DT_F32 if fused else code, rows,
+                               n_out, plan.k, out.stride(0), 0, 1, bn, 1 if swiglu else 0, 1, n_out if swiglu else 0,
+                               1 if fused else 0, *extra_in, *extra_out, err.data_ptr(), ctx.stream),
+               "gemm_tcgen05 (tokens on rows)")
+        if fused:
+            ctx.prenormed = Prenormed(then, pre_x, pre_sq, f_tiles)
+            return None
+        return Partials(out)
     bn = token_tile(rows)
     if swiglu:
         inter = plan.n // 2
@@ -195,7 +239,7 @@ def run(ctx, plan: GemmPlan, a: torch.Tensor, rows: int, out_dtype: torch.dtype,
             # epilogue and no partial results, when that alone gives every SM a block
             _check(l.llm_gemm_bf16(ctypes.addressof(plan.weight_map(BM // 2)), ctypes.addressof(plan.act_map(a, bn)),
                                    out.data_ptr(), code, rows, inter, plan.k, out.stride(0), 0, 1, bn, 1, 0, inter, 0,
-                                   err.data_ptr(), ctx.stream), "gemm_tcgen05 (swiglu)")
+                                   *NO_EXTRA, err.data_ptr(), ctx.stream), "gemm_tcgen05 (swiglu)")
             return Partials(out)
         # a narrow feed-forward: stream [gate; up] as one product split over K so that every SM takes
         # part, and add the partial results inside the SwiGLU kernel
@@ -213,6 +257,6 @@ def run(ctx, plan: GemmPlan, a: torch.Tensor, rows: int, out_dtype: torch.dtype,
         stride = 0
     _check(l.llm_gemm_bf16(ctypes.addressof(plan.map_w), ctypes.addressof(plan.act_map(a, bn)), out.data_ptr(),
                            DT_BF16 if out_dtype == torch.bfloat16 else DT_F32, rows, plan.n, plan.k,
-                           out.stride(-2), stride, splits, bn, 0, 0, 0, 0, err.data_ptr(), ctx.stream),
+                           out.stride(-2), stride, splits, bn, 0, 0, 0, 0, *NO_EXTRA, err.data_ptr(), ctx.stream),
            "gemm_tcgen05")
     return Partials(out, splits)

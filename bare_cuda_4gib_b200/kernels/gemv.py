@@ -33,7 +33,7 @@ def lib():
         l.llm_gemv_fused_smem.argtypes = [I, I]
         l.llm_gemv_fused_smem.restype = L
         l.llm_gemv_fused.argtypes = [P, I, I, I, I, I, P, L, P, I, F, P, P, I, L, I, I, P, P, P, L, I, I, I, I,
-                                     P, P, P, I, I, P, I, P, L, P, I, P, I, P, P]
+                                     P, P, P, I, I, P, I, L, P, L, P, I, P, I, P, P]
         l.llm_gemv_fused.restype = c_int
         _lib = l
     return _lib
@@ -63,10 +63,10 @@ def run(ctx, weight: torch.Tensor, x, rows: int, out_dtype: torch.dtype, buffer:
     matrix or a `LazyNorm`; `epilogue` None, `AddTo` or `RotateAndCache`.  Returns the result, or
     None when the epilogue consumed it."""
     n, k = weight.shape
-    sq_in, sq_items = None, 0
+    sq_in, sq_items, sq_stride = None, 0, 0
     if isinstance(x, LazyNorm) and x.prenormed is not None:
         pre = x.prenormed
-        pro, xt, x_stride, sq_in, sq_items = PRO_PRENORMED, pre.x, pre.x.stride(0), pre.sq, pre.items
+        pro, xt, x_stride, sq_in, sq_items, sq_stride = PRO_PRENORMED, pre.x, pre.x.stride(0), pre.sq, pre.items, pre.sq.stride(0)
         norm_w, eps, row_index, norm_code = None, x.eps, x.row_index, DT_F32
     elif isinstance(x, LazyNorm):
         pro, xt, x_stride = PRO_NORM, x.residual, x.residual.stride(0)
@@ -103,7 +103,7 @@ def run(ctx, weight: torch.Tensor, x, rows: int, out_dtype: torch.dtype, buffer:
         cache.block_table.data_ptr() if cache else 0, cache.page_stride if cache else 0,
         cache.table_stride if cache else 0, cache.page_tokens if cache else 1, cache.kv_heads if cache else 0,
         cache.head_dim if cache else 0, _ptr(positions), _ptr(row_seq), _ptr(inv_freq), q_heads, write_cache,
-        _ptr(sq_in), sq_items, _ptr(pre_x), pre_x.stride(0) if pre_x is not None else 0, _ptr(pre_w),
+        _ptr(sq_in), sq_items, sq_stride, _ptr(pre_x), pre_x.stride(0) if pre_x is not None else 0, _ptr(pre_w),
         (DT_BF16 if pre_w.dtype == torch.bfloat16 else DT_F32) if pre_w is not None else DT_F32, _ptr(pre_sq),
         sm_count(), gemm.error_word(weight.device).data_ptr(), ctx.stream), "gemv_fused")
     ctx.prenormed = Prenormed(epilogue.then_norm, pre_x, pre_sq, -(-n // 16)) if pre_x is not None else None

@@ -43,12 +43,10 @@ class Linear:
             from ..kernels import gemv
             if gemv.takes(rows, self.in_features):
                 return gemv.run(ctx, self.weight, a, rows, out_dtype, buffer, swiglu, epilogue)
-        a = K.materialize(a)
         if self.fast is not None and ctx.use_fast_gemm:
             from ..kernels import gemm
-            # (the many-token kernel can add into the residual stream itself, `add_to=`; measured
-            # slower than leaving the add to the norm kernel that follows, so it is not asked to)
-            return gemm.run(ctx, self.fast, a, rows, out_dtype, buffer, allow_partials, swiglu)
+            return gemm.run(ctx, self.fast, a, rows, out_dtype, buffer, allow_partials, swiglu, epilogue)
+        a = K.materialize(a)
         if swiglu:
             full = ctx.ws.get(buffer + ".gate_up", (rows, self.out_features), out_dtype)
             K.matmul_plain(a, self.weight, full, rows, ctx.stream)

@@ -34,9 +34,12 @@ class RMSNorm(Part):
         ctx.prenormed = None
         if lazy and delta is None and ctx.dtype == torch.bfloat16 and ctx.use_fast_gemm:
             from ..kernels import gemv
-            if gemv.takes(rows, int(self.params["size"])) and self.tensors["weight"].is_cuda:
+            mine = left if left is not None and left.norm is self else None
+            # a few-token step norms inside the consuming product; a many-token step only where the
+            # product before this norm has prepared it
+            if (gemv.takes(rows, int(self.params["size"])) or mine is not None) and self.tensors["weight"].is_cuda:
                 return K.LazyNorm(ctx, residual, self.tensors["weight"], float(self.params["eps"]), rows,
-                                  row_index, buffer, left if left is not None and left.norm is self else None)
+                                  row_index, buffer, mine)
         out = ctx.ws.get(buffer, (rows, self.params["size"]), ctx.dtype)
         K.add_rmsnorm(residual, delta, self.tensors["weight"], out, float(self.params["eps"]), rows,
                       row_index, ctx.stream)

@@ -269,12 +269,26 @@ def test_gemm_tcgen05(m, n, k, out_dtype):
         _close(got, want, 2 ** -8, 1e-4 * math.sqrt(k))
 
 
-@pytest.mark.parametrize("m,n,k,bn", [(300, 1000, 96, 0), (513, 130, 176, 0), (2048, 2048, 512, 0), (2048, 5120, 128, 256),
-                                      (1100, 3000, 192, 256), (257, 72, 64, 0)])
-def test_gemm_tcgen05_adds_into_the_residual(m, n, k, bn, monkeypatch):
-    """Many-token products that add themselves into a float32 matrix (both the two-blocks-per-SM
-    kernel and, with wide tiles and more tiles than SMs, the persistent one)."""
+class _RowNorm:
+    """What a product needs to know of the norm that reads the residual stream after it."""
+
+    prenormable = True
+
+    def __init__(self, weight, eps):
+        self.tensors, self.params = {"weight": weight}, {"eps": eps}
+
+
+@pytest.mark.parametrize("m,n,k,bn", [(300, 1000, 96, 0), (513, 132, 176, 0), (2048, 2048, 512, 0), (2048, 5120, 128, 256),
+                                      (1100, 3000, 192, 256), (257, 72, 64, 0), (700, 1000, 64, 144), (2048, 2048, 64, 128),
+                                      (1500, 1284, 128, 96)])
+@pytest.mark.parametrize("w_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tcgen05_adds_into_the_residual_and_prepares_the_next_norm(m, n, k, bn, w_dtype, monkeypatch):
+    """Many-token products that add themselves into the float32 residual stream (both the
+    two-blocks-per-SM kernel and, with wide tiles and more tiles than SMs, the persistent one) and
+    leave bfloat16(new residual * the next norm's weight) with the rows' sums of squares; then the
+    product that reads that norm, plain and with SwiGLU, against the norm and product in float64."""
     from bare_cuda_4gib_b200.kernels import gemm
+    from bare_cuda_4gib_b200.kernels import lib as K
     if bn:
         monkeypatch.setenv("BARE_CUDA_B200_GEMM_BN", str(bn))
     torch.manual_seed(m + n)
@@ -284,11 +298,40 @@ def test_gemm_tcgen05_adds_into_the_residual(m, n, k, bn, monkeypatch):
     w = torch.randn(n, k, device=DEV).to(torch.bfloat16)
     residual = torch.randn(m + 5, n, device=DEV)
     before = residual.double().clone()
-    assert gemm.run(ctx, gemm.plan_for(w), a, m, torch.float32, "out", True, False, add_to=residual[:m]) is None
+    eps = 1e-5
+    norm = _RowNorm((1 + 0.3 * torch.randn(n, device=DEV)).to(w_dtype), eps)
+    assert gemm.run(ctx, gemm.plan_for(w), a, m, torch.float32, "out", True, False,
+                    epilogue=K.AddTo(residual[:m], norm)) is None
     gemm.check_errors()
     want = before.clone()
     want[:m] += a.double() @ w.double().t()
     _close(residual, want, 1e-5, 1e-4 * math.sqrt(k))
+    pre = ctx.prenormed
+    assert pre is not None and pre.norm is norm
+    now = residual[:m].double()
+    nw = norm.tensors["weight"].double()
+    _close(pre.x[:m].float(), now * nw, 2 ** -8, 1e-6)
+    sq = pre.sq[: pre.items, :m].double().sum(0)
+    _close(sq, now.square().sum(-1), 1e-5, 1e-5)
+    monkeypatch.delenv("BARE_CUDA_B200_GEMM_BN", raising=False)
+    if n % 8:
+        return     # (the consumer's activations need rows of a multiple of 8 elements)
+    # ---- the consumers: x = rms_norm(residual) * weight is never formed; the factor goes on the sums.
+    # The reference takes the same bfloat16 input (pre.x) and applies the factor in float64, so what
+    # is left to differ is the order of the sums and the rounding of the output.
+    normed = pre.x[:m].double() * torch.rsqrt(now.square().mean(-1, keepdim=True) + eps)
+    _close(normed, now * torch.rsqrt(now.square().mean(-1, keepdim=True) + eps) * nw, 2 ** -8, 1e-6)
+    for swiglu in (False, True):
+        n2 = 384
+        w2 = (torch.randn(n2, n, device=DEV) / math.sqrt(n)).to(torch.bfloat16)
+        lazy = K.LazyNorm(ctx, residual, norm.tensors["weight"], eps, m, None, "normed", pre)
+        res = gemm.run(ctx, gemm.plan_for(w2), lazy, m, torch.bfloat16, "out2", False, swiglu)
+        gemm.check_errors()
+        full = normed @ w2.double().t()
+        if swiglu:
+            gate, up = full[:, : n2 // 2], full[:, n2 // 2:]
+            full = gate / (1 + torch.exp(-gate)) * up
+        _close(res.tensor.float(), full, 2 ** -8, 1e-4)
 
 
 @pytest.mark.parametrize("m,inter,k", [(3, 176, 64), (40, 5632, 256), (130, 256, 96), (300, 200, 128), (9, 2816, 512),
