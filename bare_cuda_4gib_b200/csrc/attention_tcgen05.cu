@@ -12,22 +12,24 @@
 //                  swizzled shared memory with TMA (one tensor map over the cache group's whole
 //                  pool, a box per page piece).  Key tiles and value tiles go through ONE ring of
 //                  slots in the order K(0) V(0) K(1) V(1) ..., each slot given back by the commit of
-//                  the last product that reads it (8 slots at head size 64, 3 at 128);
+//                  the last product that reads it (4 slots at head size 64, 3 at 128);
 //   MMA thread     S_g = Q_g K^T (M 128, N 128, K head size) into tile g's S columns of tensor memory;
 //   softmax warps  two groups of four warps; group g owns tile g and sees every key block of it.
 //                  First it stages Q_g with cp.async.  Then, one thread per row: read the row of S
-//                  from tensor memory, scale, mask, running maximum and sum in float32 (base 2, kept
-//                  in several independent partial maxima and sums so that no long dependent chain
-//                  forms), write P as bfloat16 into swizzled shared memory (the A operand of the
-//                  second product);
-//   MMA thread     O_block = P_g V (M 128, N 64 per 64 value columns, K 128) into tensor memory;
-//                  V stays as it lies in the cache ([key][channel]) and is described to the MMA as
-//                  an MN-major operand;
-//   softmax warps  O = O * correction + O_block, with O in registers, one block late, so nobody
-//                  waits for the tensor core; at the end every thread divides its row by its sum and
-//                  stores it: no merge between threads.
-// While one group exponentiates (the special-function units bound this kernel), the other reads
-// its maxima or adds its O_block, and the MMA thread serves whichever group is ready next.
+//                  from tensor memory once, 64 columns at a time, scale, mask, running maximum and
+//                  sum in float32 (base 2, kept in several independent partial maxima and sums so
+//                  that no long dependent chain forms), write P as bfloat16 into swizzled shared
+//                  memory (the A operand of the second product; two P buffers per group at head
+//                  size 64, so that P(i) is written while P(i - 1) V still runs);
+//   MMA thread     O_g (+)= P_g V (M 128, N 64 per 64 value columns, K 128): O accumulates in
+//                  tensor memory over all key blocks; V stays as it lies in the cache
+//                  ([key][channel]) and is described to the MMA as an MN-major operand;
+//   softmax warps  the maximum that the exponentials are taken against follows the row's true
+//                  maximum only when that has grown by more than 2^8, so O (and the row's sum, and
+//                  the half row of P that may already be written) is rescaled rarely; at the end
+//                  every thread divides its row of O by its sum and stores it: no merge between threads.
+// While one group exponentiates, the other reads its S, and the MMA thread serves whichever group
+// is ready next.
 // A request's last page may hold, behind its last key, what an earlier request left there: masked
 // scores never see it, but 0 x NaN would reach O through P V, so the loader clears those value rows
 // in shared memory before the last block's P V may run.
@@ -55,17 +57,18 @@ constexpr int BN = 128;          // keys per block
 constexpr int SUB = 128 * 128;   // bytes of a [128 rows x 64 bf16] swizzled sub-tile
 constexpr int Q_BYTES = KA * SUB;        // one tile's queries
 constexpr int TILE_BYTES = KA * SUB;     // one key tile or one value tile
-constexpr int P_BYTES = 2 * SUB;         // [128 rows x 128 keys] as two sub-tiles; one such buffer per group
-constexpr int SLOTS = D == 64 ? 8 : 3;   // key and value tiles in flight (what shared memory allows)
+constexpr int P_BYTES = 2 * SUB;         // [128 rows x 128 keys] as two sub-tiles
+constexpr int PBUFS = D == 64 ? 2 : 1;   // P buffers per group: with two, P(i) is written while P(i - 1) V still runs
+constexpr int SLOTS = D == 64 ? 4 : 3;   // key and value tiles in flight (what shared memory allows)
 constexpr int SOFTMAX_THREADS = 256, LOADER_THREADS = 32;
 constexpr int MMA_WARP = SOFTMAX_THREADS / 32;
 constexpr int NUM_THREADS = SOFTMAX_THREADS + 32 + LOADER_THREADS;   // warps 0-7 softmax, 8 MMA, 9 loader
 constexpr int TMEM_COLS = 512;
 constexpr int O_COL = 256;       // first tensor-memory column of the P V results (S buffers at 0 and 128)
 constexpr int GROUP_THREADS = 128;
-constexpr int S_PIECE = 64;      // columns of S a softmax thread holds in registers at a time (BN: the whole row, read once)
+constexpr int S_PIECE = 64;      // columns of S a softmax thread holds in registers at a time (one sub-tile of P)
 constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;
-constexpr size_t SMEM_BYTES = TILES * Q_BYTES + SLOTS * TILE_BYTES + TILES * P_BYTES + 256;   // 2 * SLOTS + 13 barriers, 2 words
+constexpr size_t SMEM_BYTES = TILES * Q_BYTES + SLOTS * TILE_BYTES + TILES * PBUFS * P_BYTES + 256;   // 2 * SLOTS + 17 barriers, 2 words
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -209,15 +212,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
   extern __shared__ __align__(1024) uint8_t smem[];   // swizzled tiles need 1024-byte alignment (checked below)
   uint8_t* q_smem = smem;                              // [TILES][KA sub-tiles]
   uint8_t* ring = q_smem + TILES * Q_BYTES;            // [SLOTS][KA sub-tiles]: key and value tiles in turn
-  uint8_t* p_smem = ring + SLOTS * TILE_BYTES;         // [TILES][two sub-tiles of 64 keys]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + TILES * P_BYTES);
+  uint8_t* p_smem = ring + SLOTS * TILE_BYTES;         // [TILES][PBUFS][two sub-tiles of 64 keys]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + TILES * PBUFS * P_BYTES);
   uint64_t* tile_full = bars;               // [SLOTS] loader -> MMA: the slot's tile has landed
   uint64_t* tile_empty = tile_full + SLOTS; // [SLOTS] MMA (commit) -> loader
   uint64_t* q_full = tile_empty + SLOTS;    // [2] softmax group -> MMA: Q_g staged
   uint64_t* s_full = q_full + 2;            // [2] MMA (commit) -> softmax, per group
-  uint64_t* p_full = s_full + 2;            // [2] softmax -> MMA: P written, per group
-  uint64_t* o_full = p_full + 2;            // [2] MMA (commit) -> softmax, per group
-  uint64_t* s_free = o_full + 2;            // [2] softmax -> MMA: the group holds its S values in registers
+  // (with two P buffers a group may be a whole block ahead of the MMA thread: a barrier per buffer,
+  // so that no barrier ever runs two phases ahead of the one who waits on it)
+  uint64_t* p_full = s_full + 2;            // [2][2] softmax -> MMA: P written, per group and P buffer
+  uint64_t* o_full = p_full + 4;            // [2][2] MMA (commit) -> softmax, per group and P buffer: P(i) V is complete
+  uint64_t* s_free = o_full + 4;            // [2] softmax -> MMA: the group holds its S values in registers
   uint64_t* v_clean = s_free + 2;           // loader -> MMA: the last value tile holds no stale rows
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(v_clean + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -276,8 +281,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
     for (int b = 0; b < 2; ++b) {
       mbar_init(&q_full[b], GROUP_THREADS);
       mbar_init(&s_full[b], 1);
-      mbar_init(&p_full[b], GROUP_THREADS);
-      mbar_init(&o_full[b], 1);
+      mbar_init(&p_full[2 * b], GROUP_THREADS);
+      mbar_init(&p_full[2 * b + 1], GROUP_THREADS);
+      mbar_init(&o_full[2 * b], 1);
+      mbar_init(&o_full[2 * b + 1], 1);
       mbar_init(&s_free[b], GROUP_THREADS);
     }
     mbar_init(v_clean, LOADER_THREADS);
@@ -395,17 +402,19 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
         if (last) umma_commit(&tile_empty[slot]);
       };
       // O_g (+)= P_g V(jj): the group's O accumulates in tensor memory over its key blocks (`first`: overwrite)
-      auto issue_pv = [&](int g, int jj, bool last, bool first) {
+      auto issue_pv = [&](int g, int jj, bool last, int i) {     // i: the group's i-th key block
         const int slot = (2 * jj + 1) % SLOTS;
+        const bool first = i == 0;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t v_addr = smem_u32(ring) + slot * TILE_BYTES, p_addr = smem_u32(p_smem) + g * P_BYTES;
+        const uint32_t v_addr = smem_u32(ring) + slot * TILE_BYTES;
+        const uint32_t p_addr = smem_u32(p_smem) + (g * PBUFS + i % PBUFS) * P_BYTES;
 #pragma unroll
         for (int vt = 0; vt < KA; ++vt)
 #pragma unroll
           for (int kk = 0; kk < BN / 16; ++kk)
             umma_bf16(tmem_base + O_COL + g * D + vt * 64, smem_desc_sw128(p_addr + (kk >> 2) * SUB) + 2 * (kk & 3),
                       smem_desc_sw128(v_addr + vt * SUB) + (uint64_t)(kk * 2048 >> 4), idesc_o, (kk > 0 || !first) ? 1u : 0u);
-        umma_commit(&o_full[g]);
+        umma_commit(&o_full[2 * g + i % PBUFS]);
         if (last) umma_commit(&tile_empty[slot]);
       };
       // The two groups are served as they come: a group's next S as soon as it reports that it holds the
@@ -434,10 +443,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
           }
           if (pv_next[g] < s_next[g]) {
             const int i = pv_next[g], jj = g_lo[g] + i - kb_lo;
-            if (mbar_try_wait(&p_full[g], i & 1) && landed(2 * jj + 1) &&
+            if (mbar_try_wait(&p_full[2 * g + i % PBUFS], (uint32_t)(i / PBUFS) & 1u) && landed(2 * jj + 1) &&
                 (kb_lo + jj != stale_block || mbar_try_wait(v_clean, 0))) {
               const bool last = !active(o, jj) || pv_next[o] > kb_lo + jj - g_lo[o];
-              issue_pv(g, jj, last, i == 0);
+              issue_pv(g, jj, last, i);
               pv_next[g] = i + 1;
               progress = true;
             }
@@ -455,8 +464,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
         atomicCAS(a.error_word, 0, ERR_MMA);
         umma_commit(&s_full[0]);   // release whoever waits
         umma_commit(&s_full[1]);
-        umma_commit(&o_full[0]);
-        umma_commit(&o_full[1]);
+        for (int b = 0; b < 4; ++b) umma_commit(&o_full[b]);
       }
     }
   } else {
@@ -493,23 +501,32 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
     // their quotient is exact either way.
     constexpr float RESCALE_STEP = 8.0f;
     float m = -INFINITY, l = 0.0f;
-    // this row of the group's P tile (swizzled: chunk c of row r lies at c ^ (r % 8) inside the row's 128 bytes)
-    const uint32_t p_row = smem_u32(p_smem) + g * P_BYTES + (r >> 3) * 1024 + (r & 7) * 128, p_xor = (uint32_t)(r & 7) << 4;
+    // this row of the group's P tiles (swizzled: chunk c of row r lies at c ^ (r % 8) inside the row's 128 bytes)
+    const uint32_t p_row0 = smem_u32(p_smem) + g * PBUFS * P_BYTES + (r >> 3) * 1024 + (r & 7) * 128, p_xor = (uint32_t)(r & 7) << 4;
+    // P(k) V of this group is complete (its commit arrives on the barrier of P buffer k % PBUFS)
+    auto wait_pv = [&](int k) { return mbar_wait(&o_full[2 * g + k % PBUFS], (uint32_t)(k / PBUFS) & 1u, abort_flag); };
     bool ok = true;
-    for (int i = 0; i < my_n; ++i) {
+    for (int i = 0; i < my_n && ok; ++i) {
       const int key0 = (my_lo + i) * BN;
       ok = mbar_wait(&s_full[g], i & 1, abort_flag) && !*abort_flag;
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const bool all_visible = key0 + BN - 1 <= tile_min_pos && (a.window <= 0 || key0 > tile_max_pos - a.window);
-      // S is read in pieces of S_PIECE columns: once for the row's maximum and, unless the whole row is
-      // kept in registers meanwhile (S_PIECE == BN), once more for the probabilities
-      uint32_t v[S_PIECE];
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-      auto load_piece = [&](int h) {
+      const uint32_t p_row = p_row0 + (i % PBUFS) * P_BYTES;
+      // The row of S is read once, in two pieces of 64 columns (one sub-tile of P each).  Each piece
+      // settles the maximum for itself: should the second piece move it, the probabilities of the
+      // first, which this thread has just written, are rescaled where they lie (rare, as is every move).
+      float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
+#pragma unroll
+      for (int h = 0; h < BN / S_PIECE; ++h) {
+        uint32_t v[S_PIECE];
 #pragma unroll
         for (int c = 0; c < S_PIECE; c += 32) tmem_load32_nowait(s_addr + h * S_PIECE + c, v + c);
         tmem_wait_loads();
+        if (h == BN / S_PIECE - 1) {   // the last read of S(i): the MMA thread may overwrite the buffer with S(i + 1)
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          mbar_arrive(&s_free[g]);
+        }
         if (!all_visible) {
 #pragma unroll
           for (int k = 0; k < S_PIECE; ++k) {
@@ -518,10 +535,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
             if (!visible) v[k] = 0xff800000u;   // -inf: probability 0
           }
         }
-      };
-#pragma unroll
-      for (int h = 0; h < BN / S_PIECE; ++h) {
-        load_piece(h);
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
         for (int k = 0; k < S_PIECE; k += 8) {   // four independent partial maxima
           mx0 = fmaxf(mx0, fmaxf(__uint_as_float(v[k]), __uint_as_float(v[k + 1])));
@@ -529,55 +543,57 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
           mx2 = fmaxf(mx2, fmaxf(__uint_as_float(v[k + 4]), __uint_as_float(v[k + 5])));
           mx3 = fmaxf(mx3, fmaxf(__uint_as_float(v[k + 6]), __uint_as_float(v[k + 7])));
         }
-      }
-      if (S_PIECE == BN) {     // the row is in registers: the MMA thread may write S(i + 1) over it
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        mbar_arrive(&s_free[g]);
-      }
-      const float m_new = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * a.scale_log2);   // scale > 0: the maximum commutes with it
-      // tensor-memory loads and stores are warp-wide: the warp moves its maxima together, as soon as one of
-      // its rows has outgrown its own by the step (a row that has not may follow the true maximum just as well)
-      const bool move = __any_sync(0xffffffffu, m_new > m + RESCALE_STEP);
-      // P(i) goes where P(i - 1) lay, and O may only be touched between two products: the product
-      // before must be complete (its commit on o_full says so)
-      if (i > 0 && !mbar_wait(&o_full[g], (i - 1) & 1, abort_flag)) {
-        ok = false;
-        break;
-      }
-      if (move) {
-        const float corr = fast_exp2(m - (m_new == -INFINITY ? 0.0f : m_new));   // m = -inf gives 0
-        m = m_new;
-        l *= corr;
-        if (i > 0) {     // O = O * corr in tensor memory (the first product overwrites O, nothing to scale yet)
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const float m_new = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * a.scale_log2);   // scale > 0: the maximum commutes with it
+        // tensor-memory loads and stores are warp-wide: the warp moves its maxima together, as soon as one of
+        // its rows has outgrown its own by the step (a row that has not may follow the true maximum just as well)
+        const bool move = __any_sync(0xffffffffu, m_new > m + RESCALE_STEP);
+        // P(i) goes where P(i - PBUFS) lay: the product that read it must be complete
+        if (h == 0 && i >= PBUFS && !wait_pv(i - PBUFS)) {
+          ok = false;
+          break;
+        }
+        if (move) {
+          const float corr = fast_exp2(m - (m_new == -INFINITY ? 0.0f : m_new));   // m = -inf gives 0
+          m = m_new;
+          l *= corr;
+          if (h > 0) {   // this block's first piece: its partial sums, and its probabilities where this thread wrote them
+            l0 *= corr, l1 *= corr, l2 *= corr, l3 *= corr;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              const uint32_t at = p_row + ((uint32_t)(c << 4) ^ p_xor);
+              uint32_t w[4];
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(at) : "memory");
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const __nv_bfloat162 pair = *reinterpret_cast<const __nv_bfloat162*>(&w[e]);
+                w[e] = pack_bf16(__low2float(pair) * corr, __high2float(pair) * corr);
+              }
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(at), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+            }
+          }
+          if (i > 0) {     // O = O * corr in tensor memory, between two products: the one before must be complete
+            if (!wait_pv(i - 1)) {
+              ok = false;
+              break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-          for (int c0 = 0; c0 < D; c0 += 32) {
-            uint32_t t[32];
-            tmem_load32_nowait(o_addr + c0, t);
-            tmem_wait_loads();
+            for (int c0 = 0; c0 < D; c0 += 32) {
+              uint32_t t[32];
+              tmem_load32_nowait(o_addr + c0, t);
+              tmem_wait_loads();
 #pragma unroll
-            for (int k = 0; k < 32; ++k) t[k] = __float_as_uint(__uint_as_float(t[k]) * corr);
-            tmem_store32(o_addr + c0, t);
-          }
-          tmem_wait_stores();
-        }
-      }
-      const float m_use = m == -INFINITY ? 0.0f : m;
-      // probabilities into shared memory as the A operand of P V (two sub-tiles of 64 keys); the row's
-      // sum in four independent partial sums
-      float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
-#pragma unroll
-      for (int h = 0; h < BN / S_PIECE; ++h) {
-        if (S_PIECE < BN) {
-          load_piece(h);
-          if (h == BN / S_PIECE - 1) {   // the last read of S(i): the MMA thread may overwrite the buffer with S(i + 1)
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(&s_free[g]);
+              for (int k = 0; k < 32; ++k) t[k] = __float_as_uint(__uint_as_float(t[k]) * corr);
+              tmem_store32(o_addr + c0, t);
+            }
+            tmem_wait_stores();
           }
         }
+        const float m_use = m == -INFINITY ? 0.0f : m;
+        // probabilities into shared memory as the A operand of P V (sub-tile h of 64 keys); the row's sum
+        // in four independent partial sums
 #pragma unroll
         for (int c = 0; c < S_PIECE / 8; ++c) {
-          const int chunk = h * (S_PIECE / 8) + c;       // 16-byte chunk of the row's 128 keys: sub-tile chunk / 8
           uint32_t packed[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -589,16 +605,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
             else l3 += p0 + p1;
             packed[e] = pack_bf16(p0, p1);
           }
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + (chunk >> 3) * SUB + (((chunk & 7) << 4) ^ p_xor)),
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + h * SUB + ((uint32_t)(c << 4) ^ p_xor)),
                        "r"(packed[0]), "r"(packed[1]), "r"(packed[2]), "r"(packed[3]) : "memory");
         }
       }
+      if (!ok) break;
       l += (l0 + l1) + (l2 + l3);
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      mbar_arrive(&p_full[g]);
+      mbar_arrive(&p_full[2 * g + i % PBUFS]);
     }
-    if (ok && my_n > 0) ok = mbar_wait(&o_full[g], (my_n - 1) & 1, abort_flag) && !*abort_flag;
+    if (ok && my_n > 0) ok = wait_pv(my_n - 1) && !*abort_flag;
     if (!ok) {
       *abort_flag = 1;
       atomicCAS(a.error_word, 0, ERR_SOFTMAX);

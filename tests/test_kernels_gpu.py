@@ -392,12 +392,14 @@ def test_a_bounded_wait_runs_out_and_the_kernel_returns():
 # ------------------------------------------------------------------------------ tensor-core attention
 
 def _attention_case(seqs, heads, kv_heads, d, page, window, seed, far_key=False, drop_passed=False,
-                    poison_tail=True):
+                    poison_tail=True, jumps=()):
     """seqs: [(q_len, kv_len)].  Fills a scrambled paged cache, runs the attention the launcher picks
     and the dense reference.  `drop_passed` (with a window): pages that every query of the step has
     passed are taken out of the block table and filled with NaN, as the cache manager gives them back.
     `poison_tail`: positions at and beyond a request's length in its last page hold NaN, as a page
-    may that an earlier, longer request left behind."""
+    may that an earlier, longer request left behind.  `jumps`: [(position, level)]: the key at that
+    position scores about `level` (in powers of two) above an ordinary key for every query, so the
+    running maximum of a row jumps there."""
     from bare_cuda_4gib_b200.kernels import attention as fast
     from bare_cuda_4gib_b200.kernels.lib import CacheView
 
@@ -419,6 +421,9 @@ def _attention_case(seqs, heads, kv_heads, d, page, window, seed, far_key=False,
             k = (0.05 * k.float()).to(torch.bfloat16)
             k[3 % kv_len] = 0
             k[3 % kv_len, :, 0] = 60.0
+        for pos, level in jumps:
+            if pos < kv_len:      # score = 8 * k[0] / sqrt(d) in natural units
+                k[pos, :, 0] = level * math.log(2.0) * math.sqrt(d) / 8.0
         nb = -(-kv_len // page)
         pages = perm[at: at + nb]
         at += nb
@@ -445,6 +450,9 @@ def _attention_case(seqs, heads, kv_heads, d, page, window, seed, far_key=False,
     if far_key:
         q = torch.zeros_like(q)
         q[:, :, 0] = 4.0
+    if jumps:
+        q = (0.1 * q.float()).to(torch.bfloat16)
+        q[:, :, 0] = 8.0
     starts = [sum(x for x, _ in seqs[:i]) for i in range(len(seqs))]
     ctx = _ctx()
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
@@ -517,6 +525,22 @@ def test_attention_tcgen05_long_contexts_random_data(d, heads, kv_heads, page):
     from bare_cuda_4gib_b200.kernels import attention as fast
     seqs = [(2048, 2048), (300, 1500), (5, 1900), (1, 1000), (130, 641)]
     got, want, ctx = _attention_case(seqs, heads, kv_heads, d, page, 0, seed=d + page)
+    plan = fast.plan_for(d, heads, kv_heads)
+    assert plan.tc is not None and any(v[3] == plan.prefill_rows for k, v in ctx.extras.items())   # the tcgen05 kernel ran
+    _close(got, want, 2 ** -7, 4e-3)
+
+
+@pytest.mark.parametrize("d,heads,kv_heads", [(64, 8, 2), (128, 4, 2)])
+def test_attention_tcgen05_rescales_when_a_rows_maximum_jumps(d, heads, kv_heads):
+    """With random data a row's maximum settles within its first keys and the accumulated output is
+    never rescaled again.  Here single keys score 2^12 above everything before them, in the first
+    and in the second half of a block of 128 keys and several blocks apart, so that the
+    probabilities already written for the block's first half, the row sums and the accumulator in
+    tensor memory all have to be rescaled: a missed or doubled rescale is off by a factor of 4,096."""
+    from bare_cuda_4gib_b200.kernels import attention as fast
+    jumps = [(200, 12), (300, 24), (700, 36), (1000, 48), (1001, 60)]
+    seqs = [(1200, 1200), (300, 1100), (140, 333)]
+    got, want, ctx = _attention_case(seqs, heads, kv_heads, d, 64, 0, seed=d, jumps=jumps)
     plan = fast.plan_for(d, heads, kv_heads)
     assert plan.tc is not None and any(v[3] == plan.prefill_rows for k, v in ctx.extras.items())   # the tcgen05 kernel ran
     _close(got, want, 2 ** -7, 4e-3)
