@@ -93,17 +93,25 @@ def bench_gemm(a):
     act = ctx.ws.get("a", (a.rows, a.inner), torch.bfloat16)
     act.copy_(torch.randn(a.rows, a.inner, device="cuda"))
     state = {"i": 0}
-    out_dtype = torch.float32 if a.partials else torch.bfloat16
+    out_dtype = torch.float32 if (a.partials or a.add_norm) else torch.bfloat16
+    epilogue = None
+    if a.add_norm:      # the product adds into a float32 residual stream and prepares the norm that reads it next
+        from ..kernels import lib as K
+        norm = types.SimpleNamespace(prenormable=True, tensors={"weight": torch.ones(a.out, device="cuda", dtype=torch.bfloat16)},
+                                     params={"eps": 1e-5})
+        epilogue = K.AddTo(torch.zeros(a.rows, a.out, device="cuda"), norm)
 
     def run():
         plan = plans[state["i"] % copies]
         state["i"] += 1
-        gemm.run(ctx, plan, act, a.rows, out_dtype, "out", a.partials, a.swiglu)
+        gemm.run(ctx, plan, act, a.rows, out_dtype, "out", a.partials, a.swiglu, epilogue)
 
     us = _time(run, a.iters, a.warmup)
     gemm.check_errors()
     out_bytes = a.rows * a.out * (4 if a.partials else 2)
-    _report(f"gemm rows={a.rows} out={a.out} in={a.inner} swiglu={a.swiglu} copies={copies}", us,
+    if a.add_norm:
+        out_bytes = a.rows * a.out * (4 + 4 + 2)      # residual read and written, prepared input written
+    _report(f"gemm rows={a.rows} out={a.out} in={a.inner} swiglu={a.swiglu} add_norm={a.add_norm} copies={copies}", us,
             weight_bytes + a.rows * a.inner * 2 + out_bytes, 2.0 * a.rows * n * a.inner)
 
 
@@ -240,6 +248,8 @@ def main(argv=None) -> int:
     g.add_argument("--in", dest="inner", type=int, required=True)
     g.add_argument("--swiglu", action="store_true")
     g.add_argument("--partials", action="store_true", help="float32 output that may be split over K")
+    g.add_argument("--add-norm", action="store_true",
+                   help="add into a float32 residual stream and prepare the next norm (many-token steps)")
     g.add_argument("--l2-mb", type=int, default=126)
     v = sub.add_parser("gemv", parents=[common])
     v.add_argument("--tokens", type=int, default=8)
