@@ -5,22 +5,22 @@
 // the cluster decode kernel.  As there, nothing of cuongvng/bare-cuda-4gib's [heads, T, keys] score
 // buffer exists (engine/kernels/attention_qk.cu:49-68, softmax.cu:28-42, attention_av.cu:24-44).
 //
-// One thread block = 256 packed rows of one request and one key/value head: two tiles of 128 rows
-// that see (almost) the same keys, so every key and value block is brought into shared memory once
-// for both.  Keys are visited in blocks of 128 positions:
+// One thread block = one or two tiles of 128 packed rows of one request and one key/value head (two
+// at head size 128: they see (almost) the same keys, so every key and value block is brought into
+// shared memory once for both; one at head size 64, where two blocks share an SM instead).  Keys are
+// visited in blocks of 128 positions:
 //   loader warp    copies the blocks' keys and values from the request's pages into 128-byte-
 //                  swizzled shared memory with TMA (one tensor map over the cache group's whole
 //                  pool, a box per page piece).  Key tiles and value tiles go through ONE ring of
 //                  slots in the order K(0) V(0) K(1) V(1) ..., each slot given back by the commit of
 //                  the last product that reads it (4 slots at head size 64, 3 at 128);
 //   MMA thread     S_g = Q_g K^T (M 128, N 128, K head size) into tile g's S columns of tensor memory;
-//   softmax warps  two groups of four warps; group g owns tile g and sees every key block of it.
+//   softmax warps  a group of four warps per tile; group g owns tile g and sees every key block of it.
 //                  First it stages Q_g with cp.async.  Then, one thread per row: read the row of S
 //                  from tensor memory once, 64 columns at a time, scale, mask, running maximum and
 //                  sum in float32 (base 2, kept in several independent partial maxima and sums so
 //                  that no long dependent chain forms), write P as bfloat16 into swizzled shared
-//                  memory (the A operand of the second product; two P buffers per group at head
-//                  size 64, so that P(i) is written while P(i - 1) V still runs);
+//                  memory (the A operand of the second product);
 //   MMA thread     O_g (+)= P_g V (M 128, N 64 per 64 value columns, K 128): O accumulates in
 //                  tensor memory over all key blocks; V stays as it lies in the cache
 //                  ([key][channel]) and is described to the MMA as an MN-major operand;
@@ -28,8 +28,8 @@
 //                  maximum only when that has grown by more than 2^8, so O (and the row's sum, and
 //                  the half row of P that may already be written) is rescaled rarely; at the end
 //                  every thread divides its row of O by its sum and stores it: no merge between threads.
-// While one group exponentiates, the other reads its S, and the MMA thread serves whichever group
-// is ready next.
+// While one group exponentiates, the other (of the same block or of the SM's other block) reads its S,
+// and a block's MMA thread serves whichever of its groups is ready next.
 // A request's last page may hold, behind its last key, what an earlier request left there: masked
 // scores never see it, but 0 x NaN would reach O through P V, so the loader clears those value rows
 // in shared memory before the last block's P V may run.
@@ -51,24 +51,34 @@ constexpr int D = HEAD_DIM;
 static_assert(D == 64 || D == 128, "the tcgen05 attention kernel is built for head sizes 64 and 128");
 constexpr int KA = D / 64;       // 64-wide sub-tiles ("atoms") along the head dimension
 constexpr int BM = 128;          // packed rows per tile (one softmax group)
-constexpr int TILES = 2;         // tiles per block
+// Head size 64: one tile per block and two blocks per SM (112 KB of shared memory and 256 columns of
+// tensor memory each), so one block's start and end hide behind the other's key blocks (2,048-token
+// prompt 44.1 -> 42.8 us, 8,192 tokens 511 -> 473 us).  Head size 128 has room for one block per SM
+// only: two tiles per block, which then share every key and value tile.
+#ifndef ATTN_TILES
+#define ATTN_TILES (HEAD_DIM == 64 ? 1 : 2)
+#endif
+constexpr int TILES = ATTN_TILES;   // tiles per block (1: two blocks share an SM)
+static_assert(TILES == 1 || TILES == 2, "one or two tiles per block");
 constexpr int BLOCK_ROWS = TILES * BM;
 constexpr int BN = 128;          // keys per block
 constexpr int SUB = 128 * 128;   // bytes of a [128 rows x 64 bf16] swizzled sub-tile
 constexpr int Q_BYTES = KA * SUB;        // one tile's queries
 constexpr int TILE_BYTES = KA * SUB;     // one key tile or one value tile
 constexpr int P_BYTES = 2 * SUB;         // [128 rows x 128 keys] as two sub-tiles
-constexpr int PBUFS = D == 64 ? 2 : 1;   // P buffers per group: with two, P(i) is written while P(i - 1) V still runs
-constexpr int SLOTS = D == 64 ? 4 : 3;   // key and value tiles in flight (what shared memory allows)
-constexpr int SOFTMAX_THREADS = 256, LOADER_THREADS = 32;
+#ifndef ATTN_SLOTS
+#define ATTN_SLOTS (HEAD_DIM == 64 ? 4 : 3)
+#endif
+constexpr int SLOTS = ATTN_SLOTS;   // key and value tiles in flight (what shared memory allows)
+constexpr int SOFTMAX_THREADS = 128 * TILES, LOADER_THREADS = 32;
 constexpr int MMA_WARP = SOFTMAX_THREADS / 32;
 constexpr int NUM_THREADS = SOFTMAX_THREADS + 32 + LOADER_THREADS;   // warps 0-7 softmax, 8 MMA, 9 loader
-constexpr int TMEM_COLS = 512;
-constexpr int O_COL = 256;       // first tensor-memory column of the P V results (S buffers at 0 and 128)
+constexpr int TMEM_COLS = 256 * TILES;
+constexpr int O_COL = TILES * BN;  // first tensor-memory column of the P V results (the S buffers lie before it)
 constexpr int GROUP_THREADS = 128;
 constexpr int S_PIECE = 64;      // columns of S a softmax thread holds in registers at a time (one sub-tile of P)
 constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;
-constexpr size_t SMEM_BYTES = TILES * Q_BYTES + SLOTS * TILE_BYTES + TILES * PBUFS * P_BYTES + 256;   // 2 * SLOTS + 17 barriers, 2 words
+constexpr size_t SMEM_BYTES = TILES * Q_BYTES + SLOTS * TILE_BYTES + TILES * P_BYTES + 256;   // 2 * SLOTS + 11 barriers, 2 words
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -207,22 +217,20 @@ struct AttnArgs {
 
 constexpr int ERR_LOADER = 11, ERR_MMA = 12, ERR_SOFTMAX = 13, ERR_LAYOUT = 14;
 
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS, TILES == 1 ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs a) {
   extern __shared__ __align__(1024) uint8_t smem[];   // swizzled tiles need 1024-byte alignment (checked below)
   uint8_t* q_smem = smem;                              // [TILES][KA sub-tiles]
   uint8_t* ring = q_smem + TILES * Q_BYTES;            // [SLOTS][KA sub-tiles]: key and value tiles in turn
-  uint8_t* p_smem = ring + SLOTS * TILE_BYTES;         // [TILES][PBUFS][two sub-tiles of 64 keys]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + TILES * PBUFS * P_BYTES);
+  uint8_t* p_smem = ring + SLOTS * TILE_BYTES;         // [TILES][two sub-tiles of 64 keys]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + TILES * P_BYTES);
   uint64_t* tile_full = bars;               // [SLOTS] loader -> MMA: the slot's tile has landed
   uint64_t* tile_empty = tile_full + SLOTS; // [SLOTS] MMA (commit) -> loader
   uint64_t* q_full = tile_empty + SLOTS;    // [2] softmax group -> MMA: Q_g staged
   uint64_t* s_full = q_full + 2;            // [2] MMA (commit) -> softmax, per group
-  // (with two P buffers a group may be a whole block ahead of the MMA thread: a barrier per buffer,
-  // so that no barrier ever runs two phases ahead of the one who waits on it)
-  uint64_t* p_full = s_full + 2;            // [2][2] softmax -> MMA: P written, per group and P buffer
-  uint64_t* o_full = p_full + 4;            // [2][2] MMA (commit) -> softmax, per group and P buffer: P(i) V is complete
-  uint64_t* s_free = o_full + 4;            // [2] softmax -> MMA: the group holds its S values in registers
+  uint64_t* p_full = s_full + 2;            // [2] softmax -> MMA: P written, per group
+  uint64_t* o_full = p_full + 2;            // [2] MMA (commit) -> softmax, per group: P(i) V is complete
+  uint64_t* s_free = o_full + 2;            // [2] softmax -> MMA: the group holds its S values in registers
   uint64_t* v_clean = s_free + 2;           // loader -> MMA: the last value tile holds no stale rows
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(v_clean + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -242,7 +250,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
   const int seq = a.tile_seq[tile];
   int q_start = 0, q_len = 0, kv_len = 0, row0 = 0, n_rows = 0, pos0 = 0, group = 1;
   // per group (tile of 128 rows): its key blocks [g_lo, g_hi) and the positions of its first and last row
-  int g_lo[TILES] = {0, 0}, g_hi[TILES] = {0, 0}, g_min_pos[TILES] = {0, 0}, g_max_pos[TILES] = {0, 0};
+  int g_lo[TILES] = {}, g_hi[TILES] = {}, g_min_pos[TILES] = {}, g_max_pos[TILES] = {};
   int kb_lo = 0, n_kb = 0;   // the union of the two ranges: what the loader brings
   if (seq >= 0) {
     group = a.q_heads / a.cache.kv_heads;
@@ -281,10 +289,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
     for (int b = 0; b < 2; ++b) {
       mbar_init(&q_full[b], GROUP_THREADS);
       mbar_init(&s_full[b], 1);
-      mbar_init(&p_full[2 * b], GROUP_THREADS);
-      mbar_init(&p_full[2 * b + 1], GROUP_THREADS);
-      mbar_init(&o_full[2 * b], 1);
-      mbar_init(&o_full[2 * b + 1], 1);
+      mbar_init(&p_full[b], GROUP_THREADS);
+      mbar_init(&o_full[b], 1);
       mbar_init(&s_free[b], GROUP_THREADS);
     }
     mbar_init(v_clean, LOADER_THREADS);
@@ -407,35 +413,43 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
         const bool first = i == 0;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t v_addr = smem_u32(ring) + slot * TILE_BYTES;
-        const uint32_t p_addr = smem_u32(p_smem) + (g * PBUFS + i % PBUFS) * P_BYTES;
+        const uint32_t p_addr = smem_u32(p_smem) + g * P_BYTES;
 #pragma unroll
         for (int vt = 0; vt < KA; ++vt)
 #pragma unroll
           for (int kk = 0; kk < BN / 16; ++kk)
             umma_bf16(tmem_base + O_COL + g * D + vt * 64, smem_desc_sw128(p_addr + (kk >> 2) * SUB) + 2 * (kk & 3),
                       smem_desc_sw128(v_addr + vt * SUB) + (uint64_t)(kk * 2048 >> 4), idesc_o, (kk > 0 || !first) ? 1u : 0u);
-        umma_commit(&o_full[2 * g + i % PBUFS]);
+        umma_commit(&o_full[g]);
         if (last) umma_commit(&tile_empty[slot]);
       };
       // The two groups are served as they come: a group's next S as soon as it reports that it holds the
       // S before it in registers (and the key tile has landed), its P V as soon as it reports P (and has
       // read the O_block before).  Nothing is waited for while the other group could be served.
       bool ok = true;
-      int s_next[TILES] = {0, 0}, pv_next[TILES] = {0, 0};      // per group: its next block to issue S / P V for
-      const int n_g[TILES] = {g_hi[0] - g_lo[0], g_hi[1] - g_lo[1]};
+      int s_next[TILES] = {}, pv_next[TILES] = {};      // per group: its next block to issue S / P V for
+      int n_g[TILES];
+#pragma unroll
+      for (int g = 0; g < TILES; ++g) n_g[g] = g_hi[g] - g_lo[g];
+      auto unfinished = [&]() {
+        bool any = false;
+#pragma unroll
+        for (int g = 0; g < TILES; ++g) any = any || pv_next[g] < n_g[g];
+        return any;
+      };
       auto landed = [&](int n) { return mbar_try_wait(&tile_full[n % SLOTS], (n / SLOTS) & 1); };
       unsigned long long idle_since = 0;
       unsigned idle_spins = 0;
-      while (ok && (pv_next[0] < n_g[0] || pv_next[1] < n_g[1])) {
+      while (ok && unfinished()) {
         bool progress = false;
 #pragma unroll
         for (int g = 0; g < TILES; ++g) {
-          const int o = 1 - g;
+          const int o = TILES > 1 ? 1 - g : 0;   // the other group, if there is one
           if (s_next[g] < n_g[g]) {
             const int i = s_next[g], jj = g_lo[g] + i - kb_lo;
             if ((i == 0 ? mbar_try_wait(&q_full[g], 0) : mbar_try_wait(&s_free[g], (i - 1) & 1)) && landed(2 * jj)) {
               // the other group is done with K(jj) if it never reads it or has issued its S for it already
-              const bool last = !active(o, jj) || s_next[o] > kb_lo + jj - g_lo[o];
+              const bool last = TILES == 1 || !active(o, jj) || s_next[o] > kb_lo + jj - g_lo[o];
               issue_s(g, jj, last);
               s_next[g] = i + 1;
               progress = true;
@@ -443,9 +457,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
           }
           if (pv_next[g] < s_next[g]) {
             const int i = pv_next[g], jj = g_lo[g] + i - kb_lo;
-            if (mbar_try_wait(&p_full[2 * g + i % PBUFS], (uint32_t)(i / PBUFS) & 1u) && landed(2 * jj + 1) &&
+            if (mbar_try_wait(&p_full[g], (uint32_t)i & 1u) && landed(2 * jj + 1) &&
                 (kb_lo + jj != stale_block || mbar_try_wait(v_clean, 0))) {
-              const bool last = !active(o, jj) || pv_next[o] > kb_lo + jj - g_lo[o];
+              const bool last = TILES == 1 || !active(o, jj) || pv_next[o] > kb_lo + jj - g_lo[o];
               issue_pv(g, jj, last, i);
               pv_next[g] = i + 1;
               progress = true;
@@ -462,9 +476,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
       if (!ok) {
         *abort_flag = 1;
         atomicCAS(a.error_word, 0, ERR_MMA);
-        umma_commit(&s_full[0]);   // release whoever waits
-        umma_commit(&s_full[1]);
-        for (int b = 0; b < 4; ++b) umma_commit(&o_full[b]);
+        for (int b = 0; b < TILES; ++b) umma_commit(&s_full[b]);   // release whoever waits
+        for (int b = 0; b < TILES; ++b) umma_commit(&o_full[b]);
       }
     }
   } else {
@@ -502,9 +515,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
     constexpr float RESCALE_STEP = 8.0f;
     float m = -INFINITY, l = 0.0f;
     // this row of the group's P tiles (swizzled: chunk c of row r lies at c ^ (r % 8) inside the row's 128 bytes)
-    const uint32_t p_row0 = smem_u32(p_smem) + g * PBUFS * P_BYTES + (r >> 3) * 1024 + (r & 7) * 128, p_xor = (uint32_t)(r & 7) << 4;
-    // P(k) V of this group is complete (its commit arrives on the barrier of P buffer k % PBUFS)
-    auto wait_pv = [&](int k) { return mbar_wait(&o_full[2 * g + k % PBUFS], (uint32_t)(k / PBUFS) & 1u, abort_flag); };
+    const uint32_t p_row = smem_u32(p_smem) + g * P_BYTES + (r >> 3) * 1024 + (r & 7) * 128, p_xor = (uint32_t)(r & 7) << 4;
+    // P(k) V of this group is complete
+    auto wait_pv = [&](int k) { return mbar_wait(&o_full[g], (uint32_t)k & 1u, abort_flag); };
     bool ok = true;
     for (int i = 0; i < my_n && ok; ++i) {
       const int key0 = (my_lo + i) * BN;
@@ -512,7 +525,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const bool all_visible = key0 + BN - 1 <= tile_min_pos && (a.window <= 0 || key0 > tile_max_pos - a.window);
-      const uint32_t p_row = p_row0 + (i % PBUFS) * P_BYTES;
       // The row of S is read once, in two pieces of 64 columns (one sub-tile of P each).  Each piece
       // settles the maximum for itself: should the second piece move it, the probabilities of the
       // first, which this thread has just written, are rescaled where they lie (rare, as is every move).
@@ -547,8 +559,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
         // tensor-memory loads and stores are warp-wide: the warp moves its maxima together, as soon as one of
         // its rows has outgrown its own by the step (a row that has not may follow the true maximum just as well)
         const bool move = __any_sync(0xffffffffu, m_new > m + RESCALE_STEP);
-        // P(i) goes where P(i - PBUFS) lay: the product that read it must be complete
-        if (h == 0 && i >= PBUFS && !wait_pv(i - PBUFS)) {
+        // P(i) goes where P(i - 1) lay: the product that read it must be complete
+        if (h == 0 && i > 0 && !wait_pv(i - 1)) {
           ok = false;
           break;
         }
@@ -571,11 +583,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
               asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(at), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
             }
           }
-          if (i > 0) {     // O = O * corr in tensor memory, between two products: the one before must be complete
-            if (!wait_pv(i - 1)) {
-              ok = false;
-              break;
-            }
+          if (i > 0) {     // O = O * corr in tensor memory, between two products (the one before is complete: see above)
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
             for (int c0 = 0; c0 < D; c0 += 32) {
@@ -613,7 +621,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs 
       l += (l0 + l1) + (l2 + l3);
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      mbar_arrive(&p_full[2 * g + i % PBUFS]);
+      mbar_arrive(&p_full[g]);
     }
     if (ok && my_n > 0) ok = wait_pv(my_n - 1) && !*abort_flag;
     if (!ok) {
