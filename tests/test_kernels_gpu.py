@@ -334,6 +334,28 @@ def test_gemm_tcgen05_adds_into_the_residual_and_prepares_the_next_norm(m, n, k,
         _close(res.tensor.float(), full, 2 ** -8, 1e-4)
 
 
+def test_gemm_tcgen05_leaves_the_add_to_its_caller_when_no_norm_can_be_prepared():
+    """An adding epilogue whose following norm is unknown, or not one whose factor is a single number
+    per row, is not the kernel's: the plain product comes back and the residual stream is untouched."""
+    from bare_cuda_4gib_b200.kernels import gemm
+    from bare_cuda_4gib_b200.kernels import lib as K
+    torch.manual_seed(5)
+    m, n, k = 300, 256, 128
+    ctx = _ctx()
+    a = ctx.ws.get("a", (m, k), torch.bfloat16)
+    a.copy_(torch.randn(m, k, device=DEV))
+    w = torch.randn(n, k, device=DEV).to(torch.bfloat16)
+    residual = torch.randn(m, n, device=DEV)
+    before = residual.clone()
+    other = types.SimpleNamespace(prenormable=False, tensors={"weight": torch.ones(n, device=DEV)}, params={"eps": 1e-5})
+    for then in (None, other):
+        res = gemm.run(ctx, gemm.plan_for(w), a, m, torch.float32, "out", True, False, epilogue=K.AddTo(residual, then))
+        gemm.check_errors()
+        assert res is not None and ctx.prenormed is None
+        assert torch.equal(residual, before)
+        _close(res.tensor.float().sum(0) if res.n > 1 else res.tensor.float(), a.double() @ w.double().t(), 1e-5, 1e-4 * math.sqrt(k))
+
+
 @pytest.mark.parametrize("m,inter,k", [(3, 176, 64), (40, 5632, 256), (130, 256, 96), (300, 200, 128), (9, 2816, 512),
                                        (700, 176, 64), (2048, 5632, 128), (257, 1000, 96), (90, 1408, 128), (100, 5632, 128),
                                        (200, 1000, 96), (256, 2816, 320)])
