@@ -6,7 +6,7 @@
 //
 // A decode step at batch 8 reads 17 MB of keys and values per layer, about 2.5 us of memory
 // time, so the kernel's time is the length of its chain of dependent memory trips.  Here:
-//   * A tile's key blocks (64 positions each) are dealt round-robin to the warps of a thread
+//   * A tile's key blocks (64 positions each, 32 at head size 128) are dealt round-robin to the warps of a thread
 //     block cluster: `gridDim.z` blocks (up to 8) of four warps.  Every warp requests all of its
 //     key and value blocks at once, as TMA copies over the cache pool's tensor map straight into
 //     128-byte-swizzled shared memory (one trip for the whole tile), runs its own flash-attention
@@ -38,12 +38,20 @@ namespace {
 
 constexpr int D = HEAD_DIM;
 static_assert(D == 64 || D == 128, "HEAD_DIM must be 64 or 128");
-constexpr int BN = 64;                      // keys per block
+// A warp's request for one key block is 16 KB of keys and 16 KB of values whatever the head size: 64
+// positions at head size 64, 32 at 128 (measured at head size 128, batch 8 to 64 and contexts of 2,048
+// to 8,192: 0.79 to 0.93 of the copy bandwidth with 32 positions, 0.55 to 0.74 with 64, whose 146 KB of
+// shared memory leave room for one block per SM only).
+#ifndef DECODE_KEY_BLOCK
+#define DECODE_KEY_BLOCK (HEAD_DIM == 128 ? 32 : 64)
+#endif
+constexpr int BN = DECODE_KEY_BLOCK;        // keys per block
+static_assert(BN == 32 || BN == 64, "key blocks of 32 or 64 positions");
 constexpr int BM = 16;                      // packed rows per tile
 constexpr int WARPS = 4;
 constexpr int THREADS = WARPS * 32;
 constexpr int SUBS = D / 64;                // 64-column sub-tiles per key row
-constexpr int SUB_BYTES = BN * 128;         // one sub-tile: [64 keys][128 bytes], swizzled
+constexpr int SUB_BYTES = BN * 128;         // one sub-tile: [BN keys][128 bytes], swizzled
 constexpr int KV_BYTES = 2 * SUBS * SUB_BYTES;   // keys then values of one block
 constexpr int MAX_SLOTS = 3;                // key blocks a warp may have in flight
 constexpr int QLD = D + 8;
@@ -492,6 +500,7 @@ size_t smem_bytes(int slots) {
 }  // namespace
 
 extern "C" int llm_attention_decode_head_dim() { return D; }
+extern "C" int llm_attention_decode_key_block() { return BN; }
 
 
 // Writes the 128-byte tensor map of a cache group's pool: `rows` rows of D bfloat16 starting at

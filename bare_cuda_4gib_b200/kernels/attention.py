@@ -75,6 +75,8 @@ def decode_lib(head_dim: int):
         l.llm_attention_decode.restype = c_int
         l.llm_attention_decode_pool_map.argtypes = [P, P, L, I]
         l.llm_attention_decode_pool_map.restype = c_int
+        l.llm_attention_decode_key_block.restype = c_int
+        l.key_block = int(l.llm_attention_decode_key_block())
         _decode_libs[head_dim] = l
     return l
 
@@ -100,7 +102,7 @@ class AttentionPlan:
 
     def decode_map(self, cache: CacheView):
         """The decode kernel's tensor map over a cache group's pool (boxes of at most 64 rows)."""
-        box_rows = math.gcd(KEY_BLOCK, cache.page_tokens)
+        box_rows = math.gcd(self.decode.key_block, cache.page_tokens)
         key = (cache.pool_ptr, cache.pool_elems, box_rows)
         m = self._decode_maps.get(key)
         if m is None:
@@ -112,7 +114,7 @@ class AttentionPlan:
         return m, box_rows
 
     def decode_usable(self, cache: CacheView) -> bool:
-        return self.decode is not None and cache.pool_ptr != 0 and math.gcd(KEY_BLOCK, cache.page_tokens) >= 8
+        return self.decode is not None and cache.pool_ptr != 0 and math.gcd(self.decode.key_block, cache.page_tokens) >= 8
 
     def pool_map(self, cache: CacheView):
         """The TMA tensor map over a cache group's whole pool (one per pool) and its box height."""
