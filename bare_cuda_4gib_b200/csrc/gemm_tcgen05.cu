@@ -302,13 +302,15 @@ __device__ __forceinline__ void epilogue_tokens_on_rows(uint32_t lane_base, int 
 #pragma unroll
       for (int j = 0; j < 16; ++j) g[j] = u[j] = 0u;
     }
+    // (rows past the step's last token hold whatever the activation buffer held before: nothing is
+    // computed from them, least of all a division, whose slow path such values would take)
+    if (t >= n_tokens) continue;
     float v[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       v[j] = __uint_as_float(g[j]) * rs;
       if (MODE == 1) v[j] = v[j] / (1.0f + expf(-v[j])) * (__uint_as_float(u[j]) * rs);
     }
-    if (t >= n_tokens) continue;
     const int f = f0 + c0;
     const long long at = (long long)t * ld_out + f;
     if (vec_ok && f + 16 <= n_features) {
