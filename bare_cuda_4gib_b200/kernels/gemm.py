@@ -137,8 +137,9 @@ TOKENS_ON_ROWS_ABOVE = 240    # steps with more rows put 128 tokens on the MMA r
                               # of 256 rows takes 2.32 ms that way and 2.53 ms with the weights on the MMA rows, one of 224 rows 2.5 and 2.23
 # The SwiGLU product changes over earlier: with the weights on the MMA rows a block holds only 64
 # outputs, so from about a hundred tokens on the other orientation's wider tiles measured faster
-# (TinyLlama's feed-forward at 128 / 256 tokens: 16 / 19 us against 23 / 48 us).
-SWIGLU_TOKENS_ON_ROWS_ABOVE = 96
+# (TinyLlama's feed-forward at 128 / 256 tokens: 16 / 19 us against 23 / 48 us; at 48 / 64 / 80 / 96 tokens 16.3 us
+# that way, whatever the count, against 14.9 / 16.8 / 18.5 / 20.2 us).
+SWIGLU_TOKENS_ON_ROWS_ABOVE = 60
 
 
 def feature_tile(rows: int, n_out: int, swiglu: bool) -> int:
